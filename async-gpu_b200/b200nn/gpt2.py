@@ -1,0 +1,247 @@
+"""GPT-2 models, named as in ``gpu_host::nn::models::gpt2`` (models/gpt2.rs)."""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import (ERR_SHAPE, GpuTensor, KernelRegistry, NnError, PROF_NAMES, _Cfg, _LayerW, _Weights, _f32, _f32p, _u32,
+               _u32p)
+
+
+@dataclass
+class Gpt2Config:
+    """``Gpt2Config`` (gpt2.rs:20-93)."""
+    n_layer: int = 12
+    n_embd: int = 768
+    n_head: int = 12
+    vocab_size: int = 50257
+    n_positions: int = 1024
+    layer_norm_epsilon: float = 1e-5
+
+    @classmethod
+    def small(cls):
+        return cls(12, 768, 12)
+
+    @classmethod
+    def medium(cls):
+        return cls(24, 1024, 16)
+
+    @classmethod
+    def large(cls):
+        return cls(36, 1280, 20)
+
+    @classmethod
+    def xl(cls):
+        return cls(48, 1600, 25)
+
+    def head_dim(self):
+        return self.n_embd // self.n_head
+
+    def ffn_dim(self):
+        return 4 * self.n_embd
+
+    def as_dict(self):
+        return dict(n_layer=self.n_layer, n_embd=self.n_embd, n_head=self.n_head, vocab_size=self.vocab_size,
+                    n_positions=self.n_positions, layer_norm_epsilon=self.layer_norm_epsilon)
+
+    def _c(self):
+        return _Cfg(self.n_layer, self.n_embd, self.n_head, self.vocab_size, self.n_positions, self.layer_norm_epsilon)
+
+
+_LAYER_KEYS = [("ln_1_weight", "ln_1.weight", 1), ("ln_1_bias", "ln_1.bias", 1),
+               ("c_attn_weight", "attn.c_attn.weight", 3), ("c_attn_bias", "attn.c_attn.bias", 3),
+               ("c_proj_weight", "attn.c_proj.weight", 1), ("c_proj_bias", "attn.c_proj.bias", 1),
+               ("ln_2_weight", "ln_2.weight", 1), ("ln_2_bias", "ln_2.bias", 1),
+               ("mlp_fc_weight", "mlp.c_fc.weight", 4), ("mlp_fc_bias", "mlp.c_fc.bias", 4),
+               ("mlp_proj_weight", "mlp.c_proj.weight", 4), ("mlp_proj_bias", "mlp.c_proj.bias", 1)]
+
+
+def _pack_weights(cfg: Gpt2Config, weights: dict):
+    """``Gpt2Weights`` (model.rs:112-154) from a dict keyed as the checkpoint is: ``wte``, ``wpe``,
+    ``ln_f.weight|bias`` and ``h.{i}.<name>`` with dense weights in Conv1D layout [in,out]."""
+    keep = []
+    d = cfg.n_embd
+
+    def P(name, numel):
+        a, p = _f32(weights[name])
+        if a.size != numel:
+            raise NnError(ERR_SHAPE, f"{name}: expected {numel} elements, got {a.size}")
+        keep.append(a)
+        return p
+
+    layers = (_LayerW * cfg.n_layer)()
+    for i in range(cfg.n_layer):
+        for field, key, mult in _LAYER_KEYS:
+            numel = mult * d * (d if field.endswith("_weight") and not field.startswith("ln_") else 1)
+            setattr(layers[i], field, P(f"h.{i}.{key}", numel))
+    w = _Weights(P("wte", cfg.vocab_size * d), P("wpe", cfg.n_positions * d), P("ln_f.weight", d), P("ln_f.bias", d),
+                 layers)
+    keep.append(layers)
+    return w, keep
+
+
+class KvCache:
+    """Device KV cache (``KvCache``, gpt2.rs:1064-1117) with a batch axis."""
+
+    def __init__(self, model: "Gpt2Model", batch: int = 1, capacity: int | None = None):
+        self.model = model
+        self.h = C.c_void_p()
+        cap = capacity or model.config.n_positions
+        model.reg.check(model.reg.lib.b200nn_kvcache_create(model.h, batch, cap, C.byref(self.h)))
+
+    def len(self):
+        return int(self.model.reg.lib.b200nn_kvcache_len(self.h))
+
+    def is_empty(self):
+        return self.len() == 0
+
+    def reset(self):
+        self.model.reg.check(self.model.reg.lib.b200nn_kvcache_reset(self.h))
+
+    def __del__(self):
+        try:
+            if self.h and self.model.h and self.model.reg.h:
+                self.model.reg.lib.b200nn_kvcache_destroy(self.h)
+        except Exception:
+            pass
+
+
+class Gpt2Model:
+    """``Gpt2Model::from_weights`` (gpt2.rs:337-404) and its forward / generate family."""
+    _int4 = False
+
+    def __init__(self, weights: dict, config: Gpt2Config, reg: KernelRegistry, flags: int = 0, group_size: int = 128):
+        self.reg, self.config, self.flags = reg, config, flags
+        cw, keep = _pack_weights(config, weights)
+        cc = config._c()
+        self.h = C.c_void_p()
+        if self._int4:
+            rc = reg.lib.b200nn_int4_gpt2_create(reg.h, C.byref(cc), C.byref(cw), group_size, flags, C.byref(self.h))
+        else:
+            rc = reg.lib.b200nn_gpt2_create(reg.h, C.byref(cc), C.byref(cw), flags, C.byref(self.h))
+        del keep
+        reg.check(rc)
+        self._group_size = group_size
+
+    @classmethod
+    def from_weights(cls, weights, config, reg, **kw):
+        return cls(weights, config, reg, **kw)
+
+    def forward(self, token_ids, seq_len=None) -> GpuTensor:
+        t, tp = _u32(token_ids)
+        n = t.size if seq_len is None else seq_len
+        h = C.c_void_p()
+        self.reg.check(self.reg.lib.b200nn_gpt2_forward(self.h, tp, n, C.byref(h)))
+        return GpuTensor(self.reg, h)
+
+    def forward_cached(self, token_ids, new_len, cache: KvCache) -> GpuTensor:
+        t, tp = _u32(token_ids)
+        h = C.c_void_p()
+        self.reg.check(self.reg.lib.b200nn_gpt2_forward_cached(self.h, tp, new_len, cache.h, C.byref(h)))
+        return GpuTensor(self.reg, h)
+
+    def _gen(self, fn, prompt, max_new, flags):
+        p, pp = _u32(prompt)
+        out = np.zeros(p.size + max_new, dtype=np.uint32)
+        n = C.c_size_t()
+        self.reg.check(fn(self.h, pp, p.size, max_new, self.flags | flags, out.ctypes.data_as(_u32p), C.byref(n)))
+        return out[: n.value]
+
+    def generate(self, prompt_tokens, max_new_tokens, flags: int = 8):
+        """Greedy; by default stops before appending token 50256 as the reference does."""
+        return self._gen(self.reg.lib.b200nn_gpt2_generate, prompt_tokens, max_new_tokens, flags)
+
+    def generate_cached(self, prompt_tokens, max_new_tokens, flags: int = 8):
+        return self._gen(self.reg.lib.b200nn_gpt2_generate_cached, prompt_tokens, max_new_tokens, flags)
+
+    def generate_batch(self, prompts, max_new_tokens, flags: int = 0):
+        """prompts [batch, prompt_len] -> (tokens [batch, prompt_len+max_new], lengths [batch])."""
+        p = np.ascontiguousarray(prompts, dtype=np.uint32)
+        batch, plen = p.shape
+        out = np.zeros((batch, plen + max_new_tokens), dtype=np.uint32)
+        lens = (C.c_size_t * batch)()
+        self.reg.check(self.reg.lib.b200nn_gpt2_generate_batch(
+            self.h, p.ctypes.data_as(_u32p), batch, plen, max_new_tokens, self.flags | flags,
+            out.ctypes.data_as(_u32p), lens))
+        return out, np.array(list(lens), dtype=np.int64)
+
+    def quantized_memory_bytes(self):
+        return int(self.reg.lib.b200nn_gpt2_quantized_memory_bytes(self.h))
+
+    def get_int4(self, layer: int, which: int):
+        """(packed [K/8,N], scales [ceil(K/g),N] fp16-rounded, K, N) the model holds for one Linear."""
+        k, n = C.c_size_t(), C.c_size_t()
+        self.reg.check(self.reg.lib.b200nn_gpt2_get_int4(self.h, layer, which, None, None, C.byref(k), C.byref(n)))
+        K, N, g = k.value, n.value, self._group_size
+        packed = np.zeros((K // 8, N), dtype=np.uint32)
+        scales = np.zeros(((K + g - 1) // g, N), dtype=np.float32)
+        self.reg.check(self.reg.lib.b200nn_gpt2_get_int4(self.h, layer, which, packed.ctypes.data_as(_u32p),
+                                                         scales.ctypes.data_as(_f32p), None, None))
+        return packed, scales, K, N
+
+    def __del__(self):
+        try:
+            if self.h and self.reg.h:
+                self.reg.lib.b200nn_gpt2_destroy(self.h)
+                self.h = None
+        except Exception:
+            pass
+
+
+class Int4Gpt2Model(Gpt2Model):
+    """``Int4Gpt2Model::from_weights(weights, config, group_size, &registry)`` (gpt2.rs:1356-1436)."""
+    _int4 = True
+    DEFAULT_GROUP_SIZE = 128
+
+    def group_size(self):
+        return self._group_size
+
+
+class DecodeSession:
+    """The batched greedy loop in pieces with all state on the device: prefill, then steps."""
+
+    def __init__(self, model: Gpt2Model, batch: int, capacity: int, flags: int = 0):
+        self.model, self.reg, self.batch, self.capacity = model, model.reg, batch, capacity
+        self.h = C.c_void_p()
+        self.reg.check(self.reg.lib.b200nn_session_create(model.h, batch, capacity, model.flags | flags, C.byref(self.h)))
+
+    def prefill(self, prompts):
+        p = np.ascontiguousarray(prompts, dtype=np.uint32)
+        assert p.shape[0] == self.batch
+        self.reg.check(self.reg.lib.b200nn_session_prefill(self.h, p.ctypes.data_as(_u32p), p.shape[1]))
+
+    def step(self, n_steps: int = 1):
+        self.reg.check(self.reg.lib.b200nn_session_step(self.h, n_steps))
+
+    def rewind(self, position: int):
+        """Timing aid: moves the position counter back; the cache keeps its contents."""
+        self.reg.check(self.reg.lib.b200nn_session_rewind(self.h, position))
+
+    def position(self):
+        return int(self.reg.lib.b200nn_session_position(self.h))
+
+    def tokens(self):
+        out = np.zeros((self.batch, self.capacity), dtype=np.uint32)
+        n = C.c_size_t()
+        self.reg.check(self.reg.lib.b200nn_session_tokens(self.h, out.ctypes.data_as(_u32p), self.capacity, C.byref(n)))
+        return out[:, : n.value]
+
+    def logits(self):
+        out = np.empty((self.batch, self.model.config.vocab_size), dtype=np.float32)
+        self.reg.check(self.reg.lib.b200nn_session_logits(self.h, out.ctypes.data_as(_f32p)))
+        return out
+
+    def profile_step(self):
+        t = (C.c_float * len(PROF_NAMES))()
+        b = C.c_uint64()
+        self.reg.check(self.reg.lib.b200nn_session_profile_step(self.h, t, C.byref(b)))
+        return {n: float(t[i]) for i, n in enumerate(PROF_NAMES)}, int(b.value)
+
+    def __del__(self):
+        try:
+            if self.h and self.model.h and self.reg.h:
+                self.reg.lib.b200nn_session_destroy(self.h)
+        except Exception:
+            pass

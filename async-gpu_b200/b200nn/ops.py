@@ -1,0 +1,116 @@
+"""Stateless ops, named as in ``gpu_host::nn::ops`` (ops/mod.rs:19-37)."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import (ACT_GELU_SIGMOID, ACT_GELU_TANH, ACT_RELU, ERR_SHAPE, GpuTensor, KernelRegistry, NnError, _f32,
+               _f32p, _out, _u32p, load_library)
+
+
+# ---- quantize (ops/quantize.rs) ----
+def quantize_weight_int4(weight_t, k, n, group_size):
+    """[K,N] f32 -> (packed [K/8,N] u32, scales [ceil(K/g),N] f32); raises ShapeMismatch if K%8 != 0."""
+    lib = load_library()
+    w, wp = _f32(weight_t)
+    if w.size != k * n:
+        raise NnError(ERR_SHAPE, "weight_t must be [K, N]")
+    packed = np.zeros((k // 8, n), dtype=np.uint32)
+    scales = np.zeros(((k + group_size - 1) // group_size, n), dtype=np.float32)
+    rc = lib.b200nn_quantize_weight_int4(wp, k, n, group_size, packed.ctypes.data_as(_u32p), scales.ctypes.data_as(_f32p))
+    if rc != 0:
+        raise NnError(rc, "K must be divisible by 8")
+    return packed, scales
+
+
+def quantize_int4_per_group(data, group_size):
+    lib = load_library()
+    d, dp = _f32(data)
+    packed = np.zeros(d.size // 8, dtype=np.uint32)
+    scales = np.zeros((d.size + group_size - 1) // group_size, dtype=np.float32)
+    rc = lib.b200nn_quantize_int4_per_group(dp, d.size, group_size, packed.ctypes.data_as(_u32p), scales.ctypes.data_as(_f32p))
+    if rc != 0:
+        raise NnError(rc, "length must be divisible by 8")
+    return packed, scales
+
+
+def unpack_int4(word, index):
+    return int(load_library().b200nn_unpack_int4(int(word), int(index)))
+
+
+def pack_int8_to_u32(values):
+    v = np.ascontiguousarray(values, dtype=np.int8)
+    out = np.zeros((v.size + 3) // 4, dtype=np.uint32)
+    load_library().b200nn_pack_int8_to_u32(v.ctypes.data_as(C.POINTER(C.c_int8)), v.size, out.ctypes.data_as(_u32p))
+    return out
+
+
+def quantize_int8_per_tensor(data):
+    d, dp = _f32(data)
+    q = np.zeros(d.size, dtype=np.int8)
+    s = C.c_float()
+    load_library().b200nn_quantize_int8_per_tensor(dp, d.size, q.ctypes.data_as(C.POINTER(C.c_int8)), C.byref(s))
+    return q, float(s.value)
+
+
+# ---- device ops ----
+def layer_norm(x: GpuTensor, gamma: GpuTensor, beta: GpuTensor, eps: float, reg: KernelRegistry):
+    h = C.c_void_p()
+    return _out(reg, reg.lib.b200nn_layer_norm(reg.h, x.h, gamma.h, beta.h, eps, C.byref(h)), h)
+
+
+def layer_norm_residual_dual(a, b, gamma, beta, eps, reg):
+    hs, hn = C.c_void_p(), C.c_void_p()
+    reg.check(reg.lib.b200nn_layer_norm_residual_dual(reg.h, a.h, b.h, gamma.h, beta.h, eps, C.byref(hs), C.byref(hn)))
+    return GpuTensor(reg, hs), GpuTensor(reg, hn)
+
+
+def _act(x, act, reg):
+    h = C.c_void_p()
+    return _out(reg, reg.lib.b200nn_activation(reg.h, x.h, act, C.byref(h)), h)
+
+
+def gelu(x, reg, sigmoid_form=False):
+    """tanh GELU by default; ``sigmoid_form`` selects x*sigmoid(1.702x) (the reference's v2 kernel)."""
+    return _act(x, ACT_GELU_SIGMOID if sigmoid_form else ACT_GELU_TANH, reg)
+
+
+def relu(x, reg):
+    return _act(x, ACT_RELU, reg)
+
+
+def bias_add(data, bias, reg):
+    reg.check(reg.lib.b200nn_bias_add(reg.h, data.h, bias.h))
+
+
+def elementwise_add(a, b, reg):
+    reg.check(reg.lib.b200nn_elementwise_add(reg.h, a.h, b.h))
+
+
+def split_qkv(qkv, seq_len, n_heads, d_head, reg):
+    q, k, v = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    reg.check(reg.lib.b200nn_split_qkv(reg.h, qkv.h, seq_len, n_heads, d_head, C.byref(q), C.byref(k), C.byref(v)))
+    return GpuTensor(reg, q), GpuTensor(reg, k), GpuTensor(reg, v)
+
+
+def concat_heads(heads, seq_len, n_heads, d_head, reg):
+    h = C.c_void_p()
+    return _out(reg, reg.lib.b200nn_concat_heads(reg.h, heads.h, seq_len, n_heads, d_head, C.byref(h)), h)
+
+
+def multi_head_flash_attention(q, k, v, seq_len, n_heads, d_head, causal, reg):
+    h = C.c_void_p()
+    return _out(reg, reg.lib.b200nn_multi_head_flash_attention(reg.h, q.h, k.h, v.h, seq_len, n_heads, d_head,
+                                                               int(causal), C.byref(h)), h)
+
+
+def scaled_dot_product_attention_kv(q, k, v, causal, q_offset, reg):
+    h = C.c_void_p()
+    return _out(reg, reg.lib.b200nn_attention_kv(reg.h, q.h, k.h, v.h, int(causal), q_offset, C.byref(h)), h)
+
+
+def int4_matmul(a: GpuTensor, b_host, k, n, group_size, reg):
+    b, bp = _f32(b_host)
+    h = C.c_void_p()
+    return _out(reg, reg.lib.b200nn_int4_matmul(reg.h, a.h, bp, k, n, group_size, C.byref(h)), h)

@@ -1,0 +1,177 @@
+// Internal declarations shared by the translation units of libb200nn.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "b200nn.h"
+
+// ---------------------------------------------------------------------------------------------
+// context
+// ---------------------------------------------------------------------------------------------
+struct b200nn_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    std::string last_error;
+    int last_cuda = 0;
+    int sm_count = 148;
+    int gemv_max_rows = 2;       // rows at or below this take the CUDA-core GEMV
+    uint64_t launches = 0;       // kernels launched by this library
+    uint32_t *dev_err = nullptr; // device error word (bounded waits report here)
+    // split-K / split-KV scratch, grown on demand outside stream capture
+    float *scratch = nullptr;
+    size_t scratch_bytes = 0;
+    unsigned *counters = nullptr; // arrival counters, self-resetting, zeroed at allocation
+    size_t n_counters = 0;
+    void *encode_tiled = nullptr; // cuTensorMapEncodeTiled, resolved through the runtime
+    bool capturing = false;       // true while a decode step is being captured into a graph
+};
+
+int set_error(b200nn_ctx *ctx, int code, const std::string &msg);
+int set_cuda_error(b200nn_ctx *ctx, cudaError_t e, const char *what);
+int ensure_scratch(b200nn_ctx *ctx, size_t bytes, size_t counters);
+
+#define CK(ctx, call)                                                     \
+    do {                                                                  \
+        cudaError_t _e = (call);                                          \
+        if (_e != cudaSuccess) return set_cuda_error((ctx), _e, #call);   \
+    } while (0)
+
+#define CK_LAUNCH(ctx, name)                                              \
+    do {                                                                  \
+        (ctx)->launches++;                                                \
+        cudaError_t _e = cudaPeekAtLastError();                           \
+        if (_e != cudaSuccess) return set_cuda_error((ctx), _e, name);    \
+    } while (0)
+
+#define TRY(expr)                       \
+    do {                                \
+        int _rc = (expr);               \
+        if (_rc != B200NN_OK) return _rc; \
+    } while (0)
+
+struct DevBuf {
+    void *p = nullptr;
+    size_t bytes = 0;
+    int device = 0;
+    ~DevBuf();
+};
+int dev_alloc(b200nn_ctx *ctx, size_t bytes, std::shared_ptr<DevBuf> *out);
+
+struct b200nn_tensor {
+    b200nn_ctx *ctx = nullptr;
+    std::shared_ptr<DevBuf> buf;
+    std::vector<size_t> shape;
+    size_t numel = 0;
+    float *data() const { return static_cast<float *>(buf->p); }
+};
+int tensor_alloc(b200nn_ctx *ctx, const std::vector<size_t> &shape, bool zero, b200nn_tensor **out);
+
+// ---------------------------------------------------------------------------------------------
+// weights in kernel layouts
+// ---------------------------------------------------------------------------------------------
+static constexpr int TILE_N = 128;   // output features per weight tile
+static constexpr int TILE_K = 64;    // reduction elements per weight tile
+static constexpr int TILE_BYTES = TILE_N * TILE_K / 2; // 4096
+
+// Int4 weight of a Linear y = x * dequant(W) (+bias); reference layout packed [K/8,N], scales
+// [ceil(K/g),N] (int4_linear.rs:18-33).  `tiled` is the layout the fast kernels stream:
+//   tile (nt, kb) at byte (nt*k_blocks + kb)*4096, holding rows n = nt*128 .. +127 and
+//   k = kb*64 .. +63 as [plane 2][row 128][16 bytes]; plane p of a row carries words j = 4p..4p+3,
+//   word j = k indices 8j..8j+7 of the block with nibble positions 0..7 holding
+//   k offsets 0,2,4,6,1,3,5,7 (so that (w & 0x000f000f) yields the half2 pair (k0,k1), etc.).
+//   Rows n >= N are stored as nibble 8 (value 0).
+// `scales_h` is [n_groups][n_pad] fp16.  Shapes that do not fit (K%64, group%64) keep the
+// reference layout in `ref_packed`/`ref_scales` and run on the one-thread-per-output kernel.
+struct Int4Weight {
+    int K = 0, N = 0, group = 0;
+    int n_tiles = 0, k_blocks = 0, n_pad = 0, n_groups = 0;
+    bool fast = false;
+    std::shared_ptr<DevBuf> tiled, scales_h, bias, ref_packed, ref_scales;
+    std::vector<uint32_t> host_packed; // reference-layout copies for read-back
+    std::vector<float> host_scales;    // fp16-rounded values
+    size_t memory_bytes() const { return host_packed.size() * 4 + host_scales.size() * 4; }
+};
+int int4_weight_upload(b200nn_ctx *ctx, const uint32_t *packed, const float *scales, const float *bias, size_t K,
+                       size_t N, size_t group, Int4Weight *out);
+
+// f32 weight of a Linear, stored [K,N] (= [in,out]) row-major on the device.
+struct F32Weight {
+    int K = 0, N = 0;
+    std::shared_ptr<DevBuf> w_kn, bias;
+};
+// weight given as [out,in] (Linear layout) or [in,out] (checkpoint layout)
+int f32_weight_upload(b200nn_ctx *ctx, const float *w, bool is_out_in, const float *bias, size_t K, size_t N,
+                      F32Weight *out);
+
+// ---------------------------------------------------------------------------------------------
+// epilogue shared by every Linear kernel
+// ---------------------------------------------------------------------------------------------
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_QKV = 2 };
+
+struct Epilogue {
+    int mode = EPI_STORE;
+    int act = B200NN_ACT_NONE;
+    int out_half = 0;          // out is __half* instead of float*
+    const float *bias = nullptr;
+    void *out = nullptr;       // [M, ldo]
+    int ldo = 0;
+    float *resid = nullptr;    // EPI_RESID: resid[m*ldo+n] += value (f32, in place)
+    // EPI_QKV: columns [0,d) -> out (q), [d,2d) -> K cache, [2d,3d) -> V cache
+    __half *kc = nullptr, *vc = nullptr; // this layer's cache, [seq][head][cap][64]
+    int d_model = 0, n_head = 0, rows_per_seq = 1, cap = 0;
+    const int *pos_ptr = nullptr; // optional device scalar added to pos_off
+    int pos_off = 0;
+};
+
+// ---------------------------------------------------------------------------------------------
+// kernel launchers (each in its own translation unit)
+// ---------------------------------------------------------------------------------------------
+// x: [M,K] f32 or fp16 (x_half).  Dispatches GEMV / tensor-core GEMM / generic kernel.
+int launch_int4_linear(b200nn_ctx *ctx, const Int4Weight &w, const void *x, bool x_half, int M, const Epilogue &epi);
+int launch_int4_gemv(b200nn_ctx *ctx, const Int4Weight &w, const void *x, bool x_half, int M, const Epilogue &epi);
+int launch_int4_naive(b200nn_ctx *ctx, const Int4Weight &w, const void *x, bool x_half, int M, const Epilogue &epi);
+bool int4_gemm_tc_supported(const Int4Weight &w, int M);
+int launch_int4_gemm_tc(b200nn_ctx *ctx, const Int4Weight &w, const __half *x, int M, const Epilogue &epi);
+int launch_f32_linear(b200nn_ctx *ctx, const F32Weight &w, const void *x, bool x_half, int M, const Epilogue &epi);
+
+int launch_layernorm(b200nn_ctx *ctx, const float *x, const float *res_in, float *sum_out, const float *gamma,
+                     const float *beta, float eps, int rows, int d, void *out, bool out_half);
+int launch_embedding(b200nn_ctx *ctx, const uint32_t *ids, const float *wte, const float *wpe, int n_rows, int d,
+                     int rows_per_seq, const int *pos_ptr, int pos_off, int vocab, int n_positions, float *out);
+int launch_activation(b200nn_ctx *ctx, const float *x, float *y, size_t n, int act);
+int launch_bias_add(b200nn_ctx *ctx, float *data, const float *bias, size_t total, int n_cols);
+int launch_add(b200nn_ctx *ctx, float *a, const float *b, size_t n);
+int launch_split_qkv(b200nn_ctx *ctx, const float *qkv, int seq, int H, int dh, float *q, float *k, float *v);
+int launch_concat_heads(b200nn_ctx *ctx, const float *heads, int seq, int H, int dh, float *out);
+int launch_f32_to_half(b200nn_ctx *ctx, const float *x, __half *y, size_t n);
+int launch_half_to_f32(b200nn_ctx *ctx, const __half *x, float *y, size_t n);
+// rows of `src` ([n_seq*rows_per_seq, d]) at index rows_per_seq-1 of each sequence -> dst [n_seq, d]
+int launch_gather_last_rows(b200nn_ctx *ctx, const float *src, int n_seq, int rows_per_seq, int d, float *dst);
+// logits [rows, ld] -> token per row; appends to history[row*hist_cap + *hist_len_ptr]; finished mask
+int launch_argmax(b200nn_ctx *ctx, const float *logits, int rows, int vocab, int ld, bool keep_last,
+                  uint32_t *tok_out);
+int launch_record_tokens(b200nn_ctx *ctx, const uint32_t *tok, int rows, uint32_t *history, int hist_cap,
+                         int *step_ptr, int *pos_ptr);
+
+// Decode attention: one query row per sequence against the fp16 cache (new position already
+// appended).  q [B, d] f32/half with leading dimension ldq; out [B, d] f32/half.
+int launch_decode_attention(b200nn_ctx *ctx, const void *q, bool q_half, int ldq, const __half *kc,
+                            const __half *vc, int B, int H, int cap, const int *pos_ptr, int pos_off, void *out,
+                            bool out_half, int max_ctx_hint);
+// Prefill attention: S query rows per sequence at absolute positions past..past+S-1, causal.
+int launch_prefill_attention(b200nn_ctx *ctx, const void *q, bool q_half, int ldq, const __half *kc,
+                             const __half *vc, int B, int H, int cap, int S, int past, void *out, bool out_half);
+// f32 [H,len,64] (public op layout) -> fp16 cache layout [1][H][cap][64]
+int launch_pack_kv(b200nn_ctx *ctx, const float *src, int H, int len, int cap, __half *dst);
+
+// host quantiser (quantize.cpp)
+int host_quantize_weight_int4(const float *weight_t, size_t k, size_t n, size_t group, uint32_t *packed,
+                              float *scales);
+float host_f16_round(float v);

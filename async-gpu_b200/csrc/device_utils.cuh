@@ -1,0 +1,104 @@
+// Device-side helpers shared by the kernels: activations, the Linear epilogue, reductions.
+#pragma once
+#include "common.h"
+
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+    // x*0.5*(1+tanh(sqrt(2/pi)*(x+0.044715x^3))): the GPT-2 form used by the reference's CPU model
+    // (crates/test/gpu-test-harness/src/tests_inference.rs:3680-3685).
+    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+    float inner = k0 * (x + k1 * x * x * x);
+    return 0.5f * x * (1.0f + tanhf(inner));
+}
+
+__device__ __forceinline__ float gelu_sigmoid_f(float x) {
+    // x*sigmoid(1.702x): crates/kernel/gpu-kernel-compute/src/compute_transformer.rs:1486-1504.
+    return x / (1.0f + __expf(-1.702f * x));
+}
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+    switch (act) {
+        case B200NN_ACT_GELU_TANH: return gelu_tanh_f(v);
+        case B200NN_ACT_GELU_SIGMOID: return gelu_sigmoid_f(v);
+        case B200NN_ACT_RELU: return fmaxf(v, 0.0f);
+        default: return v;
+    }
+}
+
+// Consumes one accumulated dot product for output row m (token) and column n (feature).
+__device__ __forceinline__ void epi_apply(const Epilogue &e, int m, int n, float acc) {
+    float v = acc + (e.bias ? e.bias[n] : 0.0f);
+    if (e.mode == EPI_RESID) {
+        size_t i = (size_t)m * e.ldo + n;
+        e.resid[i] += v;
+        return;
+    }
+    if (e.mode == EPI_QKV && n >= e.d_model) {
+        int c = n - e.d_model;
+        __half *cache = e.kc;
+        if (c >= e.d_model) {
+            c -= e.d_model;
+            cache = e.vc;
+        }
+        int head = c >> 6, el = c & 63;
+        int b = m / e.rows_per_seq, s = m - b * e.rows_per_seq;
+        int pos = (e.pos_ptr ? *e.pos_ptr : 0) + e.pos_off + s;
+        if (pos < e.cap) cache[(((size_t)b * e.n_head + head) * e.cap + pos) * 64 + el] = __float2half_rn(v);
+        return;
+    }
+    v = apply_act(v, e.act);
+    size_t i = (size_t)m * e.ldo + n;
+    if (e.out_half)
+        static_cast<__half *>(e.out)[i] = __float2half_rn(v);
+    else
+        static_cast<float *>(e.out)[i] = v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over the block; every thread gets the result.  red must hold 32 floats.
+__device__ __forceinline__ float block_sum(float v, float *red) {
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    float t = (lane < nw) ? red[lane] : 0.0f;
+    return warp_sum(t);
+}
+
+template <typename T>
+__device__ __forceinline__ float load_as_float(const T *p, size_t i);
+template <>
+__device__ __forceinline__ float load_as_float<float>(const float *p, size_t i) { return p[i]; }
+template <>
+__device__ __forceinline__ float load_as_float<__half>(const __half *p, size_t i) { return __half2float(p[i]); }
+
+// Unpacks one 32-bit word of the tiled int4 layout (nibble positions 0..7 = k offsets
+// 0,2,4,6,1,3,5,7, each stored +8) into four half2 holding the exact integers (k0,k1) (k2,k3)
+// (k4,k5) (k6,k7) in [-8,7].
+__device__ __forceinline__ void unpack8_int4(uint32_t w, __half2 (&q)[4]) {
+    const uint32_t MAGIC = 0x64006400u; // 1024.0 in both halves
+    uint32_t h0, h1, h2, h3;
+    asm("lop3.b32 %0, %1, 0x000f000f, %2, 0xea;" : "=r"(h0) : "r"(w), "r"(MAGIC));
+    asm("lop3.b32 %0, %1, 0x00f000f0, %2, 0xea;" : "=r"(h1) : "r"(w), "r"(MAGIC));
+    uint32_t w8 = w >> 8;
+    asm("lop3.b32 %0, %1, 0x000f000f, %2, 0xea;" : "=r"(h2) : "r"(w8), "r"(MAGIC));
+    asm("lop3.b32 %0, %1, 0x00f000f0, %2, 0xea;" : "=r"(h3) : "r"(w8), "r"(MAGIC));
+    const __half2 c1032 = __floats2half2_rn(1032.0f, 1032.0f);
+    const __half2 c16th = __floats2half2_rn(0.0625f, 0.0625f);
+    const __half2 cm72 = __floats2half2_rn(-72.0f, -72.0f);
+    q[0] = __hsub2(*reinterpret_cast<__half2 *>(&h0), c1032);       // (1024+n) - 1032
+    q[1] = __hfma2(*reinterpret_cast<__half2 *>(&h1), c16th, cm72); // (1024+16n)/16 - 72
+    q[2] = __hsub2(*reinterpret_cast<__half2 *>(&h2), c1032);
+    q[3] = __hfma2(*reinterpret_cast<__half2 *>(&h3), c16th, cm72);
+}

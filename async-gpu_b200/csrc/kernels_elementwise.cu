@@ -1,0 +1,312 @@
+// Small fused kernels of the GPT-2 path: LayerNorm (+residual), embedding gather, activations,
+// bias / residual adds, head split / concat, dtype conversion, greedy argmax.
+#include "device_utils.cuh"
+
+// ---------------------------------------------------------------------------------------------
+// LayerNorm: gamma*(x-mean)/sqrt(var+eps)+beta, biased variance (cpu_ref.rs:27-54).  One block per
+// row; the row lives in registers between the mean pass and the variance pass, so the input is
+// read once and the variance is the two-pass form (no E[x^2]-mean^2 cancellation).
+// Optional residual: s = x + res_in is normalised and also written to sum_out
+// (ops/norm.rs:248-400 `layer_norm_residual_dual`).
+// ---------------------------------------------------------------------------------------------
+template <int VPT, typename TOut>
+__global__ void __launch_bounds__(256) layernorm_kernel(const float *__restrict__ x, const float *__restrict__ res_in,
+                                                        float *__restrict__ sum_out, const float *__restrict__ gamma,
+                                                        const float *__restrict__ beta, float eps, int d,
+                                                        TOut *__restrict__ out) {
+    __shared__ float red[32];
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const float *xr = x + (size_t)row * d;
+    const float *rr = res_in ? res_in + (size_t)row * d : nullptr;
+    float v[VPT];
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        int j = tid + i * 256;
+        float t = 0.0f;
+        if (j < d) {
+            t = xr[j];
+            if (rr) t += rr[j];
+            if (sum_out) sum_out[(size_t)row * d + j] = t;
+        }
+        v[i] = t;
+        s += t;
+    }
+    float mean = block_sum(s, red) / (float)d;
+    float q = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        int j = tid + i * 256;
+        float t = (j < d) ? v[i] - mean : 0.0f;
+        q += t * t;
+    }
+    float var = block_sum(q, red) / (float)d;
+    float inv_std = rsqrtf(var + eps);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        int j = tid + i * 256;
+        if (j < d) {
+            float y = (v[i] - mean) * inv_std * gamma[j] + beta[j];
+            if constexpr (sizeof(TOut) == 2)
+                out[(size_t)row * d + j] = __float2half_rn(y);
+            else
+                out[(size_t)row * d + j] = y;
+        }
+    }
+}
+
+int launch_layernorm(b200nn_ctx *ctx, const float *x, const float *res_in, float *sum_out, const float *gamma,
+                     const float *beta, float eps, int rows, int d, void *out, bool out_half) {
+    if (rows <= 0) return B200NN_OK;
+    if (d > 256 * 32) return set_error(ctx, B200NN_ERR_UNSUPPORTED, "layer_norm: d > 8192");
+#define LN_LAUNCH(V)                                                                                              \
+    do {                                                                                                          \
+        if (out_half)                                                                                             \
+            layernorm_kernel<V, __half><<<rows, 256, 0, ctx->stream>>>(x, res_in, sum_out, gamma, beta, eps, d,   \
+                                                                      (__half *)out);                            \
+        else                                                                                                      \
+            layernorm_kernel<V, float><<<rows, 256, 0, ctx->stream>>>(x, res_in, sum_out, gamma, beta, eps, d,    \
+                                                                     (float *)out);                              \
+    } while (0)
+    int vpt = (d + 255) / 256;
+    if (vpt <= 4) LN_LAUNCH(4);
+    else if (vpt <= 8) LN_LAUNCH(8);
+    else if (vpt <= 16) LN_LAUNCH(16);
+    else LN_LAUNCH(32);
+#undef LN_LAUNCH
+    CK_LAUNCH(ctx, "layernorm_kernel");
+    return B200NN_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Embedding: out[r,:] = wte[ids[r],:] + wpe[pos(r),:], pos(r) = *pos_ptr + pos_off + r % rows_per_seq
+// (layers/embedding.rs:59-93 computes the offset form on the host; here it is one gather).
+// ---------------------------------------------------------------------------------------------
+__global__ void embedding_kernel(const uint32_t *__restrict__ ids, const float *__restrict__ wte,
+                                 const float *__restrict__ wpe, int d, int rows_per_seq, const int *pos_ptr,
+                                 int pos_off, int vocab, int n_positions, float *__restrict__ out) {
+    int r = blockIdx.x;
+    uint32_t tok = ids[r];
+    if (tok >= (uint32_t)vocab) tok = vocab - 1; // ids are validated on the host; never read out of range
+    int pos = (pos_ptr ? *pos_ptr : 0) + pos_off + r % rows_per_seq;
+    if (pos >= n_positions) pos = n_positions - 1;
+    const float *a = wte + (size_t)tok * d, *b = wpe + (size_t)pos * d;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) out[(size_t)r * d + j] = a[j] + b[j];
+}
+
+int launch_embedding(b200nn_ctx *ctx, const uint32_t *ids, const float *wte, const float *wpe, int n_rows, int d,
+                     int rows_per_seq, const int *pos_ptr, int pos_off, int vocab, int n_positions, float *out) {
+    if (n_rows <= 0) return B200NN_OK;
+    embedding_kernel<<<n_rows, 256, 0, ctx->stream>>>(ids, wte, wpe, d, rows_per_seq, pos_ptr, pos_off, vocab,
+                                                      n_positions, out);
+    CK_LAUNCH(ctx, "embedding_kernel");
+    return B200NN_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// element-wise ops (ops/activation.rs, ops/reshape.rs:112-186)
+// ---------------------------------------------------------------------------------------------
+__global__ void activation_kernel(const float *__restrict__ x, float *__restrict__ y, size_t n, int act) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += st) y[i] = apply_act(x[i], act);
+}
+__global__ void bias_add_kernel(float *__restrict__ data, const float *__restrict__ bias, size_t total, int n_cols) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += st) data[i] += bias[i % n_cols];
+}
+__global__ void add_kernel(float *__restrict__ a, const float *__restrict__ b, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += st) a[i] += b[i];
+}
+__global__ void f32_to_half_kernel(const float *__restrict__ x, __half *__restrict__ y, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += st) y[i] = __float2half_rn(x[i]);
+}
+__global__ void half_to_f32_kernel(const __half *__restrict__ x, float *__restrict__ y, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += st) y[i] = __half2float(x[i]);
+}
+
+static inline int grid_for(b200nn_ctx *ctx, size_t n, int block) {
+    size_t g = (n + block - 1) / block;
+    size_t cap = (size_t)ctx->sm_count * 16;
+    return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+int launch_activation(b200nn_ctx *ctx, const float *x, float *y, size_t n, int act) {
+    if (!n) return B200NN_OK;
+    activation_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(x, y, n, act);
+    CK_LAUNCH(ctx, "activation_kernel");
+    return B200NN_OK;
+}
+int launch_bias_add(b200nn_ctx *ctx, float *data, const float *bias, size_t total, int n_cols) {
+    if (!total) return B200NN_OK;
+    bias_add_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(data, bias, total, n_cols);
+    CK_LAUNCH(ctx, "bias_add_kernel");
+    return B200NN_OK;
+}
+int launch_add(b200nn_ctx *ctx, float *a, const float *b, size_t n) {
+    if (!n) return B200NN_OK;
+    add_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(a, b, n);
+    CK_LAUNCH(ctx, "add_kernel");
+    return B200NN_OK;
+}
+int launch_f32_to_half(b200nn_ctx *ctx, const float *x, __half *y, size_t n) {
+    if (!n) return B200NN_OK;
+    f32_to_half_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(x, y, n);
+    CK_LAUNCH(ctx, "f32_to_half_kernel");
+    return B200NN_OK;
+}
+int launch_half_to_f32(b200nn_ctx *ctx, const __half *x, float *y, size_t n) {
+    if (!n) return B200NN_OK;
+    half_to_f32_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(x, y, n);
+    CK_LAUNCH(ctx, "half_to_f32_kernel");
+    return B200NN_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// split_qkv / concat_heads (ops/attention.rs:105-142, 515-549): [seq,3d] <-> Q,K,V [H,seq,dh]
+// with Q columns [0,d), K [d,2d), V [2d,3d), head h at h*dh.
+// ---------------------------------------------------------------------------------------------
+__global__ void split_qkv_kernel(const float *__restrict__ qkv, int seq, int H, int dh, float *__restrict__ q,
+                                 float *__restrict__ k, float *__restrict__ v) {
+    size_t total = (size_t)H * seq * dh;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+    int d = H * dh;
+    for (; i < total; i += st) {
+        int e = i % dh;
+        int s = (i / dh) % seq;
+        int h = i / ((size_t)dh * seq);
+        const float *row = qkv + (size_t)s * 3 * d + h * dh + e;
+        q[i] = row[0];
+        k[i] = row[d];
+        v[i] = row[2 * d];
+    }
+}
+__global__ void concat_heads_kernel(const float *__restrict__ heads, int seq, int H, int dh, float *__restrict__ out) {
+    size_t total = (size_t)H * seq * dh;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += st) {
+        int e = i % dh;
+        int h = (i / dh) % H;
+        int s = i / ((size_t)dh * H);
+        out[i] = heads[((size_t)h * seq + s) * dh + e];
+    }
+}
+int launch_split_qkv(b200nn_ctx *ctx, const float *qkv, int seq, int H, int dh, float *q, float *k, float *v) {
+    size_t n = (size_t)seq * H * dh;
+    if (!n) return B200NN_OK;
+    split_qkv_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(qkv, seq, H, dh, q, k, v);
+    CK_LAUNCH(ctx, "split_qkv_kernel");
+    return B200NN_OK;
+}
+int launch_concat_heads(b200nn_ctx *ctx, const float *heads, int seq, int H, int dh, float *out) {
+    size_t n = (size_t)seq * H * dh;
+    if (!n) return B200NN_OK;
+    concat_heads_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(heads, seq, H, dh, out);
+    CK_LAUNCH(ctx, "concat_heads_kernel");
+    return B200NN_OK;
+}
+
+__global__ void gather_last_rows_kernel(const float *__restrict__ src, int rows_per_seq, int d, float *__restrict__ dst) {
+    int b = blockIdx.x;
+    const float *s = src + ((size_t)b * rows_per_seq + rows_per_seq - 1) * d;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) dst[(size_t)b * d + j] = s[j];
+}
+int launch_gather_last_rows(b200nn_ctx *ctx, const float *src, int n_seq, int rows_per_seq, int d, float *dst) {
+    if (n_seq <= 0) return B200NN_OK;
+    gather_last_rows_kernel<<<n_seq, 256, 0, ctx->stream>>>(src, rows_per_seq, d, dst);
+    CK_LAUNCH(ctx, "gather_last_rows_kernel");
+    return B200NN_OK;
+}
+
+// f32 [H,len,64] -> fp16 [H,cap,64]
+__global__ void pack_kv_kernel(const float *__restrict__ src, int len, int cap, size_t total, __half *__restrict__ dst) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += st) {
+        int e = i & 63;
+        size_t r = i >> 6;
+        int s = r % len;
+        int h = r / len;
+        dst[((size_t)h * cap + s) * 64 + e] = __float2half_rn(src[i]);
+    }
+}
+int launch_pack_kv(b200nn_ctx *ctx, const float *src, int H, int len, int cap, __half *dst) {
+    size_t n = (size_t)H * len * 64;
+    if (!n) return B200NN_OK;
+    pack_kv_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(src, len, cap, n, dst);
+    CK_LAUNCH(ctx, "pack_kv_kernel");
+    return B200NN_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Greedy argmax over logits [rows, ld] restricted to [0, vocab).  keep_last=false keeps the first
+// maximum (the CPU f64 reference, tests_inference.rs:4504-4515); keep_last=true keeps the last
+// (Rust max_by, models/gpt2.rs:991-997).
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ logits, int vocab, int ld,
+                                                      int keep_last, uint32_t *__restrict__ tok_out) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const float *row = logits + (size_t)blockIdx.x * ld;
+    float best = -INFINITY;
+    int bi = keep_last ? -1 : 0x7fffffff;
+    for (int j = threadIdx.x; j < vocab; j += blockDim.x) {
+        float v = row[j];
+        if (v > best || (v == best && (keep_last ? j > bi : j < bi))) {
+            best = v;
+            bi = j;
+        }
+    }
+    auto better = [&](float v, int i, float bv, int bidx) {
+        return v > bv || (v == bv && (keep_last ? i > bidx : i < bidx));
+    };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, best, bi)) { best = ov; bi = oi; }
+    }
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    if (lane == 0) { sv[w] = best; si[w] = bi; }
+    __syncthreads();
+    if (w == 0) {
+        int nw = blockDim.x >> 5;
+        best = lane < nw ? sv[lane] : -INFINITY;
+        bi = lane < nw ? si[lane] : (keep_last ? -1 : 0x7fffffff);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better(ov, oi, best, bi)) { best = ov; bi = oi; }
+        }
+        if (lane == 0) tok_out[blockIdx.x] = (bi < 0 || bi >= vocab) ? 0u : (uint32_t)bi;
+    }
+}
+int launch_argmax(b200nn_ctx *ctx, const float *logits, int rows, int vocab, int ld, bool keep_last,
+                  uint32_t *tok_out) {
+    if (rows <= 0) return B200NN_OK;
+    argmax_kernel<<<rows, 1024, 0, ctx->stream>>>(logits, vocab, ld, keep_last ? 1 : 0, tok_out);
+    CK_LAUNCH(ctx, "argmax_kernel");
+    return B200NN_OK;
+}
+
+// Appends this step's token of every sequence to the history and advances the step / position
+// counters that the next step's kernels read (single block, so the increment is ordered).
+__global__ void record_tokens_kernel(const uint32_t *__restrict__ tok, int rows, uint32_t *__restrict__ history,
+                                     int hist_cap, int *step_ptr, int *pos_ptr) {
+    int step = *step_ptr;
+    for (int r = threadIdx.x; r < rows; r += blockDim.x)
+        if (step < hist_cap) history[(size_t)r * hist_cap + step] = tok[r];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        *step_ptr = step + 1;
+        if (pos_ptr) *pos_ptr += 1;
+    }
+}
+int launch_record_tokens(b200nn_ctx *ctx, const uint32_t *tok, int rows, uint32_t *history, int hist_cap,
+                         int *step_ptr, int *pos_ptr) {
+    record_tokens_kernel<<<1, 256, 0, ctx->stream>>>(tok, rows, history, hist_cap, step_ptr, pos_ptr);
+    CK_LAUNCH(ctx, "record_tokens_kernel");
+    return B200NN_OK;
+}

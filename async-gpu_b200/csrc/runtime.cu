@@ -1,0 +1,228 @@
+// Context, device buffers, tensors, host-side quantiser and the upload / re-tiling of weights.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <thread>
+
+#include "common.h"
+
+// ---------------------------------------------------------------------------------------------
+// errors
+// ---------------------------------------------------------------------------------------------
+int set_error(b200nn_ctx *ctx, int code, const std::string &msg) {
+    if (ctx) ctx->last_error = msg;
+    return code;
+}
+
+int set_cuda_error(b200nn_ctx *ctx, cudaError_t e, const char *what) {
+    if (ctx) {
+        ctx->last_cuda = (int)e;
+        ctx->last_error = std::string("CUDA error ") + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ") at " + what;
+    }
+    return B200NN_ERR_CUDA;
+}
+
+DevBuf::~DevBuf() {
+    if (p) {
+        int cur = -1;
+        cudaGetDevice(&cur);
+        if (cur != device) cudaSetDevice(device);
+        cudaFree(p);
+        if (cur >= 0 && cur != device) cudaSetDevice(cur);
+    }
+}
+
+int dev_alloc(b200nn_ctx *ctx, size_t bytes, std::shared_ptr<DevBuf> *out) {
+    auto b = std::make_shared<DevBuf>();
+    b->device = ctx->device;
+    b->bytes = bytes;
+    CK(ctx, cudaSetDevice(ctx->device));
+    CK(ctx, cudaMalloc(&b->p, bytes ? bytes : 16));
+    *out = b;
+    return B200NN_OK;
+}
+
+int tensor_alloc(b200nn_ctx *ctx, const std::vector<size_t> &shape, bool zero, b200nn_tensor **out) {
+    size_t n = 1;
+    for (size_t s : shape) n *= s;
+    auto *t = new b200nn_tensor();
+    t->ctx = ctx;
+    t->shape = shape;
+    t->numel = n;
+    int rc = dev_alloc(ctx, n * sizeof(float), &t->buf);
+    if (rc != B200NN_OK) {
+        delete t;
+        return rc;
+    }
+    if (zero && n) {
+        cudaError_t e = cudaMemsetAsync(t->buf->p, 0, n * sizeof(float), ctx->stream);
+        if (e != cudaSuccess) {
+            delete t;
+            return set_cuda_error(ctx, e, "cudaMemsetAsync");
+        }
+    }
+    *out = t;
+    return B200NN_OK;
+}
+
+// Split-K / split-KV scratch.  Grown only outside graph capture; a captured step must have been
+// run once eagerly (which sizes the scratch) before it is captured.
+int ensure_scratch(b200nn_ctx *ctx, size_t bytes, size_t counters) {
+    if (bytes > ctx->scratch_bytes) {
+        if (ctx->capturing) return set_error(ctx, B200NN_ERR_UNSUPPORTED, "scratch would grow during graph capture");
+        CK(ctx, cudaStreamSynchronize(ctx->stream));
+        if (ctx->scratch) CK(ctx, cudaFree(ctx->scratch));
+        ctx->scratch = nullptr;
+        size_t nb = std::max(bytes, (size_t)8 << 20);
+        CK(ctx, cudaMalloc(&ctx->scratch, nb));
+        ctx->scratch_bytes = nb;
+    }
+    if (counters > ctx->n_counters) {
+        if (ctx->capturing) return set_error(ctx, B200NN_ERR_UNSUPPORTED, "counters would grow during graph capture");
+        CK(ctx, cudaStreamSynchronize(ctx->stream));
+        if (ctx->counters) CK(ctx, cudaFree(ctx->counters));
+        ctx->counters = nullptr;
+        size_t nc = std::max(counters, (size_t)65536);
+        CK(ctx, cudaMalloc(&ctx->counters, nc * sizeof(unsigned)));
+        CK(ctx, cudaMemset(ctx->counters, 0, nc * sizeof(unsigned)));
+        ctx->n_counters = nc;
+    }
+    return B200NN_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// host quantiser: crates/core/gpu-host/src/nn/ops/quantize.rs
+// ---------------------------------------------------------------------------------------------
+float host_f16_round(float v) { return __half2float(__float2half_rn(v)); }
+
+template <typename F>
+static void parallel_for(size_t n, F f) {
+    unsigned hw = std::thread::hardware_concurrency();
+    size_t nt = std::min<size_t>(hw ? hw : 4, 64);
+    if (n < 256 || nt <= 1) {
+        f(0, n);
+        return;
+    }
+    std::vector<std::thread> th;
+    size_t per = (n + nt - 1) / nt;
+    for (size_t t = 0; t < nt; ++t) {
+        size_t a = t * per, b = std::min(n, a + per);
+        if (a >= b) break;
+        th.emplace_back([=] { f(a, b); });
+    }
+    for (auto &t : th) t.join();
+}
+
+static inline uint32_t quant_nibble(float v, float inv_scale) {
+    // quantize.rs:144-145: round half away from zero (Rust f32::round), clamp to [-8,7], store +8.
+    int q = (int)std::round(v * inv_scale);
+    q = std::max(-8, std::min(7, q));
+    return (uint32_t)(q + 8) & 0xFu;
+}
+
+// quantize.rs:102-153.
+int host_quantize_weight_int4(const float *weight_t, size_t k, size_t n, size_t group, uint32_t *packed,
+                              float *scales) {
+    if (k % 8 != 0 || group == 0) return B200NN_ERR_SHAPE;
+    size_t k_packed = k / 8, n_groups = (k + group - 1) / group;
+    parallel_for(n, [=](size_t c0, size_t c1) {
+        for (size_t col = c0; col < c1; ++col) {
+            for (size_t g = 0; g < n_groups; ++g) {
+                size_t s = g * group, e = std::min(k, s + group);
+                float max_abs = 0.0f;
+                for (size_t ki = s; ki < e; ++ki) max_abs = std::max(max_abs, std::fabs(weight_t[ki * n + col]));
+                scales[g * n + col] = (max_abs < 1e-12f) ? 1.0f : max_abs / 7.0f;
+            }
+            for (size_t kp = 0; kp < k_packed; ++kp) {
+                uint32_t word = 0;
+                for (unsigned bit = 0; bit < 8; ++bit) {
+                    size_t ki = kp * 8 + bit;
+                    float inv = 1.0f / scales[(ki / group) * n + col];
+                    word |= quant_nibble(weight_t[ki * n + col], inv) << (bit * 4);
+                }
+                packed[kp * n + col] = word;
+            }
+        }
+    });
+    return B200NN_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// weight upload
+// ---------------------------------------------------------------------------------------------
+static int upload(b200nn_ctx *ctx, const void *host, size_t bytes, std::shared_ptr<DevBuf> *out) {
+    TRY(dev_alloc(ctx, bytes, out));
+    if (bytes) CK(ctx, cudaMemcpy((*out)->p, host, bytes, cudaMemcpyHostToDevice));
+    return B200NN_OK;
+}
+
+int int4_weight_upload(b200nn_ctx *ctx, const uint32_t *packed, const float *scales, const float *bias, size_t K,
+                       size_t N, size_t group, Int4Weight *w) {
+    if (K == 0 || N == 0 || K % 8 != 0 || group == 0)
+        return set_error(ctx, B200NN_ERR_SHAPE, "Int4Linear: K must be a positive multiple of 8 and group > 0");
+    w->K = (int)K;
+    w->N = (int)N;
+    w->group = (int)group;
+    w->n_groups = (int)((K + group - 1) / group);
+    w->n_tiles = (int)((N + TILE_N - 1) / TILE_N);
+    w->n_pad = w->n_tiles * TILE_N;
+    w->k_blocks = (int)(K / TILE_K);
+    w->fast = (K % TILE_K == 0) && (group % TILE_K == 0);
+    w->host_packed.assign(packed, packed + (K / 8) * N);
+    w->host_scales.resize((size_t)w->n_groups * N);
+    for (size_t i = 0; i < w->host_scales.size(); ++i) w->host_scales[i] = host_f16_round(scales[i]);
+    if (bias) TRY(upload(ctx, bias, N * sizeof(float), &w->bias));
+    if (!w->fast) {
+        TRY(upload(ctx, w->host_packed.data(), w->host_packed.size() * 4, &w->ref_packed));
+        TRY(upload(ctx, w->host_scales.data(), w->host_scales.size() * 4, &w->ref_scales));
+        return B200NN_OK;
+    }
+    // re-tile: see the layout comment on Int4Weight
+    size_t tile_bytes = (size_t)w->n_tiles * w->k_blocks * TILE_BYTES;
+    std::vector<uint32_t> tiled(tile_bytes / 4);
+    const int k_blocks = w->k_blocks;
+    const uint32_t *hp = w->host_packed.data();
+    uint32_t *tp = tiled.data();
+    parallel_for((size_t)w->n_tiles, [=](size_t t0, size_t t1) {
+        for (size_t nt = t0; nt < t1; ++nt)
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                uint32_t *tile = tp + (nt * k_blocks + kb) * (TILE_BYTES / 4);
+                for (int r = 0; r < TILE_N; ++r) {
+                    size_t n = nt * TILE_N + r;
+                    for (int j = 0; j < 8; ++j) {
+                        uint32_t ref = (n < N) ? hp[((size_t)kb * 8 + j) * N + n] : 0x88888888u;
+                        uint32_t o = 0;
+                        static const int src[8] = {0, 2, 4, 6, 1, 3, 5, 7};
+                        for (int i = 0; i < 8; ++i) o |= ((ref >> (4 * src[i])) & 0xFu) << (4 * i);
+                        tile[(j >> 2) * 512 + r * 4 + (j & 3)] = o;
+                    }
+                }
+            }
+    });
+    std::vector<__half> sh((size_t)w->n_groups * w->n_pad, __float2half_rn(0.0f));
+    for (int g = 0; g < w->n_groups; ++g)
+        for (size_t n = 0; n < N; ++n) sh[(size_t)g * w->n_pad + n] = __float2half_rn(w->host_scales[(size_t)g * N + n]);
+    TRY(upload(ctx, tiled.data(), tile_bytes, &w->tiled));
+    TRY(upload(ctx, sh.data(), sh.size() * sizeof(__half), &w->scales_h));
+    return B200NN_OK;
+}
+
+int f32_weight_upload(b200nn_ctx *ctx, const float *wsrc, bool is_out_in, const float *bias, size_t K, size_t N,
+                      F32Weight *w) {
+    if (K == 0 || N == 0) return set_error(ctx, B200NN_ERR_SHAPE, "Linear: empty weight");
+    w->K = (int)K;
+    w->N = (int)N;
+    if (is_out_in) { // [N,K] -> [K,N]
+        std::vector<float> t(K * N);
+        float *tp = t.data();
+        parallel_for(N, [=](size_t n0, size_t n1) {
+            for (size_t n = n0; n < n1; ++n)
+                for (size_t k = 0; k < K; ++k) tp[k * N + n] = wsrc[n * K + k];
+        });
+        TRY(upload(ctx, t.data(), K * N * sizeof(float), &w->w_kn));
+    } else {
+        TRY(upload(ctx, wsrc, K * N * sizeof(float), &w->w_kn));
+    }
+    if (bias) TRY(upload(ctx, bias, N * sizeof(float), &w->bias));
+    return B200NN_OK;
+}

@@ -1,0 +1,293 @@
+/*
+ * b200nn — C ABI of the B200-native GPT-2 inference path that stands in for
+ * async-gpu's `gpu_host::nn` module (Linear / Int4Linear / LayerNorm / causal
+ * attention with KV cache / GELU MLP / Gpt2Model forward + generate).
+ *
+ * The reference has no FFI for this path: its boundary is the Rust `nn` API,
+ * which reaches kernels by name through `KernelRegistry` and launches them with
+ * cudarc.  Each entry point below names the Rust item it replaces
+ * (file:line relative to the reference repository; GH = crates/core/gpu-host/src).
+ * A Rust `-sys` crate binds these symbols one to one.
+ *
+ * Conventions
+ *   - Plain pointers and sizes only.  "host" pointers are ordinary host memory,
+ *     "dev" pointers are CUDA device memory of the context's device.
+ *   - Every function that can fail returns an int32 status (B200NN_*); the text
+ *     of the last failure is kept per context (b200nn_last_error_message).
+ *   - All tensors a caller can see are f32, row-major, contiguous, as in the
+ *     reference (GH/nn/tensor.rs:45-60).  fp16 / int4 exist only inside the library.
+ *   - One context per GPU, used from one host thread at a time; work is ordered on
+ *     the context's stream.  Functions returning host data synchronise that stream.
+ *   - There is no CPU fallback: without a CUDA device every compute entry point
+ *     fails with B200NN_ERR_CUDA.
+ */
+#ifndef B200NN_H
+#define B200NN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define B200NN_API __attribute__((visibility("default")))
+#else
+#define B200NN_API
+#endif
+
+/* Status codes; 1-4 mirror NnError's variants (GH/nn/error.rs:7-29). */
+enum {
+    B200NN_OK = 0,
+    B200NN_ERR_SHAPE = 1,       /* NnError::ShapeMismatch                      */
+    B200NN_ERR_DIM = 2,         /* NnError::DimOutOfRange                      */
+    B200NN_ERR_UNSUPPORTED = 3, /* NnError::KernelNotFound / unsupported shape */
+    B200NN_ERR_CUDA = 4,        /* NnError::Cuda                               */
+    B200NN_ERR_DEVICE = 5,      /* a kernel's bounded wait ran out             */
+    B200NN_ERR_ARG = 6          /* null handle / invalid argument              */
+};
+
+/* Activation selector (GH/nn/layers/linear.rs:24-33 `Activation`). */
+enum { B200NN_ACT_NONE = 0, B200NN_ACT_GELU_TANH = 1, B200NN_ACT_GELU_SIGMOID = 2, B200NN_ACT_RELU = 3 };
+
+/* Model / generation flags. */
+enum {
+    B200NN_GELU_SIGMOID = 1u << 0,   /* x*sigmoid(1.702x) (compute_transformer.rs:1473) instead of tanh */
+    B200NN_QUANT_LM_HEAD = 1u << 1,  /* int4 models: quantise the tied LM head as well               */
+    B200NN_ARGMAX_LAST = 1u << 2,    /* keep the last maximum on ties (GH/nn/models/gpt2.rs:991-997)  */
+    B200NN_STOP_ON_EOS = 1u << 3     /* stop before appending token 50256 (gpt2.rs:698-700)          */
+};
+
+typedef struct b200nn_ctx b200nn_ctx;
+typedef struct b200nn_tensor b200nn_tensor;
+typedef struct b200nn_linear b200nn_linear;
+typedef struct b200nn_int4_linear b200nn_int4_linear;
+typedef struct b200nn_layernorm b200nn_layernorm;
+typedef struct b200nn_embedding b200nn_embedding;
+typedef struct b200nn_attention b200nn_attention;
+typedef struct b200nn_gpt2 b200nn_gpt2;
+typedef struct b200nn_kvcache b200nn_kvcache;
+typedef struct b200nn_session b200nn_session;
+
+/* ---- context: KernelRegistry::init_default (GH/nn/registry.rs:131-135) --------------------- */
+B200NN_API const char *b200nn_version(void);
+B200NN_API int32_t b200nn_ctx_create(int32_t device_ordinal, b200nn_ctx **out);
+B200NN_API void b200nn_ctx_destroy(b200nn_ctx *ctx);
+B200NN_API int32_t b200nn_ctx_synchronize(b200nn_ctx *ctx);
+/* cudaStream_t of the context, for callers that record their own events on it. */
+B200NN_API void *b200nn_ctx_stream(b200nn_ctx *ctx);
+B200NN_API const char *b200nn_last_error_message(b200nn_ctx *ctx);
+B200NN_API int32_t b200nn_last_cuda_error(b200nn_ctx *ctx);
+/* Reads and clears the device-side error word (non-zero after a bounded wait gave up). */
+B200NN_API int32_t b200nn_ctx_device_error(b200nn_ctx *ctx, uint32_t *word_out);
+/* Number of kernels this library has launched on the context since creation. */
+B200NN_API uint64_t b200nn_ctx_launch_count(b200nn_ctx *ctx);
+/* Linear layers with at most this many input rows take the CUDA-core GEMV; more rows take the
+ * tcgen05 GEMM.  Negative restores the default. */
+B200NN_API int32_t b200nn_ctx_set_gemv_max_rows(b200nn_ctx *ctx, int32_t rows);
+
+/* ---- GpuTensor (GH/nn/tensor.rs:45-110, 201-221, 270) -------------------------------------- */
+B200NN_API int32_t b200nn_tensor_from_host(b200nn_ctx *ctx, const float *host, const size_t *shape, int32_t ndim,
+                                           b200nn_tensor **out);
+B200NN_API int32_t b200nn_tensor_zeros(b200nn_ctx *ctx, const size_t *shape, int32_t ndim, b200nn_tensor **out);
+B200NN_API int32_t b200nn_tensor_to_host(const b200nn_tensor *t, float *host, size_t capacity_elems);
+B200NN_API int32_t b200nn_tensor_ndim(const b200nn_tensor *t);
+B200NN_API size_t b200nn_tensor_numel(const b200nn_tensor *t);
+B200NN_API int32_t b200nn_tensor_shape(const b200nn_tensor *t, size_t *shape_out, int32_t capacity);
+B200NN_API int32_t b200nn_tensor_reshape(const b200nn_tensor *t, const size_t *shape, int32_t ndim, b200nn_tensor **out);
+B200NN_API int32_t b200nn_tensor_clone(const b200nn_tensor *t, b200nn_tensor **out);
+B200NN_API float *b200nn_tensor_data(b200nn_tensor *t); /* device pointer */
+B200NN_API void b200nn_tensor_destroy(b200nn_tensor *t);
+
+/* ---- host quantiser (GH/nn/ops/quantize.rs:56-162) ----------------------------------------- */
+/* weight_t [K,N] row-major -> packed [K/8,N] u32 (nibble i of a word = k index 8*kp+i, value+8),
+ * scales [ceil(K/group),N] f32.  K%8 != 0 returns B200NN_ERR_SHAPE (the reference asserts). */
+B200NN_API int32_t b200nn_quantize_weight_int4(const float *weight_t, size_t k, size_t n, size_t group,
+                                               uint32_t *packed, float *scales);
+B200NN_API int32_t b200nn_quantize_int4_per_group(const float *data, size_t len, size_t group, uint32_t *packed,
+                                                  float *scales);
+B200NN_API int32_t b200nn_unpack_int4(uint32_t packed, int32_t index);
+B200NN_API int32_t b200nn_pack_int8_to_u32(const int8_t *values, size_t n, uint32_t *packed);
+B200NN_API int32_t b200nn_quantize_int8_per_tensor(const float *data, size_t n, int8_t *q, float *scale);
+
+/* ---- stateless ops (GH/nn/ops/mod.rs:19-37) ------------------------------------------------- */
+/* ops::layer_norm (ops/norm.rs:14-81). gamma/beta: tensors of [d]. */
+B200NN_API int32_t b200nn_layer_norm(b200nn_ctx *ctx, const b200nn_tensor *x, const b200nn_tensor *gamma,
+                                     const b200nn_tensor *beta, float eps, b200nn_tensor **out);
+/* ops::layer_norm_residual_dual (ops/norm.rs:248-400): sum=a+b, norm=LN(sum); both returned. */
+B200NN_API int32_t b200nn_layer_norm_residual_dual(b200nn_ctx *ctx, const b200nn_tensor *a, const b200nn_tensor *b,
+                                                   const b200nn_tensor *gamma, const b200nn_tensor *beta, float eps,
+                                                   b200nn_tensor **sum_out, b200nn_tensor **norm_out);
+/* ops::gelu (ops/activation.rs:14-16) and the other Activation kinds; `act` is B200NN_ACT_*. */
+B200NN_API int32_t b200nn_activation(b200nn_ctx *ctx, const b200nn_tensor *x, int32_t act, b200nn_tensor **out);
+/* ops::bias_add (ops/reshape.rs:112-156): data[i] += bias[i % n_cols], in place. */
+B200NN_API int32_t b200nn_bias_add(b200nn_ctx *ctx, b200nn_tensor *data, const b200nn_tensor *bias);
+/* ops::elementwise_add (ops/reshape.rs:166-186): a += b, in place. */
+B200NN_API int32_t b200nn_elementwise_add(b200nn_ctx *ctx, b200nn_tensor *a, const b200nn_tensor *b);
+/* ops::split_qkv / ops::concat_heads (ops/attention.rs:105-142, 515-549). */
+B200NN_API int32_t b200nn_split_qkv(b200nn_ctx *ctx, const b200nn_tensor *qkv, size_t seq_len, size_t n_heads,
+                                    size_t d_head, b200nn_tensor **q, b200nn_tensor **k, b200nn_tensor **v);
+B200NN_API int32_t b200nn_concat_heads(b200nn_ctx *ctx, const b200nn_tensor *heads, size_t seq_len, size_t n_heads,
+                                       size_t d_head, b200nn_tensor **out);
+/* ops::multi_head_flash_attention (ops/attention.rs:151-202): q,k,v [H,seq,64] -> [H,seq,64]. */
+B200NN_API int32_t b200nn_multi_head_flash_attention(b200nn_ctx *ctx, const b200nn_tensor *q, const b200nn_tensor *k,
+                                                     const b200nn_tensor *v, size_t seq_len, size_t n_heads,
+                                                     size_t d_head, int32_t causal, b200nn_tensor **out);
+/* ops::scaled_dot_product_attention_kv (ops/attention.rs:557-606): one head, q [q_len,64] against
+ * k,v [kv_len,64], causal with q_offset. */
+B200NN_API int32_t b200nn_attention_kv(b200nn_ctx *ctx, const b200nn_tensor *q, const b200nn_tensor *k,
+                                       const b200nn_tensor *v, int32_t causal, size_t q_offset, b200nn_tensor **out);
+/* ops::int4_matmul (ops/gemm.rs:1186-1266): quantise B [K,N] on the host, then A[M,K] x dequant(B). */
+B200NN_API int32_t b200nn_int4_matmul(b200nn_ctx *ctx, const b200nn_tensor *a, const float *b_host, size_t k, size_t n,
+                                      size_t group, b200nn_tensor **out);
+
+/* ---- Linear (GH/nn/layers/linear.rs:58-88, 131-166, 283-313) -------------------------------- */
+/* weight [out,in] row-major host f32, bias [out] or NULL. */
+B200NN_API int32_t b200nn_linear_create(b200nn_ctx *ctx, const float *weight, const float *bias, size_t in_features,
+                                        size_t out_features, b200nn_linear **out);
+B200NN_API int32_t b200nn_linear_forward(b200nn_linear *l, const b200nn_tensor *x, b200nn_tensor **y);
+B200NN_API int32_t b200nn_linear_forward_fused(b200nn_linear *l, const b200nn_tensor *x, int32_t act, b200nn_tensor **y);
+B200NN_API void b200nn_linear_destroy(b200nn_linear *l);
+
+/* ---- Int4Linear (GH/nn/layers/int4_linear.rs:40-147) ---------------------------------------- */
+/* packed [K/8,N] u32, scales [ceil(K/group),N] f32 (rounded to fp16 inside), bias [N] or NULL. */
+B200NN_API int32_t b200nn_int4_linear_create(b200nn_ctx *ctx, const uint32_t *packed, const float *scales,
+                                             const float *bias, size_t in_features, size_t out_features, size_t group,
+                                             b200nn_int4_linear **out);
+B200NN_API int32_t b200nn_int4_linear_forward(b200nn_int4_linear *l, const b200nn_tensor *x, b200nn_tensor **y);
+/* Same computation on caller-owned buffers.  _dev: x [m,K], y [m,N] device f32, enqueued on the
+ * context stream, no synchronisation.  _host: pageable or pinned host buffers; copies in, runs,
+ * copies out and synchronises. */
+B200NN_API int32_t b200nn_int4_linear_forward_dev(b200nn_int4_linear *l, const float *x_dev, size_t m, float *y_dev);
+B200NN_API int32_t b200nn_int4_linear_forward_host(b200nn_int4_linear *l, const float *x_host, size_t m, float *y_host);
+B200NN_API size_t b200nn_int4_linear_memory_bytes(const b200nn_int4_linear *l); /* int4_linear.rs:136-146 */
+B200NN_API void b200nn_int4_linear_destroy(b200nn_int4_linear *l);
+
+/* ---- LayerNorm (GH/nn/layers/norm.rs:24-55) -------------------------------------------------- */
+B200NN_API int32_t b200nn_layernorm_create(b200nn_ctx *ctx, const float *gamma, const float *beta, size_t d, float eps,
+                                           b200nn_layernorm **out);
+B200NN_API int32_t b200nn_layernorm_forward(b200nn_layernorm *ln, const b200nn_tensor *x, b200nn_tensor **y);
+B200NN_API void b200nn_layernorm_destroy(b200nn_layernorm *ln);
+
+/* ---- Embedding (GH/nn/layers/embedding.rs:25-93) --------------------------------------------- */
+B200NN_API int32_t b200nn_embedding_create(b200nn_ctx *ctx, const float *wte, const float *wpe, size_t vocab,
+                                           size_t max_seq, size_t d, b200nn_embedding **out);
+/* forward_tokens_with_offset: out[p,:] = wte[ids[p],:] + wpe[offset+p,:]; ids are host u32. */
+B200NN_API int32_t b200nn_embedding_forward_tokens(b200nn_embedding *e, const uint32_t *ids_host, size_t n,
+                                                   size_t pos_offset, b200nn_tensor **out);
+B200NN_API void b200nn_embedding_destroy(b200nn_embedding *e);
+
+/* ---- MultiHeadAttention (GH/nn/layers/attention.rs:30-184) ----------------------------------- */
+/* qkv_weight [3d,d], qkv_bias [3d], out_weight [d,d], out_bias [d] (Linear layout [out,in]). */
+B200NN_API int32_t b200nn_attention_create(b200nn_ctx *ctx, const float *qkv_weight, const float *qkv_bias,
+                                           const float *out_weight, const float *out_bias, size_t n_embd,
+                                           size_t n_heads, b200nn_attention **out);
+B200NN_API int32_t b200nn_attention_forward_causal(b200nn_attention *a, const b200nn_tensor *x, b200nn_tensor **y);
+/* forward_cached: x [new_len,d]; cached_k/cached_v host f32 [n_heads][kv_len*d_head] flattened head
+ * after head; returns y and the new K,V rows [n_heads][new_len*d_head] in host buffers. */
+B200NN_API int32_t b200nn_attention_forward_cached(b200nn_attention *a, const b200nn_tensor *x, const float *cached_k,
+                                                   const float *cached_v, size_t kv_len, b200nn_tensor **y,
+                                                   float *new_k_out, float *new_v_out);
+B200NN_API void b200nn_attention_destroy(b200nn_attention *a);
+
+/* ---- GPT-2 models (GH/nn/models/gpt2.rs) ------------------------------------------------------ */
+/* Gpt2Config (gpt2.rs:20-93). */
+typedef struct {
+    int32_t n_layer, n_embd, n_head, vocab_size, n_positions;
+    float layer_norm_epsilon;
+} b200nn_gpt2_config;
+B200NN_API int32_t b200nn_gpt2_config_preset(const char *name /* small|medium|large|xl */, b200nn_gpt2_config *out);
+
+/* Gpt2Weights / TransformerLayerWeights (GH/model.rs:112-154): host f32, dense weights in the
+ * checkpoint's Conv1D layout [in,out]. */
+typedef struct {
+    const float *ln_1_weight, *ln_1_bias;
+    const float *c_attn_weight /* [d,3d] */, *c_attn_bias;
+    const float *c_proj_weight /* [d,d] */, *c_proj_bias;
+    const float *ln_2_weight, *ln_2_bias;
+    const float *mlp_fc_weight /* [d,4d] */, *mlp_fc_bias;
+    const float *mlp_proj_weight /* [4d,d] */, *mlp_proj_bias;
+} b200nn_gpt2_layer_weights;
+typedef struct {
+    const float *wte /* [vocab,d] */, *wpe /* [n_positions,d] */;
+    const float *ln_f_weight, *ln_f_bias;
+    const b200nn_gpt2_layer_weights *layers; /* n_layer entries */
+} b200nn_gpt2_weights;
+
+/* Gpt2Model::from_weights (gpt2.rs:337-404): f32 weights. */
+B200NN_API int32_t b200nn_gpt2_create(b200nn_ctx *ctx, const b200nn_gpt2_config *cfg, const b200nn_gpt2_weights *w,
+                                      uint32_t flags, b200nn_gpt2 **out);
+/* Int4Gpt2Model::from_weights (gpt2.rs:1356-1436): quantises every block Linear on the host with
+ * the rule of quantize.rs:102-153 (scales then rounded to fp16); embeddings and LayerNorm stay f32;
+ * the LM head stays f32 unless B200NN_QUANT_LM_HEAD. */
+B200NN_API int32_t b200nn_int4_gpt2_create(b200nn_ctx *ctx, const b200nn_gpt2_config *cfg, const b200nn_gpt2_weights *w,
+                                           size_t group_size, uint32_t flags, b200nn_gpt2 **out);
+B200NN_API void b200nn_gpt2_destroy(b200nn_gpt2 *m);
+B200NN_API int32_t b200nn_gpt2_get_config(const b200nn_gpt2 *m, b200nn_gpt2_config *out);
+/* Int4Gpt2Model::quantized_memory_bytes (gpt2.rs:1563-1576); 0 for an f32 model. */
+B200NN_API size_t b200nn_gpt2_quantized_memory_bytes(const b200nn_gpt2 *m);
+/* Read back the int4 data the model holds for one block Linear (which: 0 c_attn, 1 c_proj, 2 mlp.c_fc,
+ * 3 mlp.c_proj; layer -1 with which 0 = the LM head), in the reference layout: packed [K/8,N], scales
+ * [ceil(K/g),N] (already fp16-rounded).  Lets a checker run the same nibbles through its own math. */
+B200NN_API int32_t b200nn_gpt2_get_int4(const b200nn_gpt2 *m, int32_t layer, int32_t which, uint32_t *packed,
+                                        float *scales, size_t *k_out, size_t *n_out);
+
+/* Gpt2Model::forward / Int4Gpt2Model::forward (gpt2.rs:481-499, 1522-1533): one sequence of host
+ * token ids -> logits [seq_len,vocab] for every position. */
+B200NN_API int32_t b200nn_gpt2_forward(b200nn_gpt2 *m, const uint32_t *ids_host, size_t seq_len, b200nn_tensor **logits);
+
+/* KvCache (gpt2.rs:1064-1117), device resident, fp16, with a batch axis added:
+ * [layer][sequence][head][capacity][64] for K and V. */
+B200NN_API int32_t b200nn_kvcache_create(b200nn_gpt2 *m, size_t batch, size_t capacity, b200nn_kvcache **out);
+B200NN_API size_t b200nn_kvcache_len(const b200nn_kvcache *c);
+B200NN_API int32_t b200nn_kvcache_reset(b200nn_kvcache *c);
+B200NN_API void b200nn_kvcache_destroy(b200nn_kvcache *c);
+/* Gpt2Model::forward_cached (gpt2.rs:712-734): ids_host is [batch,new_len] (batch = the cache's);
+ * appends to the cache and returns logits [batch*new_len,vocab]. */
+B200NN_API int32_t b200nn_gpt2_forward_cached(b200nn_gpt2 *m, const uint32_t *ids_host, size_t new_len,
+                                              b200nn_kvcache *cache, b200nn_tensor **logits);
+
+/* Gpt2Model::generate / generate_cached, Int4Gpt2Model::generate (gpt2.rs:672-706, 740-783,
+ * 1536-1560): greedy decoding of one sequence.  out_tokens holds prompt_len+max_new entries;
+ * *n_out = prompt + generated count.  Both run KV-cached on the device (same tokens as the
+ * reference's uncached loop, which recomputes the same positions). */
+B200NN_API int32_t b200nn_gpt2_generate(b200nn_gpt2 *m, const uint32_t *prompt, size_t prompt_len, size_t max_new,
+                                        uint32_t flags, uint32_t *out_tokens, size_t *n_out);
+B200NN_API int32_t b200nn_gpt2_generate_cached(b200nn_gpt2 *m, const uint32_t *prompt, size_t prompt_len,
+                                               size_t max_new, uint32_t flags, uint32_t *out_tokens, size_t *n_out);
+/* Batched greedy decoding (added axis; batch=1 equals the call above): prompts [batch,prompt_len]
+ * host u32 -> out_tokens [batch,prompt_len+max_new], out_lens [batch]. */
+B200NN_API int32_t b200nn_gpt2_generate_batch(b200nn_gpt2 *m, const uint32_t *prompts, size_t batch, size_t prompt_len,
+                                              size_t max_new, uint32_t flags, uint32_t *out_tokens, size_t *out_lens);
+
+/* ---- decode session: the batched generate loop in pieces, state resident on the device -------- */
+/* A session owns a KV cache for `batch` sequences of up to `capacity` positions plus the step
+ * buffers.  prefill() runs the prompts and picks the first token; step() runs n greedy decode
+ * steps, feeding each sequence's token back on the device, without host synchronisation. */
+B200NN_API int32_t b200nn_session_create(b200nn_gpt2 *m, size_t batch, size_t capacity, uint32_t flags,
+                                         b200nn_session **out);
+B200NN_API int32_t b200nn_session_prefill(b200nn_session *s, const uint32_t *prompts_host, size_t prompt_len);
+B200NN_API int32_t b200nn_session_step(b200nn_session *s, size_t n_steps);
+/* Move the position counter back (keeps the cache contents): lets a benchmark time the same
+ * context window repeatedly. */
+B200NN_API int32_t b200nn_session_rewind(b200nn_session *s, size_t position);
+B200NN_API size_t b200nn_session_position(const b200nn_session *s);
+/* Tokens generated so far, [batch,generated] host u32 (synchronises). */
+B200NN_API int32_t b200nn_session_tokens(b200nn_session *s, uint32_t *out, size_t capacity_per_seq, size_t *generated);
+/* Logits of the most recent step, [batch,vocab] host f32 (synchronises). */
+B200NN_API int32_t b200nn_session_logits(b200nn_session *s, float *out);
+/* Per-kernel-family device time of ONE decode step at the current position, measured with CUDA
+ * events around each launch (Gpt2Model::forward_profiled, gpt2.rs:529-568).  times_ms has
+ * B200NN_PROF_COUNT entries. */
+enum {
+    B200NN_PROF_EMBED = 0, B200NN_PROF_LAYERNORM, B200NN_PROF_LINEAR, B200NN_PROF_ATTENTION,
+    B200NN_PROF_LM_HEAD, B200NN_PROF_ARGMAX, B200NN_PROF_COUNT
+};
+B200NN_API int32_t b200nn_session_profile_step(b200nn_session *s, float *times_ms, uint64_t *linear_bytes);
+B200NN_API void b200nn_session_destroy(b200nn_session *s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200NN_H */

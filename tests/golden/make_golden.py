@@ -1,0 +1,26 @@
+"""Generates tests/golden/tiny_gpt2_golden.npz with the CPU oracle (run from the repository root:
+``python tests/golden/make_golden.py``).  The reference is Rust and cannot run offline, so the
+vectors are the oracle's own outputs, pinned so that later edits to the oracle cannot drift
+unnoticed; the reference's known-answer tests live in reference_kats.json."""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path[:0] = [ROOT, os.path.join(ROOT, "async-gpu_b200")]
+from oracle import oracle  # noqa: E402
+from b200nn import synth  # noqa: E402
+from b200nn.gpt2 import Gpt2Config  # noqa: E402
+
+TINY = dict(n_layer=2, n_embd=128, n_head=2, vocab_size=211, n_positions=32, layer_norm_epsilon=1e-5)
+SEED = 21
+w = synth.gpt2_weights(Gpt2Config(**TINY), base_seed=SEED, std=0.08, random_ln=True)
+m = oracle.Model(TINY, w)
+tokens = synth.token_ids(77, (10,), TINY["vocab_size"])
+logits = m.forward(tokens)
+generated, _ = m.generate_cached(tokens[:5], 8)
+p, s = oracle.quantize_weight_int4(w["h.0.mlp.c_fc.weight"], 128, 512, 128)
+np.savez_compressed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "tiny_gpt2_golden.npz"),
+                    seed=SEED, tokens=tokens, logits=logits, generated=generated, fc_packed=p, fc_scales=s)
+print("written", logits.shape, generated)

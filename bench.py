@@ -1,0 +1,323 @@
+#!/usr/bin/env python
+"""Benchmark of the int4 GPT-2 decode path.
+
+    python bench.py --gpus N --steps K --warmup W            # this library, one rank per GPU
+    python bench.py --impl reference --steps K --warmup W    # the reference's CPU path (oracle port)
+
+Workload (BASELINE.json configs[4]): GPT-2 XL, every Linear int4 group-128 (LM head included), fp16
+KV cache, 256 independent sequences sharded over the ranks (256/N each, no data-path collective),
+prompt of 128 random token ids, greedy decode of 128 tokens.  A "step" is one greedy decode step of
+every sequence of the batch (all layers, LM head, argmax, token fed back on the device) at context
+128 + (step mod 128).  Weights and token ids are seeded synthetic data.
+
+One JSON line is printed by rank 0; see DESIGN.md for the meaning of every key.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path[:0] = [os.path.join(ROOT, "async-gpu_b200"), ROOT]
+
+WORKLOADS = {
+    # name: (preset, total batch, prompt, max_new)
+    "gpt2-xl-int4-b256": ("xl", 256, 128, 128),
+    "gpt2-small-int4-b32": ("small", 32, 512, 256),
+}
+METRIC = "int4 GPT-2 decode tokens/sec"
+UNIT = "tokens/s"
+
+
+def shard_bounds(total: int, world: int, rank: int):
+    """Contiguous block partition of `total` sequences: the first total % world ranks get one more."""
+    base, extra = divmod(total, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    return 6650.0, 1400.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.rows, self._halt = index, [], threading.Event()
+
+    def run(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        while not self._halt.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={q}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                f = [x.strip() for x in out.strip().split(",")]
+                if len(f) >= 6:
+                    self.rows.append(f)
+            except Exception:
+                pass
+            self._halt.wait(0.2)
+
+    def finish(self):
+        self._halt.set()
+        self.join(timeout=6)
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        sm = sorted(float(r[0]) for r in self.rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(self.rows[0][1]), "reasons": reasons,
+                "samples": len(self.rows)}
+
+
+def build_int4_oracle_weights(cfg, w, group=128):
+    """int4-quantises every dense weight and the LM head with the ORACLE's quantiser, rounds the scales
+    to fp16 and dequantises again: the f32 matrices the CPU reference path multiplies."""
+    from oracle import oracle
+    d = cfg.n_embd
+    out = dict(w)
+    for i in range(cfg.n_layer):
+        for nm, (k, n) in {"attn.c_attn.weight": (d, 3 * d), "attn.c_proj.weight": (d, d),
+                           "mlp.c_fc.weight": (d, 4 * d), "mlp.c_proj.weight": (4 * d, d)}.items():
+            key = f"h.{i}.{nm}"
+            p, s = oracle.quantize_weight_int4(w[key], k, n, group)
+            out[key] = oracle.dequant_weight_int4(p, oracle.f16_round(s), k, n, group)
+    wt = np.ascontiguousarray(w["wte"].T)
+    p, s = oracle.quantize_weight_int4(wt, d, cfg.vocab_size, group)
+    out["lm_head"] = oracle.dequant_weight_int4(p, oracle.f16_round(s), d, cfg.vocab_size, group)
+    return out
+
+
+def cpu_decode_sample(cfg, w, prompt, steps, warmup):
+    """Times `steps` KV-cached greedy decode steps of ONE sequence on the host cores with the oracle."""
+    from oracle import oracle
+    om = oracle.Model(cfg.as_dict(), w)
+    flags = oracle.KV_FP16
+    if warmup:
+        om.time_decode(prompt, warmup, flags)
+    sec, _ = om.time_decode(prompt, steps, flags)
+    return sec, oracle.num_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    from b200nn import synth  # seeded data generator only (numpy); no library code runs on this arm
+    from b200nn.gpt2 import Gpt2Config
+    preset, total, prompt_len, max_new = WORKLOADS[args.workload]
+    cfg = getattr(Gpt2Config, preset)()
+    w = build_int4_oracle_weights(cfg, synth.gpt2_weights(cfg))
+    prompt = synth.token_ids(synth.BASE_SEED + 7, (total, prompt_len), cfg.vocab_size)[0, : args.cpu_prompt]
+    steps = min(args.steps, args.cpu_max_steps)
+    sec, threads = cpu_decode_sample(cfg, w, prompt, steps, min(args.warmup, 2))
+    value = steps / sec
+    sample = (f"1 of {total} sequences, prompt {args.cpu_prompt} tokens, {steps} KV-cached greedy decode steps, "
+              f"f64 accumulate, OpenMP over output columns")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": min(args.warmup, 2), "ms_per_step": 1e3 * sec / steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "int4 weights, f64 accumulate", "data": "synthetic",
+        "config": {"workload": args.workload, "note": "CPU restatement of the reference path (Rust reference "
+                   "cannot be built offline); each step is one decode step of a 1-sequence sample"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+    import b200nn
+    from b200nn import DecodeSession, Gpt2Config, Int4Gpt2Model, synth
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        args.gpus = world
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    preset, total, prompt_len, max_new = WORKLOADS[args.workload]
+    if args.batch:
+        total = args.batch
+    cfg = getattr(Gpt2Config, preset)()
+    lo, hi = shard_bounds(total, world, rank)
+    batch = hi - lo
+    reg = b200nn.KernelRegistry(local)
+    w = synth.gpt2_weights(cfg)
+    t0 = time.time()
+    model = Int4Gpt2Model.from_weights(w, cfg, reg, flags=b200nn.QUANT_LM_HEAD, group_size=128)
+    build_s = time.time() - t0
+    prompts_all = synth.token_ids(synth.BASE_SEED + 7, (total, prompt_len), cfg.vocab_size)
+    prompts = np.ascontiguousarray(prompts_all[lo:hi])
+
+    capacity = prompt_len + max_new + 8
+    sess = DecodeSession(model, batch, capacity)
+    sess.prefill(prompts)
+    stream = torch.cuda.ExternalStream(reg.stream, device=torch.device("cuda", local))
+    window = max_new  # context goes prompt_len .. prompt_len + window - 1, then wraps
+
+    def run_steps(n):
+        done = 0
+        while done < n:
+            room = prompt_len + window - sess.position()
+            if room <= 0:
+                sess.rewind(prompt_len)
+                room = window
+            k = min(room, n - done)
+            sess.step(k)
+            done += k
+
+    run_steps(max(args.warmup, 3))
+    reg.synchronize()
+    sess.rewind(prompt_len)
+    launches0 = reg.launch_count()
+    sampler = ClockSampler(local)
+    barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        run_steps(args.steps)
+        e1.record(stream)
+    torch.cuda.synchronize()
+    barrier()
+    clocks = sampler.finish()
+    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    launches = reg.launch_count() - launches0
+    value = total * args.steps / (ms / 1e3)
+
+    # per-kernel-family device time of single decode steps at mid-window context (CUDA events
+    # around every launch on the library's stream), for the roofline of the dominant kernel
+    sess.rewind(prompt_len)
+    run_steps(window // 2)
+    fam = {n: 0.0 for n in b200nn.PROF_NAMES}
+    reps = 3
+    lin_bytes = 0
+    ctx_mid = sess.position() + 1
+    for _ in range(reps):
+        t, lin_bytes = sess.profile_step()
+        for k2, v in t.items():
+            fam[k2] += v / reps
+        sess.rewind(sess.position() - 1)
+    hbm_peak, tf_peak, peak_kind = peaks()
+    H, L, d = cfg.n_head, cfg.n_layer, cfg.n_embd
+    act_b = 2 if batch > 2 else 4
+    attn_bytes_launch = batch * H * ctx_mid * 64 * 2 * 2 + 2 * batch * d * act_b
+    lin_flops = sum(2 * batch * k * n for k, n in ((d, 3 * d), (d, d), (d, 4 * d), (4 * d, d))) * L
+    roofs = {
+        "attention": {"kernel": "decode_attn_kernel", "bound": "hbm", "unit": "GB/s", "peak": hbm_peak,
+                      "achieved": attn_bytes_launch * L / (fam["attention"] * 1e-3) / 1e9 if fam["attention"] else 0.0},
+        "linear": {"kernel": "int4 Linear kernels (4 per layer)", "bound": "hbm", "unit": "GB/s", "peak": hbm_peak,
+                   "achieved": lin_bytes / (fam["linear"] * 1e-3) / 1e9 if fam["linear"] else 0.0,
+                   "tensor_tflops": lin_flops / (fam["linear"] * 1e-3) / 1e12 if fam["linear"] else 0.0},
+    }
+    dominant = max(("attention", "linear"), key=lambda k2: fam[k2])
+    roof = dict(roofs[dominant])
+    roof["frac"] = roof["achieved"] / roof["peak"] if roof["peak"] else None
+    roof["traffic"] = None
+    roof["peak_source"] = peak_kind
+    roof["launch_ms"] = fam[dominant] / (L * (4 if dominant == "linear" else 1))
+    roof["step_family_ms"] = {k2: round(v, 4) for k2, v in fam.items()}
+    roof["other"] = {k2: {"achieved": v["achieved"], "frac": v["achieved"] / v["peak"]} for k2, v in roofs.items()
+                     if k2 != dominant}
+
+    # end to end through the public batched generate call: host prompts in, host tokens out
+    e2e_runs = []
+    for _ in range(args.e2e_runs):
+        barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out, lens = model.generate_batch(prompts, max_new)
+        t1 = time.perf_counter()
+        dt = torch.tensor([t1 - t0], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        e2e_runs.append(float(dt.item()))
+    e2e = None
+    if e2e_runs:
+        best = min(e2e_runs)
+        e2e = {"value": total * max_new / best, "unit": UNIT, "h2d_bytes_per_step": batch * prompt_len * 4 / max_new,
+               "d2h_bytes_per_step": batch * max_new * 4 / max_new, "seconds_per_generate": best,
+               "note": "generate_batch: prefill + %d decode steps, host token ids in, host tokens out; "
+                       "bytes are per decode step per rank" % max_new}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int4 weights / fp16 operands / f32 accumulate", "data": "synthetic",
+        "config": {"workload": args.workload, "total_sequences": total, "sequences_per_gpu": batch,
+                   "prompt_len": prompt_len, "decode_window": [prompt_len, prompt_len + window - 1],
+                   "l2": "inputs larger than L2 (weights + KV read per step: %.1f GB)" %
+                         ((lin_bytes + attn_bytes_launch * L) / 1e9),
+                   "model_build_s": round(build_s, 1)},
+        "roofline": roof, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        wq = build_int4_oracle_weights(cfg, w)
+        steps = args.cpu_steps
+        sec, threads = cpu_decode_sample(cfg, wq, prompts_all[0, : args.cpu_prompt], steps, 1)
+        line["cpu_baseline"] = {"value": steps / sec, "unit": UNIT, "cores": threads, "kind": "port",
+                                "sample": f"1 of {total} sequences, prompt {args.cpu_prompt}, {steps} KV-cached decode "
+                                          f"steps with the oracle (f64 accumulate)"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="gpt2-xl-int4-b256", choices=sorted(WORKLOADS))
+    ap.add_argument("--batch", type=int, default=0, help="override the total number of sequences")
+    ap.add_argument("--e2e-runs", type=int, default=2)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-steps", type=int, default=8)
+    ap.add_argument("--cpu-prompt", type=int, default=32)
+    ap.add_argument("--cpu-max-steps", type=int, default=64)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.gpus > 1 and "RANK" not in os.environ:
+        # convenience: relaunch under torchrun when called plainly with --gpus N
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", "29511", os.path.abspath(__file__)] + sys.argv[1:]
+        return subprocess.call(cmd)
+    return run_b200(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,97 @@
+"""CPU tests of the C-ABI library: it loads, exports every declared symbol, its host-side logic
+(the quantiser) matches the oracle, and without a GPU it fails loudly instead of falling back."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+import b200nn
+from b200nn import ops
+from oracle import oracle
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "b200nn.h")).read()
+    return sorted(set(re.findall(r"B200NN_API[^;]*?\b(b200nn_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = b200nn.load_library()
+    names = _declared_symbols()
+    assert len(names) > 70
+    for n in names:
+        assert hasattr(lib, n), f"libb200nn.so does not export {n}"
+    # and the Python mirror binds each of them with a signature
+    assert set(names) == set(lib._declared)
+
+
+def test_version_string():
+    assert b"sm_100a" in b200nn.load_library().b200nn_version()
+
+
+def _has_gpu():
+    try:
+        import torch
+        return torch.cuda.is_available()
+    except Exception:
+        return False
+
+
+@pytest.mark.skipif(_has_gpu(), reason="checks the no-GPU behaviour")
+def test_no_gpu_means_error_not_fallback():
+    with pytest.raises(b200nn.NnError) as e:
+        b200nn.KernelRegistry.init_default()
+    assert e.value.code == b200nn.ERR_CUDA
+
+
+@pytest.mark.parametrize("k,n,group", [(8, 4, 128), (64, 24, 32), (768, 96, 128), (1600, 33, 128)])
+def test_host_quantizer_matches_oracle(k, n, group):
+    rng = np.random.default_rng(k + n)
+    w = (rng.standard_normal((k, n)) * 0.02).astype(np.float32)
+    w[:, -1] = 0.0
+    p, s = ops.quantize_weight_int4(w, k, n, group)
+    po, so = oracle.quantize_weight_int4(w, k, n, group)
+    assert np.array_equal(p, po) and np.array_equal(s, so)
+
+
+def test_host_quantizer_rejects_bad_k():
+    with pytest.raises(b200nn.NnError) as e:
+        ops.quantize_weight_int4(np.zeros((12, 4), np.float32), 12, 4, 128)
+    assert e.value.code == b200nn.ERR_SHAPE
+
+
+def test_host_pack_helpers_match_reference_kats():
+    assert ops.pack_int8_to_u32([1, 2, 3, 4, 5, 6, 7, 8]).tolist() == [0x04030201, 0x08070605]
+    assert ops.pack_int8_to_u32([1, 2, 3]).tolist() == [0x00030201]
+    q, s = ops.quantize_int8_per_tensor([0.0, 1.0, -1.0, 0.5])
+    assert abs(s - 1 / 127) < 1e-6 and q[:3].tolist() == [0, 127, -127]
+    data = np.array([0.0, 1.0, -1.0, 0.5, 0.25, -0.5, 0.75, -0.75], dtype=np.float32)
+    p, sc = ops.quantize_int4_per_group(data, 128)
+    po, so = oracle.quantize_int4_per_group(data, 128)
+    assert np.array_equal(p, po) and np.array_equal(sc, so)
+    word = sum(((v + 8) & 0xF) << (4 * i) for i, v in enumerate(range(-4, 4)))
+    assert [ops.unpack_int4(word, i) for i in range(8)] == list(range(-4, 4))
+
+
+def test_config_presets():
+    lib = b200nn.load_library()
+    for name, (l, d, h) in dict(small=(12, 768, 12), medium=(24, 1024, 16), large=(36, 1280, 20),
+                                xl=(48, 1600, 25)).items():
+        c = b200nn._Cfg()
+        assert lib.b200nn_gpt2_config_preset(name.encode(), C.byref(c)) == 0
+        assert (c.n_layer, c.n_embd, c.n_head, c.vocab_size, c.n_positions) == (l, d, h, 50257, 1024)
+        py = getattr(b200nn.Gpt2Config, name)()
+        assert (py.n_layer, py.n_embd, py.n_head) == (l, d, h) and py.head_dim() == 64 and py.ffn_dim() == 4 * d
+    assert lib.b200nn_gpt2_config_preset(b"huge", C.byref(b200nn._Cfg())) == b200nn.ERR_UNSUPPORTED
+
+
+def test_null_handles_are_rejected():
+    lib = b200nn.load_library()
+    assert lib.b200nn_ctx_synchronize(None) == b200nn.ERR_ARG
+    assert lib.b200nn_session_step(None, 1) == b200nn.ERR_ARG
+    assert lib.b200nn_tensor_numel(None) == 0
+    assert lib.b200nn_kvcache_len(None) == 0

@@ -1,0 +1,199 @@
+"""GPU parity tests of the single ops and layers, through the C ABI, against the CPU oracle.
+
+Tolerances: f32 CUDA-core kernels are compared at 1e-5 relative RMS (f32 accumulation against the
+oracle's f64); kernels that feed fp16 operands to the tensor cores at 5e-4 relative RMS, inside
+the path's budget of 1e-3 relative RMS / 2e-2 max-abs on logits."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import b200nn
+import np_ref
+from b200nn import GpuTensor, ops, synth
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+KATS = json.load(open(os.path.join(HERE, "golden", "reference_kats.json")))
+
+
+def _formula(expr, n, **env):
+    return np.array([eval(expr, {}, dict(i=i, **env)) for i in range(n)], dtype=np.float32)
+
+
+# ---- isolated int4 Linear: the shapes of the benchmark's second configuration -------------------
+@pytest.mark.parametrize("k,n", [(768, 3072), (3072, 768), (768, 2304), (768, 50257)])
+@pytest.mark.parametrize("m", [1, 8, 64])
+def test_int4_linear_shapes(reg, m, k, n):
+    packed, scales, x, _ = synth.int4_linear_case(100 + m, m, k, n, 128)
+    lin = b200nn.Int4Linear(packed, scales, None, k, n, 128, reg)
+    y = lin.forward(GpuTensor.from_host(x, (m, k), reg)).to_host()
+    ref = oracle.int4_linear(x, packed, scales, None, m, n, k, 128, f64=True)
+    assert y.shape == (m, n)
+    rr = np_ref.rel_rms(y, ref)
+    tc = m > 2  # rows above the GEMV threshold take the fp16 tensor-core path
+    assert rr < (5e-4 if tc else 1e-5), rr
+    assert np.abs(y - ref).max() < (2e-2 if tc else 1e-3)
+    assert lin.memory_bytes() == packed.size * 4 + scales.size * 4
+
+
+@pytest.mark.parametrize("m,k,n,group", [(1, 1600, 1600, 128), (2, 6400, 1600, 128), (3, 1600, 4800, 128),
+                                         (4, 128, 130, 64), (7, 192, 257, 64), (5, 64, 1, 64)])
+def test_int4_linear_ragged(reg, m, k, n, group):
+    # K=1600 has a ragged last group of 64; N not a multiple of the 128-row tile; bias present
+    packed, scales, x, _ = synth.int4_linear_case(7 * m + k, m, k, n, group)
+    bias = np.linspace(-0.5, 0.5, n).astype(np.float32)
+    reg.set_gemv_max_rows(8)  # exercise the CUDA-core path for every row count here
+    try:
+        y = b200nn.Int4Linear(packed, scales, bias, k, n, group, reg).forward(GpuTensor.from_host(x, (m, k), reg)).to_host()
+    finally:
+        reg.set_gemv_max_rows(-1)
+    ref = oracle.int4_linear(x, packed, scales, bias, m, n, k, group, f64=True)
+    assert np_ref.rel_rms(y, ref) < 1e-5
+
+
+@pytest.mark.parametrize("k,n,group", [(8, 4, 128), (24, 5, 16), (40, 3, 128)])
+def test_int4_linear_odd_shapes_take_generic_kernel(reg, k, n, group):
+    # shapes the tiled layout cannot hold (K % 64 != 0) still work, as in the reference
+    rng = np.random.default_rng(k)
+    w = (rng.standard_normal((k, n)) * 0.1).astype(np.float32)
+    packed, scales = ops.quantize_weight_int4(w, k, n, group)
+    x = rng.standard_normal((3, k)).astype(np.float32)
+    y = b200nn.Int4Linear(packed, scales, None, k, n, group, reg).forward(GpuTensor.from_host(x, (3, k), reg)).to_host()
+    sc16 = oracle.f16_round(scales)  # the library keeps group scales in fp16
+    ref = oracle.int4_linear(x, packed, sc16, None, 3, n, k, group, f64=True)
+    assert np.abs(y - ref).max() < 1e-5
+
+
+def test_int4_linear_host_entry_and_errors(reg):
+    packed, scales, x, _ = synth.int4_linear_case(5, 2, 768, 768, 128)
+    lin = b200nn.Int4Linear(packed, scales, None, 768, 768, 128, reg)
+    y = lin.forward_host(x)
+    ref = oracle.int4_linear(x, packed, scales, None, 2, 768, 768, 128)
+    assert np_ref.rel_rms(y, ref) < 1e-5
+    with pytest.raises(b200nn.NnError) as e:  # int4_linear.rs:74-79 shape check
+        lin.forward(GpuTensor.zeros((2, 700), reg))
+    assert e.value.code == b200nn.ERR_SHAPE
+    with pytest.raises(b200nn.NnError):
+        b200nn.Int4Linear(packed, scales, None, 770, 768, 128, reg)
+
+
+def test_int4_matmul_op(reg):
+    rng = np.random.default_rng(1)
+    b = (rng.standard_normal((256, 96)) * 0.05).astype(np.float32)
+    a = rng.standard_normal((2, 256)).astype(np.float32)
+    y = ops.int4_matmul(GpuTensor.from_host(a, (2, 256), reg), b, 256, 96, 128, reg).to_host()
+    p, s = oracle.quantize_weight_int4(b, 256, 96, 128)
+    ref = oracle.int4_linear(a, p, oracle.f16_round(s), None, 2, 96, 256, 128)
+    assert np_ref.rel_rms(y, ref) < 1e-5
+
+
+# ---- f32 Linear: the reference's own arithmetic-pattern tests (layers/linear.rs:388-464) ---------
+@pytest.mark.parametrize("idx", [0, 1])
+def test_linear_reference_patterns(reg, idx):
+    c = KATS["patterns"][idx]
+    b, k, n = c["batch"], c["in"], c["out"]
+    w = _formula(c["weight_formula"], n * k)
+    bias = _formula(c["bias_formula"], n)
+    x = _formula(c["input_formula"], b * k)
+    y = b200nn.Linear(w, bias, k, n, reg).forward(GpuTensor.from_host(x, (b, k), reg)).to_host()
+    ref = oracle.matmul(x, np.ascontiguousarray(w.reshape(n, k).T), b, k, n) + bias
+    assert y.shape == (b, n)
+    assert np.abs(y - ref).max() < min(c["tol"], 1e-4)
+
+
+@pytest.mark.parametrize("m", [1, 3, 70])
+def test_linear_fused_activation(reg, m):
+    rng = np.random.default_rng(m)
+    w = (rng.standard_normal((200, 96)) * 0.1).astype(np.float32)  # [out,in]
+    bias = rng.standard_normal(200).astype(np.float32)
+    x = rng.standard_normal((m, 96)).astype(np.float32)
+    lin = b200nn.Linear(w, bias, 96, 200, reg)
+    pre = x.astype(np.float64) @ w.astype(np.float64).T + bias
+    y = lin.forward_fused(GpuTensor.from_host(x, (m, 96), reg), b200nn.ACT_GELU_TANH).to_host()
+    assert np.abs(y - np_ref.gelu_tanh(pre)).max() < 1e-4
+    y = lin.forward_fused(GpuTensor.from_host(x, (m, 96), reg), b200nn.ACT_RELU).to_host()
+    assert np.abs(y - np.maximum(pre, 0)).max() < 1e-4
+    with pytest.raises(b200nn.NnError):
+        lin.forward(GpuTensor.zeros((m, 95), reg))
+
+
+# ---- LayerNorm, activations, element-wise -------------------------------------------------------
+def test_layernorm_reference_pattern(reg):
+    c = KATS["patterns"][2]
+    b, d = c["batch"], c["d"]
+    g = _formula(c["gamma_formula"], d)
+    be = _formula(c["beta_formula"], d)
+    x = _formula(c["input_formula"], b * d, batch=b, d=d)
+    y = b200nn.LayerNorm(g, be, c["eps"], reg).forward(GpuTensor.from_host(x, (b, d), reg)).to_host()
+    assert np.abs(y - oracle.layer_norm(x, g, be, c["eps"]).reshape(b, d)).max() < 1e-5
+
+
+@pytest.mark.parametrize("rows,d", [(1, 768), (33, 1600), (5, 64), (3, 5000)])
+def test_layernorm_and_residual_dual(reg, rows, d):
+    rng = np.random.default_rng(d)
+    x = (rng.standard_normal((rows, d)) * 3 + 50).astype(np.float32)  # large mean: needs the two-pass variance
+    r = rng.standard_normal((rows, d)).astype(np.float32)
+    g = rng.standard_normal(d).astype(np.float32)
+    b = rng.standard_normal(d).astype(np.float32)
+    tg, tb = GpuTensor.from_host(g, (d,), reg), GpuTensor.from_host(b, (d,), reg)
+    y = ops.layer_norm(GpuTensor.from_host(x, (rows, d), reg), tg, tb, 1e-5, reg).to_host()
+    assert np.abs(y - oracle.layer_norm(x, g, b).reshape(rows, d)).max() < 2e-4
+    s, nrm = ops.layer_norm_residual_dual(GpuTensor.from_host(x, (rows, d), reg), GpuTensor.from_host(r, (rows, d), reg),
+                                          tg, tb, 1e-5, reg)
+    assert np.array_equal(s.to_host(), x + r)
+    assert np.abs(nrm.to_host() - oracle.layer_norm(x + r, g, b).reshape(rows, d)).max() < 2e-4
+
+
+def test_gelu_forms(reg):
+    x = np.linspace(-5, 5, 1001).astype(np.float32)  # range of tests_transformer.rs:128-207
+    t = GpuTensor.from_host(x, (1001,), reg)
+    assert np.abs(ops.gelu(t, reg).to_host() - oracle.gelu_tanh(x)).max() < 1e-5
+    assert np.abs(ops.gelu(t, reg, sigmoid_form=True).to_host() - oracle.gelu_sigmoid(x)).max() < 1e-5
+    assert np.abs(b200nn.GELU(reg).forward(t).to_host() - np_ref.gelu_tanh(x)).max() < 1e-5
+
+
+def test_bias_add_elementwise_add_reshape(reg):
+    rng = np.random.default_rng(2)
+    a = rng.standard_normal((6, 10)).astype(np.float32)
+    b = rng.standard_normal((6, 10)).astype(np.float32)
+    bias = rng.standard_normal(10).astype(np.float32)
+    ta = GpuTensor.from_host(a, (6, 10), reg)
+    ops.bias_add(ta, GpuTensor.from_host(bias, (10,), reg), reg)
+    ops.elementwise_add(ta, GpuTensor.from_host(b, (6, 10), reg), reg)
+    assert np.allclose(ta.to_host(), a + bias + b, atol=1e-6)
+    v = ta.reshape((3, 20))
+    assert v.shape() == (3, 20) and np.array_equal(v.to_host().ravel(), ta.to_host().ravel())
+    with pytest.raises(b200nn.NnError):
+        ta.reshape((7, 7))
+    z = GpuTensor.zeros((4, 4), reg)
+    assert not z.to_host().any() and z.clone_tensor().numel() == 16
+
+
+def test_embedding_with_offset(reg):
+    rng = np.random.default_rng(3)
+    wte = rng.standard_normal((50, 64)).astype(np.float32)
+    wpe = rng.standard_normal((16, 64)).astype(np.float32)
+    e = b200nn.Embedding(wte, wpe, 50, 16, 64, reg)
+    ids = np.array([3, 49, 0, 7], dtype=np.uint32)
+    assert np.array_equal(e.forward_tokens(ids).to_host(), wte[ids] + wpe[:4])   # tests_transformer.rs:739-836
+    assert np.array_equal(e.forward_tokens_with_offset(ids, 4, 9).to_host(), wte[ids] + wpe[9:13])
+    with pytest.raises(b200nn.NnError):
+        e.forward_tokens(np.array([50], dtype=np.uint32))
+    with pytest.raises(b200nn.NnError):
+        e.forward_tokens_with_offset(ids, 4, 13)
+
+
+def test_split_qkv_concat_heads_roundtrip(reg):
+    rng = np.random.default_rng(4)
+    seq, H, dh = 7, 3, 64
+    qkv = rng.standard_normal((seq, 3 * H * dh)).astype(np.float32)
+    q, k, v = ops.split_qkv(GpuTensor.from_host(qkv, qkv.shape, reg), seq, H, dh, reg)
+    d = H * dh
+    for t, off in ((q, 0), (k, d), (v, 2 * d)):
+        ref = qkv[:, off:off + d].reshape(seq, H, dh).transpose(1, 0, 2)
+        assert np.array_equal(t.to_host(), ref)
+    back = ops.concat_heads(q, seq, H, dh, reg).to_host()
+    assert np.array_equal(back, qkv[:, :d])

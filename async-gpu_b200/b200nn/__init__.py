@@ -73,6 +73,8 @@ def load_library() -> C.CDLL:
             "b200nn_last_error_message": (C.c_char_p, [vp]), "b200nn_last_cuda_error": (i32, [vp]),
             "b200nn_ctx_device_error": (i32, [vp, _u32p]), "b200nn_ctx_launch_count": (C.c_uint64, [vp]),
             "b200nn_ctx_set_gemv_max_rows": (i32, [vp, i32]),
+            "b200nn_ctx_set_tuning": (i32, [vp, C.c_char_p, i32]),
+            "b200nn_ctx_read_trace": (i32, [vp, C.POINTER(C.c_longlong)]),
             "b200nn_tensor_from_host": (i32, [vp, _f32p, szp, i32, vpp]),
             "b200nn_tensor_zeros": (i32, [vp, szp, i32, vpp]), "b200nn_tensor_to_host": (i32, [vp, _f32p, sz]),
             "b200nn_tensor_ndim": (i32, [vp]), "b200nn_tensor_numel": (sz, [vp]),
@@ -186,6 +188,9 @@ class KernelRegistry:
 
     def set_gemv_max_rows(self, rows: int):
         self.check(self.lib.b200nn_ctx_set_gemv_max_rows(self.h, rows))
+
+    def set_tuning(self, key: str, value: int):
+        self.check(self.lib.b200nn_ctx_set_tuning(self.h, key.encode(), value))
 
     def device_error(self) -> int:
         w = C.c_uint32()

@@ -158,12 +158,16 @@ int launch_decode_attention(b200nn_ctx *ctx, const void *q, bool q_half, int ldq
     dim3 grid(H, B, n_splits);
     int ldo = H * 64;
 #define DA(QT, OT)                                                                                                  \
-    decode_attn_kernel<QT, OT><<<grid, 128, 0, ctx->stream>>>((const QT *)q, ldq, kc, vc, H, cap, pos_ptr, pos_off, \
-                                                             (OT *)out, ldo, ctx->scratch, ctx->counters)
-    if (q_half && out_half) DA(__half, __half);
-    else if (q_half) DA(__half, float);
-    else if (out_half) DA(float, __half);
-    else DA(float, float);
+    {                                                                                                               \
+        PREFER_SMEM_ONCE((decode_attn_kernel<QT, OT>));                                                             \
+        decode_attn_kernel<QT, OT><<<grid, 128, 0, ctx->stream>>>((const QT *)q, ldq, kc, vc, H, cap, pos_ptr,      \
+                                                                 pos_off, (OT *)out, ldo, ctx->scratch,            \
+                                                                 ctx->counters);                                   \
+    }
+    if (q_half && out_half) DA(__half, __half)
+    else if (q_half) DA(__half, float)
+    else if (out_half) DA(float, __half)
+    else DA(float, float)
 #undef DA
     CK_LAUNCH(ctx, "decode_attn_kernel");
     return B200NN_OK;
@@ -274,12 +278,15 @@ int launch_prefill_attention(b200nn_ctx *ctx, const void *q, bool q_half, int ld
     dim3 grid((S + 63) / 64, H, B);
     int ldo = H * 64;
 #define PA(QT, OT)                                                                                                \
-    prefill_attn_kernel<QT, OT><<<grid, 256, 0, ctx->stream>>>((const QT *)q, ldq, kc, vc, H, cap, S, past,        \
-                                                               (OT *)out, ldo)
-    if (q_half && out_half) PA(__half, __half);
-    else if (q_half) PA(__half, float);
-    else if (out_half) PA(float, __half);
-    else PA(float, float);
+    {                                                                                                             \
+        PREFER_SMEM_ONCE((prefill_attn_kernel<QT, OT>));                                                          \
+        prefill_attn_kernel<QT, OT><<<grid, 256, 0, ctx->stream>>>((const QT *)q, ldq, kc, vc, H, cap, S, past,    \
+                                                                   (OT *)out, ldo);                               \
+    }
+    if (q_half && out_half) PA(__half, __half)
+    else if (q_half) PA(__half, float)
+    else if (out_half) PA(float, __half)
+    else PA(float, float)
 #undef PA
     CK_LAUNCH(ctx, "prefill_attn_kernel");
     return B200NN_OK;

@@ -70,6 +70,26 @@ extern "C" int32_t b200nn_ctx_set_gemv_max_rows(b200nn_ctx *ctx, int32_t rows) {
     ctx->gemv_max_rows = rows < 0 ? 2 : rows;
     return B200NN_OK;
 }
+extern "C" int32_t b200nn_ctx_set_tuning(b200nn_ctx *ctx, const char *key, int32_t value) {
+    if (!ctx || !key) return B200NN_ERR_ARG;
+    if (!strcmp(key, "tc_mb")) ctx->tc_mb = value;
+    else if (!strcmp(key, "tc_splits")) ctx->tc_splits = value;
+    else if (!strcmp(key, "tc_min_kb")) ctx->tc_min_kb = value < 1 ? 1 : value;
+    else if (!strcmp(key, "trace")) { // value != 0: allocate (once) and clear a 256-slot stamp buffer
+        if (value && !ctx->trace && cudaMalloc(&ctx->trace, 256 * sizeof(long long)) != cudaSuccess) return B200NN_ERR_CUDA;
+        if (ctx->trace) cudaMemset(ctx->trace, 0, 256 * sizeof(long long));
+        if (!value && ctx->trace) { cudaFree(ctx->trace); ctx->trace = nullptr; }
+    }
+    else if (!strcmp(key, "gemv_max_rows")) ctx->gemv_max_rows = value < 0 ? 2 : value;
+    else return set_error(ctx, B200NN_ERR_UNSUPPORTED, std::string("unknown tuning key ") + key);
+    return B200NN_OK;
+}
+extern "C" int32_t b200nn_ctx_read_trace(b200nn_ctx *ctx, long long *out256) {
+    if (!ctx || !out256 || !ctx->trace) return B200NN_ERR_ARG;
+    CK(ctx, cudaStreamSynchronize(ctx->stream));
+    CK(ctx, cudaMemcpy(out256, ctx->trace, 256 * sizeof(long long), cudaMemcpyDeviceToHost));
+    return B200NN_OK;
+}
 extern "C" int32_t b200nn_ctx_device_error(b200nn_ctx *ctx, uint32_t *word_out) {
     if (!ctx || !word_out) return B200NN_ERR_ARG;
     CK(ctx, cudaSetDevice(ctx->device));

@@ -30,6 +30,8 @@ struct b200nn_ctx {
     unsigned *counters = nullptr; // arrival counters, self-resetting, zeroed at allocation
     size_t n_counters = 0;
     void *encode_tiled = nullptr; // cuTensorMapEncodeTiled, resolved through the runtime
+    int tc_mb = 0, tc_splits = 0, tc_min_kb = 4; // tensor-core GEMM tuning overrides (0 = automatic)
+    long long *trace = nullptr;   // optional device buffer for in-kernel time stamps (measurement aid)
     bool capturing = false;       // true while a decode step is being captured into a graph
 };
 
@@ -48,6 +50,23 @@ int ensure_scratch(b200nn_ctx *ctx, size_t bytes, size_t counters);
         (ctx)->launches++;                                                \
         cudaError_t _e = cudaPeekAtLastError();                           \
         if (_e != cudaSuccess) return set_cuda_error((ctx), _e, name);    \
+    } while (0)
+
+// Every kernel of the library asks for the largest shared-memory carve-out, so that consecutive
+// kernels of a decode step never make the SMs re-partition L1 / shared memory between launches
+// (the tensor-core GEMM needs ~100-180 KB of shared memory; a kernel that prefers L1 before or after
+// it costs a reconfiguration of several microseconds).  Call once per kernel function.
+template <typename Kernel>
+inline void prefer_max_smem(Kernel kern) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+#define PREFER_SMEM_ONCE(kern)                    \
+    do {                                          \
+        static bool _done = false;                \
+        if (!_done) {                             \
+            prefer_max_smem(kern);                \
+            _done = true;                         \
+        }                                         \
     } while (0)
 
 #define TRY(expr)                       \

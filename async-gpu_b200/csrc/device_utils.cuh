@@ -24,9 +24,8 @@ __device__ __forceinline__ float apply_act(float v, int act) {
     }
 }
 
-// Consumes one accumulated dot product for output row m (token) and column n (feature).
-__device__ __forceinline__ void epi_apply(const Epilogue &e, int m, int n, float acc) {
-    float v = acc + (e.bias ? e.bias[n] : 0.0f);
+// Consumes one finished output value v (bias already added) for row m (token), column n (feature).
+__device__ __forceinline__ void epi_store(const Epilogue &e, int m, int n, float v) {
     if (e.mode == EPI_RESID) {
         size_t i = (size_t)m * e.ldo + n;
         e.resid[i] += v;
@@ -51,6 +50,59 @@ __device__ __forceinline__ void epi_apply(const Epilogue &e, int m, int n, float
         static_cast<__half *>(e.out)[i] = __float2half_rn(v);
     else
         static_cast<float *>(e.out)[i] = v;
+}
+
+// Four consecutive columns n..n+3 (n % 4 == 0) of row m in one go: 16-byte (f32) or 8-byte (fp16)
+// stores when the destination allows it, element-wise otherwise.  pos_ptr must already be folded
+// into e.pos_off by the caller (it is not dereferenced here for the vector path).
+__device__ __forceinline__ void epi_store4(const Epilogue &e, int m, int n, float4 v, int N) {
+    const bool vec = (n + 3 < N) && ((e.ldo & 3) == 0) && (e.pos_ptr == nullptr);
+    if (!vec) {
+        if (n < N) epi_store(e, m, n, v.x);
+        if (n + 1 < N) epi_store(e, m, n + 1, v.y);
+        if (n + 2 < N) epi_store(e, m, n + 2, v.z);
+        if (n + 3 < N) epi_store(e, m, n + 3, v.w);
+        return;
+    }
+    if (e.mode == EPI_RESID) {
+        float4 *p = reinterpret_cast<float4 *>(e.resid + (size_t)m * e.ldo + n);
+        float4 r = *p;
+        r.x += v.x; r.y += v.y; r.z += v.z; r.w += v.w;
+        *p = r;
+        return;
+    }
+    if (e.mode == EPI_QKV && n >= e.d_model) {
+        int c = n - e.d_model;
+        __half *cache = e.kc;
+        if (c >= e.d_model) {
+            c -= e.d_model;
+            cache = e.vc;
+        }
+        const int head = c >> 6, el = c & 63;
+        const int b = m / e.rows_per_seq, s = m - b * e.rows_per_seq;
+        const int pos = e.pos_off + s;
+        if (pos < e.cap) {
+            __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+            uint2 u = make_uint2(*reinterpret_cast<uint32_t *>(&lo), *reinterpret_cast<uint32_t *>(&hi));
+            *reinterpret_cast<uint2 *>(cache + (((size_t)b * e.n_head + head) * e.cap + pos) * 64 + el) = u;
+        }
+        return;
+    }
+    v.x = apply_act(v.x, e.act); v.y = apply_act(v.y, e.act);
+    v.z = apply_act(v.z, e.act); v.w = apply_act(v.w, e.act);
+    const size_t i = (size_t)m * e.ldo + n;
+    if (e.out_half) {
+        __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+        *reinterpret_cast<uint2 *>(static_cast<__half *>(e.out) + i) =
+            make_uint2(*reinterpret_cast<uint32_t *>(&lo), *reinterpret_cast<uint32_t *>(&hi));
+    } else {
+        *reinterpret_cast<float4 *>(static_cast<float *>(e.out) + i) = v;
+    }
+}
+
+// Same, from a raw accumulated dot product.
+__device__ __forceinline__ void epi_apply(const Epilogue &e, int m, int n, float acc) {
+    epi_store(e, m, n, acc + (e.bias ? e.bias[n] : 0.0f));
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

@@ -138,6 +138,8 @@ int launch_int4_naive(b200nn_ctx *ctx, const Int4Weight &w, const void *x, bool 
     if (!w.ref_packed) return set_error(ctx, B200NN_ERR_UNSUPPORTED, "int4 weight has no reference-layout copy");
     size_t total = (size_t)M * w.N;
     int grid = (int)((total + 255) / 256);
+    PREFER_SMEM_ONCE(int4_naive_kernel<__half>);
+    PREFER_SMEM_ONCE(int4_naive_kernel<float>);
     if (x_half)
         int4_naive_kernel<__half><<<grid, 256, 0, ctx->stream>>>((const uint32_t *)w.ref_packed->p,
                                                                  (const float *)w.ref_scales->p, (const __half *)x, M,
@@ -164,6 +166,7 @@ static int gemv_chunk(b200nn_ctx *ctx, const Int4Weight &w, const XT *x, int m_v
     size_t smem = (size_t)MT * per * 64 * 4 + (size_t)MT * 128 * 4;
     if (splits > 1) TRY(ensure_scratch(ctx, (size_t)splits * MT * w.n_pad * 4, (size_t)w.n_tiles));
     dim3 grid(w.n_tiles, splits);
+    PREFER_SMEM_ONCE((int4_gemv_kernel<MT, XT>));
     int4_gemv_kernel<MT, XT><<<grid, 256, smem, ctx->stream>>>(
         (const uint4 *)w.tiled->p, (const __half *)w.scales_h->p, x, m_valid, m0, w.K, w.N, w.k_blocks, w.n_pad,
         w.group, per, epi, ctx->scratch, ctx->counters);

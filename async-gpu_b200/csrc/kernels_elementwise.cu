@@ -61,6 +61,8 @@ int launch_layernorm(b200nn_ctx *ctx, const float *x, const float *res_in, float
     if (d > 256 * 32) return set_error(ctx, B200NN_ERR_UNSUPPORTED, "layer_norm: d > 8192");
 #define LN_LAUNCH(V)                                                                                              \
     do {                                                                                                          \
+        PREFER_SMEM_ONCE((layernorm_kernel<V, __half>));                                                          \
+        PREFER_SMEM_ONCE((layernorm_kernel<V, float>));                                                           \
         if (out_half)                                                                                             \
             layernorm_kernel<V, __half><<<rows, 256, 0, ctx->stream>>>(x, res_in, sum_out, gamma, beta, eps, d,   \
                                                                       (__half *)out);                            \
@@ -97,6 +99,7 @@ __global__ void embedding_kernel(const uint32_t *__restrict__ ids, const float *
 int launch_embedding(b200nn_ctx *ctx, const uint32_t *ids, const float *wte, const float *wpe, int n_rows, int d,
                      int rows_per_seq, const int *pos_ptr, int pos_off, int vocab, int n_positions, float *out) {
     if (n_rows <= 0) return B200NN_OK;
+    PREFER_SMEM_ONCE(embedding_kernel);
     embedding_kernel<<<n_rows, 256, 0, ctx->stream>>>(ids, wte, wpe, d, rows_per_seq, pos_ptr, pos_off, vocab,
                                                       n_positions, out);
     CK_LAUNCH(ctx, "embedding_kernel");
@@ -135,30 +138,35 @@ static inline int grid_for(b200nn_ctx *ctx, size_t n, int block) {
 
 int launch_activation(b200nn_ctx *ctx, const float *x, float *y, size_t n, int act) {
     if (!n) return B200NN_OK;
+    PREFER_SMEM_ONCE(activation_kernel);
     activation_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(x, y, n, act);
     CK_LAUNCH(ctx, "activation_kernel");
     return B200NN_OK;
 }
 int launch_bias_add(b200nn_ctx *ctx, float *data, const float *bias, size_t total, int n_cols) {
     if (!total) return B200NN_OK;
+    PREFER_SMEM_ONCE(bias_add_kernel);
     bias_add_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(data, bias, total, n_cols);
     CK_LAUNCH(ctx, "bias_add_kernel");
     return B200NN_OK;
 }
 int launch_add(b200nn_ctx *ctx, float *a, const float *b, size_t n) {
     if (!n) return B200NN_OK;
+    PREFER_SMEM_ONCE(add_kernel);
     add_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(a, b, n);
     CK_LAUNCH(ctx, "add_kernel");
     return B200NN_OK;
 }
 int launch_f32_to_half(b200nn_ctx *ctx, const float *x, __half *y, size_t n) {
     if (!n) return B200NN_OK;
+    PREFER_SMEM_ONCE(f32_to_half_kernel);
     f32_to_half_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(x, y, n);
     CK_LAUNCH(ctx, "f32_to_half_kernel");
     return B200NN_OK;
 }
 int launch_half_to_f32(b200nn_ctx *ctx, const __half *x, float *y, size_t n) {
     if (!n) return B200NN_OK;
+    PREFER_SMEM_ONCE(half_to_f32_kernel);
     half_to_f32_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(x, y, n);
     CK_LAUNCH(ctx, "half_to_f32_kernel");
     return B200NN_OK;
@@ -196,6 +204,7 @@ __global__ void concat_heads_kernel(const float *__restrict__ heads, int seq, in
 int launch_split_qkv(b200nn_ctx *ctx, const float *qkv, int seq, int H, int dh, float *q, float *k, float *v) {
     size_t n = (size_t)seq * H * dh;
     if (!n) return B200NN_OK;
+    PREFER_SMEM_ONCE(split_qkv_kernel);
     split_qkv_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(qkv, seq, H, dh, q, k, v);
     CK_LAUNCH(ctx, "split_qkv_kernel");
     return B200NN_OK;
@@ -203,6 +212,7 @@ int launch_split_qkv(b200nn_ctx *ctx, const float *qkv, int seq, int H, int dh, 
 int launch_concat_heads(b200nn_ctx *ctx, const float *heads, int seq, int H, int dh, float *out) {
     size_t n = (size_t)seq * H * dh;
     if (!n) return B200NN_OK;
+    PREFER_SMEM_ONCE(concat_heads_kernel);
     concat_heads_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(heads, seq, H, dh, out);
     CK_LAUNCH(ctx, "concat_heads_kernel");
     return B200NN_OK;
@@ -215,6 +225,7 @@ __global__ void gather_last_rows_kernel(const float *__restrict__ src, int rows_
 }
 int launch_gather_last_rows(b200nn_ctx *ctx, const float *src, int n_seq, int rows_per_seq, int d, float *dst) {
     if (n_seq <= 0) return B200NN_OK;
+    PREFER_SMEM_ONCE(gather_last_rows_kernel);
     gather_last_rows_kernel<<<n_seq, 256, 0, ctx->stream>>>(src, rows_per_seq, d, dst);
     CK_LAUNCH(ctx, "gather_last_rows_kernel");
     return B200NN_OK;
@@ -234,6 +245,7 @@ __global__ void pack_kv_kernel(const float *__restrict__ src, int len, int cap, 
 int launch_pack_kv(b200nn_ctx *ctx, const float *src, int H, int len, int cap, __half *dst) {
     size_t n = (size_t)H * len * 64;
     if (!n) return B200NN_OK;
+    PREFER_SMEM_ONCE(pack_kv_kernel);
     pack_kv_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(src, len, cap, n, dst);
     CK_LAUNCH(ctx, "pack_kv_kernel");
     return B200NN_OK;
@@ -286,6 +298,7 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
 int launch_argmax(b200nn_ctx *ctx, const float *logits, int rows, int vocab, int ld, bool keep_last,
                   uint32_t *tok_out) {
     if (rows <= 0) return B200NN_OK;
+    PREFER_SMEM_ONCE(argmax_kernel);
     argmax_kernel<<<rows, 1024, 0, ctx->stream>>>(logits, vocab, ld, keep_last ? 1 : 0, tok_out);
     CK_LAUNCH(ctx, "argmax_kernel");
     return B200NN_OK;
@@ -306,6 +319,7 @@ __global__ void record_tokens_kernel(const uint32_t *__restrict__ tok, int rows,
 }
 int launch_record_tokens(b200nn_ctx *ctx, const uint32_t *tok, int rows, uint32_t *history, int hist_cap,
                          int *step_ptr, int *pos_ptr) {
+    PREFER_SMEM_ONCE(record_tokens_kernel);
     record_tokens_kernel<<<1, 256, 0, ctx->stream>>>(tok, rows, history, hist_cap, step_ptr, pos_ptr);
     CK_LAUNCH(ctx, "record_tokens_kernel");
     return B200NN_OK;

@@ -135,6 +135,7 @@ static int f32_gemv_chunk(b200nn_ctx *ctx, const F32Weight &w, const XT *x, int 
     splits = (w.K + per - 1) / per;
     if (splits > 1) TRY(ensure_scratch(ctx, (size_t)splits * MT * w.N * 4, (size_t)col_blocks));
     dim3 grid(col_blocks, splits);
+    PREFER_SMEM_ONCE((f32_gemv_kernel<MT, XT>));
     f32_gemv_kernel<MT, XT><<<grid, 256, (size_t)MT * per * 4, ctx->stream>>>(
         (const float *)w.w_kn->p, x, m_valid, m0, w.K, w.N, per, epi, ctx->scratch, ctx->counters);
     CK_LAUNCH(ctx, "f32_gemv_kernel");
@@ -153,6 +154,7 @@ static int f32_linear_t(b200nn_ctx *ctx, const F32Weight &w, const XT *x, int M,
         return f32_gemv_chunk<1, XT>(ctx, w, x, 1, 0, epi);
     }
     dim3 grid((w.N + 63) / 64, (M + 63) / 64);
+    PREFER_SMEM_ONCE(f32_gemm_kernel<XT>);
     f32_gemm_kernel<XT><<<grid, 256, 0, ctx->stream>>>((const float *)w.w_kn->p, x, M, w.K, w.N, epi);
     CK_LAUNCH(ctx, "f32_gemm_kernel");
     return B200NN_OK;

@@ -7,6 +7,18 @@ namespace tc {
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+// One lane of the (converged) warp is chosen; the compiler treats the guarded region as run by a
+// single thread, which lets warp-uniform operands stay in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 // ---- mbarrier ---------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -30,6 +42,20 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Blocking form: the hardware parks the thread until the phase completes or an internal time
+// limit passes (no issue slots are burnt while parked, unlike a test_wait spin loop).
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Bounded wait.  Gives up after WAIT_CYCLES clock cycles (about a second), or as soon as another
 // thread of the block has given up; the caller then leaves its loop and the block tears down
 // normally.  `code` identifies the wait in the device error word.  The result is made uniform
@@ -40,20 +66,32 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     bool ok = mbar_test(bar, parity);
     if (!ok) {
         const long long t0 = clock64();
-        uint32_t spins = 0;
-        while (!(ok = mbar_test(bar, parity))) {
-            if ((++spins & 63u) == 0) {
-                if (*abort_flag) break;
-                if (clock64() - t0 > WAIT_CYCLES) {
-                    *abort_flag = 1;
-                    atomicCAS(dev_err, 0u, code);
-                    break;
-                }
-                __nanosleep(20);
+        while (!(ok = mbar_try(bar, parity))) { // each failed try has already waited the hardware's time slice
+            if (*abort_flag) break;
+            if (clock64() - t0 > WAIT_CYCLES) {
+                *abort_flag = 1;
+                atomicCAS(dev_err, 0u, code);
+                break;
             }
         }
     }
     return __all_sync(0xffffffffu, ok);
+}
+
+// Single-thread form of the bounded wait (no warp vote): for roles run by one elected lane.
+__device__ __forceinline__ bool mbar_wait1(uint32_t bar, uint32_t parity, volatile int *abort_flag, uint32_t *dev_err,
+                                           uint32_t code) {
+    if (mbar_test(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try(bar, parity)) {
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_CYCLES) {
+            *abort_flag = 1;
+            atomicCAS(dev_err, 0u, code);
+            return false;
+        }
+    }
+    return true;
 }
 
 // ---- proxies / fences -------------------------------------------------------------------------
@@ -121,6 +159,29 @@ __device__ __forceinline__ void umma_f16_ss(uint32_t d_tmem, uint64_t a_desc, ui
         : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (128 rows = TMEM lanes, 16 fp16 along K packed two
+// per 32-bit column, i.e. 8 columns) is read from tensor memory.
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        :
+        : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// registers -> TMEM: this warp's 32 lanes x 16 consecutive 32-bit columns starting at taddr
+__device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16};"
+        :
+        : "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // Arrives once on the mbarrier when every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");

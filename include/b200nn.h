@@ -86,6 +86,13 @@ B200NN_API uint64_t b200nn_ctx_launch_count(b200nn_ctx *ctx);
 /* Linear layers with at most this many input rows take the CUDA-core GEMV; more rows take the
  * tcgen05 GEMM.  Negative restores the default. */
 B200NN_API int32_t b200nn_ctx_set_gemv_max_rows(b200nn_ctx *ctx, int32_t rows);
+/* Tuning overrides of the tensor-core GEMM's launch policy, for measurements: "tc_mb" (cap of the
+ * token-tile width: 16..256, 0 = default), "tc_splits" (K splits, 0 = automatic), "tc_min_kb"
+ * (fewest 64-wide K blocks per split), "gemv_max_rows". */
+B200NN_API int32_t b200nn_ctx_set_tuning(b200nn_ctx *ctx, const char *key, int32_t value);
+/* Measurement aid: after set_tuning("trace", 1) the first block of the next tensor-core GEMM
+ * writes SM-clock stamps of its pipeline events into a 256-slot buffer; this copies it out. */
+B200NN_API int32_t b200nn_ctx_read_trace(b200nn_ctx *ctx, long long *out256);
 
 /* ---- GpuTensor (GH/nn/tensor.rs:45-110, 201-221, 270) -------------------------------------- */
 B200NN_API int32_t b200nn_tensor_from_host(b200nn_ctx *ctx, const float *host, const size_t *shape, int32_t ndim,

@@ -37,6 +37,8 @@ decode_attn_kernel(const QT *__restrict__ q, int ldq, const __half *__restrict__
     __shared__ int is_last;
     const int h = blockIdx.x, b = blockIdx.y, split = blockIdx.z, n_splits = gridDim.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 3, c = lane & 7;
+    pdl_trigger();
+    pdl_wait();
     int ctx = (pos_ptr ? *pos_ptr : 0) + pos_off + 1;
     if (ctx > cap) ctx = cap;
     int chunk = (((ctx + n_splits - 1) / n_splits) + 15) & ~15;
@@ -160,9 +162,8 @@ int launch_decode_attention(b200nn_ctx *ctx, const void *q, bool q_half, int ldq
 #define DA(QT, OT)                                                                                                  \
     {                                                                                                               \
         PREFER_SMEM_ONCE((decode_attn_kernel<QT, OT>));                                                             \
-        decode_attn_kernel<QT, OT><<<grid, 128, 0, ctx->stream>>>((const QT *)q, ldq, kc, vc, H, cap, pos_ptr,      \
-                                                                 pos_off, (OT *)out, ldo, ctx->scratch,            \
-                                                                 ctx->counters);                                   \
+        launch_pdl(ctx, decode_attn_kernel<QT, OT>, grid, dim3(128), 0, (const QT *)q, ldq, kc, vc, H, cap, pos_ptr, \
+                   pos_off, (OT *)out, ldo, ctx->scratch, ctx->counters);                                           \
     }
     if (q_half && out_half) DA(__half, __half)
     else if (q_half) DA(__half, float)

@@ -75,6 +75,7 @@ extern "C" int32_t b200nn_ctx_set_tuning(b200nn_ctx *ctx, const char *key, int32
     if (!strcmp(key, "tc_mb")) ctx->tc_mb = value;
     else if (!strcmp(key, "tc_splits")) ctx->tc_splits = value;
     else if (!strcmp(key, "tc_min_kb")) ctx->tc_min_kb = value < 1 ? 1 : value;
+    else if (!strcmp(key, "pdl")) ctx->pdl = value ? 1 : 0;
     else if (!strcmp(key, "trace")) { // value != 0: allocate (once) and clear a 256-slot stamp buffer
         if (value && !ctx->trace && cudaMalloc(&ctx->trace, 256 * sizeof(long long)) != cudaSuccess) return B200NN_ERR_CUDA;
         if (ctx->trace) cudaMemset(ctx->trace, 0, 256 * sizeof(long long));

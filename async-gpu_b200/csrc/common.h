@@ -32,6 +32,7 @@ struct b200nn_ctx {
     void *encode_tiled = nullptr; // cuTensorMapEncodeTiled, resolved through the runtime
     int tc_mb = 0, tc_splits = 0, tc_min_kb = 4; // tensor-core GEMM tuning overrides (0 = automatic)
     long long *trace = nullptr;   // optional device buffer for in-kernel time stamps (measurement aid)
+    int pdl = 1;                  // launch the decode-step kernels with programmatic dependent launch
     bool capturing = false;       // true while a decode step is being captured into a graph
 };
 
@@ -68,6 +69,25 @@ inline void prefer_max_smem(Kernel kern) {
             _done = true;                         \
         }                                         \
     } while (0)
+
+// Launch with programmatic dependent launch allowed: the kernel may start while its predecessor
+// on the stream is still running and must execute pdl_wait() (griddepcontrol.wait) before it reads
+// or writes anything the predecessor touches.  Only kernels that do so are launched this way.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(b200nn_ctx *ctx, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 #define TRY(expr)                       \
     do {                                \

@@ -2,6 +2,12 @@
 #pragma once
 #include "common.h"
 
+// Programmatic dependent launch: wait until the preceding kernel on the stream has completed and
+// its writes are visible (a no-op when the kernel was not launched as a programmatic dependent),
+// and allow the following kernel to begin launching.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float gelu_tanh_f(float x) {
     // x*0.5*(1+tanh(sqrt(2/pi)*(x+0.044715x^3))): the GPT-2 form used by the reference's CPU model
     // (crates/test/gpu-test-harness/src/tests_inference.rs:3680-3685).

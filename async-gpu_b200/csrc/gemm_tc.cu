@@ -81,6 +81,7 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
     const int kb0 = split * kb_per_split;
     const int nkb = min(kb_per_split, k_blocks - kb0);
     if (tid == 0) TRACE(0);
+    pdl_trigger(); // the next kernel may start its own prologue / weight prefetch
 
     // carve shared memory: rings 1024-byte aligned, barriers and group scales behind them
     const uint32_t base = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -141,6 +142,7 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
         //      bytes are expected on the same barrier the dequant warps arrive on ----
         int s = 0, kx = kb0 * TILE_K;
         uint32_t ph = 1;
+        pdl_wait(); // the activations are the previous kernel's output
         for (int i = 0; i < nkb; ++i) {
             if (i >= NS && !tc::mbar_wait(S.ax_empty + 8 * s, ph, &abort_flag, dev_err, ERR_X_EMPTY)) break;
             if (tc::elect_one()) {
@@ -229,6 +231,7 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
             if (dw_lane0) tc::mbar_arrive(S.a_full + 8 * sa);
             if (t == 0 && i < 32) TRACE(128 + i);
         }
+        pdl_wait(); // the epilogue touches buffers the previous kernel may still be using
         bar_sync_dequant<DQ>();
         if (!abort_flag) tc::mbar_wait(S.acc_full, 0, &abort_flag, dev_err, ERR_ACC);
         bar_sync_dequant<DQ>();
@@ -274,6 +277,27 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
             if (splits == 1) {
                 for (int c = w8; c < rows; c += NW)
                     epi_store4(e2, mt * MB + c, n4, f4_add(stage4[c * 32 + lane], b4), N);
+            } else if (epi.mode == EPI_RESID) {
+                // residual epilogue with split K: every split adds its partial tile straight into the
+                // f32 residual stream with vector reductions at L2 (no scratch, no second pass); the
+                // bias goes in with split 0.  The order in which the splits' partials are added is not
+                // fixed, so the last bits of the sum can differ between runs.
+                const float4 add0 = (split == 0) ? b4 : make_float4(0.f, 0.f, 0.f, 0.f);
+                const bool vec = (n4 + 3 < N) && ((epi.ldo & 3) == 0);
+                for (int c = w8; c < rows; c += NW) {
+                    const float4 v = f4_add(stage4[c * 32 + lane], add0);
+                    float *dst = epi.resid + (size_t)(mt * MB + c) * epi.ldo + n4;
+                    if (vec) {
+                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v.x), "f"(v.y),
+                                     "f"(v.z), "f"(v.w)
+                                     : "memory");
+                    } else {
+                        if (n4 < N) atomicAdd(dst, v.x);
+                        if (n4 + 1 < N) atomicAdd(dst + 1, v.y);
+                        if (n4 + 2 < N) atomicAdd(dst + 2, v.z);
+                        if (n4 + 3 < N) atomicAdd(dst + 3, v.w);
+                    }
+                }
             } else {
                 float4 *part4 = reinterpret_cast<float4 *>(scratch + (((size_t)tile_lin * splits + split) * MB) * TILE_N);
                 for (int c = w8; c < rows; c += NW) part4[c * 32 + lane] = stage4[c * 32 + lane];
@@ -351,20 +375,28 @@ int launch_cfg(b200nn_ctx *ctx, const Int4Weight &w, const __half *x, int M, con
     const int m_tiles = (M + MB - 1) / MB;
     const int base_ctas = w.n_tiles * m_tiles;
     const int ctas_per_sm = (smem <= 113 * 1024 && 2 * TC <= 512) ? 2 : 1;
-    int splits = (ctx->sm_count * ctas_per_sm + base_ctas - 1) / base_ctas;
-    splits = std::min(splits, std::max(1, w.k_blocks / ctx->tc_min_kb)); // at least tc_min_kb K blocks per split
+    // K split: fills the GPU when there are few (feature tile x token tile) pairs.  The residual
+    // epilogue reduces its splits with L2 vector adds, which is cheap, so it splits down to
+    // tc_min_kb K blocks per block; the other epilogues pay a second pass by the last block and
+    // split only when fewer than a quarter of the SMs would otherwise have work.
+    const int target = ctx->sm_count * ctas_per_sm;
+    int splits = 1;
+    if (epi.mode == EPI_RESID)
+        splits = std::min((target + base_ctas - 1) / base_ctas, std::max(1, w.k_blocks / ctx->tc_min_kb));
+    else if (base_ctas * 4 <= target)
+        splits = std::min(target / (2 * base_ctas), std::max(1, w.k_blocks / (2 * ctx->tc_min_kb)));
     splits = std::max(1, std::min(splits, 32));
     if (ctx->tc_splits > 0) splits = std::min(ctx->tc_splits, w.k_blocks);
     int per = (w.k_blocks + splits - 1) / splits;
     const int per_max = std::max(1, (kMaxScaleGroups - 2) * w.group / TILE_K); // scales must fit their buffer
     per = std::min(per, per_max);
     splits = (w.k_blocks + per - 1) / per;
-    if (splits > 1)
+    if (splits > 1 && epi.mode != EPI_RESID)
         TRY(ensure_scratch(ctx, (size_t)base_ctas * splits * MB * TILE_N * sizeof(float), (size_t)base_ctas));
     dim3 grid(w.n_tiles, splits, m_tiles);
-    kern<<<grid, 96 + 128 * NG, smem, ctx->stream>>>((const uint8_t *)w.tiled->p, (const __half *)w.scales_h->p, tmap, M,
-                                                     w.N, w.k_blocks, w.n_pad, w.group, per, epi, ctx->scratch,
-                                                     ctx->counters, ctx->dev_err, ctx->trace);
+    CK(ctx, launch_pdl(ctx, kern, grid, dim3(96 + 128 * NG), smem, (const uint8_t *)w.tiled->p,
+                       (const __half *)w.scales_h->p, tmap, M, w.N, w.k_blocks, w.n_pad, w.group, per, epi, ctx->scratch,
+                       ctx->counters, ctx->dev_err, ctx->trace));
     CK_LAUNCH(ctx, "int4_gemm_tc_kernel");
     return B200NN_OK;
 }

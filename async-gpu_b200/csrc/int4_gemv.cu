@@ -24,6 +24,8 @@ int4_gemv_kernel(const uint4 *__restrict__ tiles, const __half *__restrict__ sca
     const int kb1 = min(kb0 + kb_per_split, k_blocks);
     const int len = kb_per_split * 64;
     const int n = nt * TILE_N + r;
+    pdl_trigger();
+    pdl_wait();
 
     for (int i = tid; i < MT * len; i += 256) {
         int m = i / len, kk = i - m * len;
@@ -167,9 +169,9 @@ static int gemv_chunk(b200nn_ctx *ctx, const Int4Weight &w, const XT *x, int m_v
     if (splits > 1) TRY(ensure_scratch(ctx, (size_t)splits * MT * w.n_pad * 4, (size_t)w.n_tiles));
     dim3 grid(w.n_tiles, splits);
     PREFER_SMEM_ONCE((int4_gemv_kernel<MT, XT>));
-    int4_gemv_kernel<MT, XT><<<grid, 256, smem, ctx->stream>>>(
-        (const uint4 *)w.tiled->p, (const __half *)w.scales_h->p, x, m_valid, m0, w.K, w.N, w.k_blocks, w.n_pad,
-        w.group, per, epi, ctx->scratch, ctx->counters);
+    launch_pdl(ctx, int4_gemv_kernel<MT, XT>, grid, dim3(256), smem, (const uint4 *)w.tiled->p,
+               (const __half *)w.scales_h->p, x, m_valid, m0, w.K, w.N, w.k_blocks, w.n_pad, w.group, per, epi, ctx->scratch,
+               ctx->counters);
     CK_LAUNCH(ctx, "int4_gemv_kernel");
     return B200NN_OK;
 }

@@ -16,6 +16,8 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const float *__restrict_
                                                         TOut *__restrict__ out) {
     __shared__ float red[32];
     const int row = blockIdx.x, tid = threadIdx.x;
+    pdl_trigger();
+    pdl_wait();
     const float *xr = x + (size_t)row * d;
     const float *rr = res_in ? res_in + (size_t)row * d : nullptr;
     float v[VPT];
@@ -64,11 +66,11 @@ int launch_layernorm(b200nn_ctx *ctx, const float *x, const float *res_in, float
         PREFER_SMEM_ONCE((layernorm_kernel<V, __half>));                                                          \
         PREFER_SMEM_ONCE((layernorm_kernel<V, float>));                                                           \
         if (out_half)                                                                                             \
-            layernorm_kernel<V, __half><<<rows, 256, 0, ctx->stream>>>(x, res_in, sum_out, gamma, beta, eps, d,   \
-                                                                      (__half *)out);                            \
+            launch_pdl(ctx, layernorm_kernel<V, __half>, dim3(rows), dim3(256), 0, x, res_in, sum_out, gamma,    \
+                       beta, eps, d, (__half *)out);                                                             \
         else                                                                                                      \
-            layernorm_kernel<V, float><<<rows, 256, 0, ctx->stream>>>(x, res_in, sum_out, gamma, beta, eps, d,    \
-                                                                     (float *)out);                              \
+            launch_pdl(ctx, layernorm_kernel<V, float>, dim3(rows), dim3(256), 0, x, res_in, sum_out, gamma,     \
+                       beta, eps, d, (float *)out);                                                              \
     } while (0)
     int vpt = (d + 255) / 256;
     if (vpt <= 4) LN_LAUNCH(4);
@@ -88,6 +90,8 @@ __global__ void embedding_kernel(const uint32_t *__restrict__ ids, const float *
                                  const float *__restrict__ wpe, int d, int rows_per_seq, const int *pos_ptr,
                                  int pos_off, int vocab, int n_positions, float *__restrict__ out) {
     int r = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
     uint32_t tok = ids[r];
     if (tok >= (uint32_t)vocab) tok = vocab - 1; // ids are validated on the host; never read out of range
     int pos = (pos_ptr ? *pos_ptr : 0) + pos_off + r % rows_per_seq;
@@ -100,8 +104,8 @@ int launch_embedding(b200nn_ctx *ctx, const uint32_t *ids, const float *wte, con
                      int rows_per_seq, const int *pos_ptr, int pos_off, int vocab, int n_positions, float *out) {
     if (n_rows <= 0) return B200NN_OK;
     PREFER_SMEM_ONCE(embedding_kernel);
-    embedding_kernel<<<n_rows, 256, 0, ctx->stream>>>(ids, wte, wpe, d, rows_per_seq, pos_ptr, pos_off, vocab,
-                                                      n_positions, out);
+    launch_pdl(ctx, embedding_kernel, dim3(n_rows), dim3(256), 0, ids, wte, wpe, d, rows_per_seq, pos_ptr, pos_off, vocab,
+               n_positions, out);
     CK_LAUNCH(ctx, "embedding_kernel");
     return B200NN_OK;
 }
@@ -260,6 +264,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
                                                       int keep_last, uint32_t *__restrict__ tok_out) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    pdl_trigger();
+    pdl_wait();
     const float *row = logits + (size_t)blockIdx.x * ld;
     float best = -INFINITY;
     int bi = keep_last ? -1 : 0x7fffffff;
@@ -299,7 +305,7 @@ int launch_argmax(b200nn_ctx *ctx, const float *logits, int rows, int vocab, int
                   uint32_t *tok_out) {
     if (rows <= 0) return B200NN_OK;
     PREFER_SMEM_ONCE(argmax_kernel);
-    argmax_kernel<<<rows, 1024, 0, ctx->stream>>>(logits, vocab, ld, keep_last ? 1 : 0, tok_out);
+    launch_pdl(ctx, argmax_kernel, dim3(rows), dim3(1024), 0, logits, vocab, ld, keep_last ? 1 : 0, tok_out);
     CK_LAUNCH(ctx, "argmax_kernel");
     return B200NN_OK;
 }
@@ -308,6 +314,8 @@ int launch_argmax(b200nn_ctx *ctx, const float *logits, int rows, int vocab, int
 // counters that the next step's kernels read (single block, so the increment is ordered).
 __global__ void record_tokens_kernel(const uint32_t *__restrict__ tok, int rows, uint32_t *__restrict__ history,
                                      int hist_cap, int *step_ptr, int *pos_ptr) {
+    pdl_trigger();
+    pdl_wait();
     int step = *step_ptr;
     for (int r = threadIdx.x; r < rows; r += blockDim.x)
         if (step < hist_cap) history[(size_t)r * hist_cap + step] = tok[r];
@@ -320,7 +328,7 @@ __global__ void record_tokens_kernel(const uint32_t *__restrict__ tok, int rows,
 int launch_record_tokens(b200nn_ctx *ctx, const uint32_t *tok, int rows, uint32_t *history, int hist_cap,
                          int *step_ptr, int *pos_ptr) {
     PREFER_SMEM_ONCE(record_tokens_kernel);
-    record_tokens_kernel<<<1, 256, 0, ctx->stream>>>(tok, rows, history, hist_cap, step_ptr, pos_ptr);
+    launch_pdl(ctx, record_tokens_kernel, dim3(1), dim3(256), 0, tok, rows, history, hist_cap, step_ptr, pos_ptr);
     CK_LAUNCH(ctx, "record_tokens_kernel");
     return B200NN_OK;
 }

@@ -130,6 +130,7 @@ def load_library() -> C.CDLL:
             "b200nn_session_rewind": (i32, [vp, sz]), "b200nn_session_position": (sz, [vp]),
             "b200nn_session_tokens": (i32, [vp, _u32p, sz, szp]), "b200nn_session_logits": (i32, [vp, _f32p]),
             "b200nn_session_profile_step": (i32, [vp, _f32p, C.POINTER(C.c_uint64)]),
+            "b200nn_session_time_family": (i32, [vp, i32, i32, _f32p, C.POINTER(C.c_uint64)]),
             "b200nn_session_destroy": (None, [vp]),
         }
         for name, (res, args) in sig.items():

@@ -239,6 +239,14 @@ class DecodeSession:
         self.reg.check(self.reg.lib.b200nn_session_profile_step(self.h, t, C.byref(b)))
         return {n: float(t[i]) for i, n in enumerate(PROF_NAMES)}, int(b.value)
 
+    def time_family(self, family: str, reps: int = 3):
+        """(milliseconds, launches) of one kernel family run alone `reps` times; prefill again afterwards."""
+        ms = C.c_float()
+        n = C.c_uint64()
+        self.reg.check(self.reg.lib.b200nn_session_time_family(self.h, PROF_NAMES.index(family), reps, C.byref(ms),
+                                                               C.byref(n)))
+        return float(ms.value), int(n.value)
+
     def __del__(self):
         try:
             if self.h and self.model.h and self.reg.h:

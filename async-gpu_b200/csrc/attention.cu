@@ -28,7 +28,7 @@ __device__ __forceinline__ void half8_to_float(const uint4 &u, float (&f)[8]) {
 }
 
 template <typename QT, typename OT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 6)
 decode_attn_kernel(const QT *__restrict__ q, int ldq, const __half *__restrict__ kc, const __half *__restrict__ vc,
                    int H, int cap, const int *__restrict__ pos_ptr, int pos_off, OT *__restrict__ out, int ldo,
                    float *__restrict__ scratch, unsigned *__restrict__ counters) {
@@ -57,37 +57,54 @@ decode_attn_kernel(const QT *__restrict__ q, int ldq, const __half *__restrict__
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
 
-    for (int jw = p0 + warp * 4; jw < p1; jw += 32) { // warp-uniform trip count (full-mask shuffles)
-        // two rows per trip: jw+g and jw+g+16 (loads issued before any math)
-        const int ja = jw + g, jb = ja + 16;
-        const bool va = ja < p1, vb = jb < p1;
-        uint4 ka = make_uint4(0, 0, 0, 0), kb = ka, wa = ka, wb = ka;
-        if (va) { ka = kp[(size_t)ja * 8 + c]; wa = vp[(size_t)ja * 8 + c]; }
-        if (vb) { kb = kp[(size_t)jb * 8 + c]; wb = vp[(size_t)jb * 8 + c]; }
-        float kf[8], sa = 0.0f, sb = 0.0f;
-        half8_to_float(ka, kf);
+    constexpr int R = 4; // rows per lane group per trip: R x (K + V) 16-byte loads in flight per thread
+    for (int jw = p0 + warp * 4; jw < p1; jw += 16 * R) { // warp-uniform trip count (full-mask shuffles)
+        // rows jw+g, jw+g+16, ...: all loads are issued before any math
+        uint4 kr[R], vr[R];
+        bool valid[R];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sa = fmaf(qf[i], kf[i], sa);
-        half8_to_float(kb, kf);
+        for (int r = 0; r < R; ++r) {
+            const int j = jw + g + 16 * r;
+            valid[r] = j < p1;
+            kr[r] = make_uint4(0, 0, 0, 0);
+            vr[r] = kr[r];
+            if (valid[r]) {
+                kr[r] = __ldg(kp + (size_t)j * 8 + c);
+                vr[r] = __ldg(vp + (size_t)j * 8 + c);
+            }
+        }
+        float sc[R];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sb = fmaf(qf[i], kf[i], sb);
+        for (int r = 0; r < R; ++r) {
+            float kf[8];
+            half8_to_float(kr[r], kf);
+            float t = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) t = fmaf(qf[i], kf[i], t);
+            sc[r] = t;
+        }
 #pragma unroll
         for (int o = 1; o < 8; o <<= 1) {
-            sa += __shfl_xor_sync(0xffffffffu, sa, o);
-            sb += __shfl_xor_sync(0xffffffffu, sb, o);
+#pragma unroll
+            for (int r = 0; r < R; ++r) sc[r] += __shfl_xor_sync(0xffffffffu, sc[r], o);
         }
         float m_new = m;
-        if (va) m_new = fmaxf(m_new, sa);
-        if (vb) m_new = fmaxf(m_new, sb);
-        float corr = exp2f(m - m_new);
-        float pa = va ? exp2f(sa - m_new) : 0.0f;
-        float pb = vb ? exp2f(sb - m_new) : 0.0f;
-        l = l * corr + pa + pb;
-        float vf[8], uf[8];
-        half8_to_float(wa, vf);
-        half8_to_float(wb, uf);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = fmaf(pb, uf[i], fmaf(pa, vf[i], acc[i] * corr));
+        for (int r = 0; r < R; ++r)
+            if (valid[r]) m_new = fmaxf(m_new, sc[r]);
+        const float corr = exp2f(m - m_new);
+        l *= corr;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] *= corr;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const float p = valid[r] ? exp2f(sc[r] - m_new) : 0.0f;
+            l += p;
+            float vf[8];
+            half8_to_float(vr[r], vf);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = fmaf(p, vf[i], acc[i]);
+        }
         m = m_new;
     }
 

@@ -32,6 +32,7 @@ struct b200nn_ctx {
     void *encode_tiled = nullptr; // cuTensorMapEncodeTiled, resolved through the runtime
     int tc_mb = 0, tc_splits = 0, tc_min_kb = 4; // tensor-core GEMM tuning overrides (0 = automatic)
     long long *trace = nullptr;   // optional device buffer for in-kernel time stamps (measurement aid)
+    uint32_t fam_mask = 0xffffffffu; // kernel families run_blocks / run_head launch (timing aid)
     int pdl = 1;                  // launch the decode-step kernels with programmatic dependent launch
     bool capturing = false;       // true while a decode step is being captured into a graph
 };

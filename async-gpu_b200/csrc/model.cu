@@ -187,7 +187,7 @@ int run_blocks(b200nn_gpt2 *m, Workspace &ws, b200nn_kvcache &kv, int B, int S, 
     float *x = (float *)ws.x->p;
     for (int l = 0; l < m->cfg.n_layer; ++l) {
         const BlockW &b = m->blocks[l];
-        TRY(launch_layernorm(ctx, x, nullptr, nullptr, (const float *)b.ln1_g->p, (const float *)b.ln1_b->p,
+        if (ctx->fam_mask & (1u << B200NN_PROF_LAYERNORM)) TRY(launch_layernorm(ctx, x, nullptr, nullptr, (const float *)b.ln1_g->p, (const float *)b.ln1_b->p,
                              m->cfg.layer_norm_epsilon, T, d, ws.ln->p, act_half));
         prof_mark(ctx, prof, B200NN_PROF_LAYERNORM);
         Epilogue e;
@@ -203,9 +203,10 @@ int run_blocks(b200nn_gpt2 *m, Workspace &ws, b200nn_kvcache &kv, int B, int S, 
         e.cap = (int)kv.cap;
         e.pos_ptr = pos_ptr;
         e.pos_off = pos_off;
-        TRY(linear_forward(ctx, b.qkv, ws.ln->p, act_half, T, e));
+        if (ctx->fam_mask & (1u << B200NN_PROF_LINEAR)) TRY(linear_forward(ctx, b.qkv, ws.ln->p, act_half, T, e));
         prof_mark(ctx, prof, B200NN_PROF_LINEAR);
-        if (S == 1)
+        if (!(ctx->fam_mask & (1u << B200NN_PROF_ATTENTION))) {
+        } else if (S == 1)
             TRY(launch_decode_attention(ctx, ws.q->p, act_half, d, kv.kl(l), kv.vl(l), B, H, (int)kv.cap, pos_ptr,
                                         pos_off, ws.att->p, act_half, (int)kv.cap));
         else
@@ -216,9 +217,9 @@ int run_blocks(b200nn_gpt2 *m, Workspace &ws, b200nn_kvcache &kv, int B, int S, 
         r.mode = EPI_RESID;
         r.resid = x;
         r.ldo = d;
-        TRY(linear_forward(ctx, b.proj, ws.att->p, act_half, T, r));
+        if (ctx->fam_mask & (1u << B200NN_PROF_LINEAR)) TRY(linear_forward(ctx, b.proj, ws.att->p, act_half, T, r));
         prof_mark(ctx, prof, B200NN_PROF_LINEAR);
-        TRY(launch_layernorm(ctx, x, nullptr, nullptr, (const float *)b.ln2_g->p, (const float *)b.ln2_b->p,
+        if (ctx->fam_mask & (1u << B200NN_PROF_LAYERNORM)) TRY(launch_layernorm(ctx, x, nullptr, nullptr, (const float *)b.ln2_g->p, (const float *)b.ln2_b->p,
                              m->cfg.layer_norm_epsilon, T, d, ws.ln->p, act_half));
         prof_mark(ctx, prof, B200NN_PROF_LAYERNORM);
         Epilogue f;
@@ -227,9 +228,9 @@ int run_blocks(b200nn_gpt2 *m, Workspace &ws, b200nn_kvcache &kv, int B, int S, 
         f.out = ws.fc->p;
         f.ldo = 4 * d;
         f.out_half = act_half;
-        TRY(linear_forward(ctx, b.fc, ws.ln->p, act_half, T, f));
+        if (ctx->fam_mask & (1u << B200NN_PROF_LINEAR)) TRY(linear_forward(ctx, b.fc, ws.ln->p, act_half, T, f));
         prof_mark(ctx, prof, B200NN_PROF_LINEAR);
-        TRY(linear_forward(ctx, b.fcproj, ws.fc->p, act_half, T, r));
+        if (ctx->fam_mask & (1u << B200NN_PROF_LINEAR)) TRY(linear_forward(ctx, b.fcproj, ws.fc->p, act_half, T, r));
         prof_mark(ctx, prof, B200NN_PROF_LINEAR);
     }
     return B200NN_OK;
@@ -239,14 +240,14 @@ int run_head(b200nn_gpt2 *m, Workspace &ws, const float *x, int rows, bool act_h
     b200nn_ctx *ctx = m->ctx;
     const int d = m->cfg.n_embd, V = m->cfg.vocab_size;
     bool head_half = act_half && m->lm_head.int4 && int4_gemm_tc_supported(m->lm_head.q, rows);
-    TRY(launch_layernorm(ctx, x, nullptr, nullptr, (const float *)m->lnf_g->p, (const float *)m->lnf_b->p,
+    if (ctx->fam_mask & (1u << B200NN_PROF_LAYERNORM)) TRY(launch_layernorm(ctx, x, nullptr, nullptr, (const float *)m->lnf_g->p, (const float *)m->lnf_b->p,
                          m->cfg.layer_norm_epsilon, rows, d, ws.last_ln->p, head_half));
     prof_mark(ctx, prof, B200NN_PROF_LAYERNORM);
     Epilogue e;
     e.mode = EPI_STORE;
     e.out = ws.logits->p;
     e.ldo = V;
-    TRY(linear_forward(ctx, m->lm_head, ws.last_ln->p, head_half, rows, e));
+    if (ctx->fam_mask & (1u << B200NN_PROF_LM_HEAD)) TRY(linear_forward(ctx, m->lm_head, ws.last_ln->p, head_half, rows, e));
     prof_mark(ctx, prof, B200NN_PROF_LM_HEAD);
     return B200NN_OK;
 }

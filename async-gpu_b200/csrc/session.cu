@@ -358,6 +358,47 @@ extern "C" int32_t b200nn_session_profile_step(b200nn_session *s, float *times_m
     return B200NN_OK;
 }
 
+extern "C" int32_t b200nn_session_time_family(b200nn_session *s, int32_t family, int32_t reps, float *ms_total,
+                                              uint64_t *launches) {
+    if (!s || !ms_total || reps <= 0) return B200NN_ERR_ARG;
+    b200nn_gpt2 *m = s->m;
+    b200nn_ctx *ctx = m->ctx;
+    if (!s->prefilled) return set_error(ctx, B200NN_ERR_ARG, "time_family before prefill");
+    if (family != B200NN_PROF_LAYERNORM && family != B200NN_PROF_LINEAR && family != B200NN_PROF_ATTENTION &&
+        family != B200NN_PROF_LM_HEAD)
+        return set_error(ctx, B200NN_ERR_UNSUPPORTED, "time_family: family must be layernorm, linear, attention or lm_head");
+    if (s->position + 1 > s->cap) return set_error(ctx, B200NN_ERR_DIM, "time_family: capacity exceeded");
+    CK(ctx, cudaSetDevice(ctx->device));
+    const int B = (int)s->batch;
+    const bool ah = model_act_half(m, B);
+    cudaEvent_t e0, e1;
+    CK(ctx, cudaEventCreate(&e0));
+    CK(ctx, cudaEventCreate(&e1));
+    const uint64_t before = ctx->launches;
+    uint64_t per_pass = 0;
+    ctx->fam_mask = 1u << family;
+    int rc = B200NN_OK;
+    // one untimed pass sizes scratch and warms the instruction cache
+    for (int r = -1; r < reps && rc == B200NN_OK; ++r) {
+        if (r == 0) cudaEventRecord(e0, ctx->stream);
+        rc = run_blocks(m, s->ws_step, s->kv, B, 1, s->pos_ptr(), 0, ah, nullptr);
+        if (rc == B200NN_OK) rc = run_head(m, s->ws_step, (const float *)s->ws_step.x->p, B, ah, nullptr);
+        if (r == -1) per_pass = ctx->launches - before;
+    }
+    cudaEventRecord(e1, ctx->stream);
+    ctx->fam_mask = 0xffffffffu;
+    cudaError_t ce = cudaStreamSynchronize(ctx->stream);
+    float ms = 0.0f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    TRY(rc);
+    if (ce != cudaSuccess) return set_cuda_error(ctx, ce, "time_family");
+    *ms_total = ms;
+    if (launches) *launches = per_pass * (uint64_t)reps;
+    return B200NN_OK;
+}
+
 // ---------------------------------------------------------------------------------------------
 // greedy generation
 // ---------------------------------------------------------------------------------------------

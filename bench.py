@@ -219,15 +219,16 @@ def run_b200(args):
     # around every launch on the library's stream), for the roofline of the dominant kernel
     sess.rewind(prompt_len)
     run_steps(window // 2)
-    fam = {n: 0.0 for n in b200nn.PROF_NAMES}
-    reps = 3
-    lin_bytes = 0
     ctx_mid = sess.position() + 1
-    for _ in range(reps):
-        t, lin_bytes = sess.profile_step()
-        for k2, v in t.items():
-            fam[k2] += v / reps
-        sess.rewind(sess.position() - 1)
+    _, lin_bytes = sess.profile_step()  # algorithmic bytes of the Linear kernels of one step
+    sess.rewind(sess.position() - 1)
+    # each family alone: its launches of one step, three passes back to back between two CUDA
+    # events on the library's stream (the activations are scratch afterwards)
+    fam, fam_launches, reps = {}, {}, 3
+    for name in ("attention", "linear", "layernorm", "lm_head"):
+        ms_f, n_f = sess.time_family(name, reps)
+        fam[name] = ms_f / reps
+        fam_launches[name] = n_f // reps
     hbm_peak, tf_peak, peak_kind = peaks()
     H, L, d = cfg.n_head, cfg.n_layer, cfg.n_embd
     act_b = 2 if batch > 2 else 4
@@ -245,7 +246,8 @@ def run_b200(args):
     roof["frac"] = roof["achieved"] / roof["peak"] if roof["peak"] else None
     roof["traffic"] = None
     roof["peak_source"] = peak_kind
-    roof["launch_ms"] = fam[dominant] / (L * (4 if dominant == "linear" else 1))
+    roof["launch_ms"] = fam[dominant] / max(1, fam_launches[dominant])
+    roof["launches_per_step"] = fam_launches
     roof["step_family_ms"] = {k2: round(v, 4) for k2, v in fam.items()}
     roof["other"] = {k2: {"achieved": v["achieved"], "frac": v["achieved"] / v["peak"]} for k2, v in roofs.items()
                      if k2 != dominant}

@@ -292,6 +292,13 @@ enum {
     B200NN_PROF_LM_HEAD, B200NN_PROF_ARGMAX, B200NN_PROF_COUNT
 };
 B200NN_API int32_t b200nn_session_profile_step(b200nn_session *s, float *times_ms, uint64_t *linear_bytes);
+/* Device time of ONE kernel family in isolation: launches only that family's kernels of a decode
+ * step (e.g. the decode-attention launch of every layer) `reps` times back to back at the current
+ * position, between two CUDA events on the context's stream.  *ms_total is the elapsed time,
+ * *launches the number of kernels it covers.  The activations are left in an arbitrary state:
+ * call prefill() again before decoding on. */
+B200NN_API int32_t b200nn_session_time_family(b200nn_session *s, int32_t family, int32_t reps, float *ms_total,
+                                              uint64_t *launches);
 B200NN_API void b200nn_session_destroy(b200nn_session *s);
 
 #ifdef __cplusplus

@@ -1,35 +1,95 @@
 // Group-wise int4 weight-only Linear on CUDA cores.
 //
 //   int4_gemv_kernel   few input rows (decode of one or two sequences): HBM-bound streaming of the
-//                      tiled nibbles with 128-bit coalesced loads, in-register dequantisation,
-//                      f32 accumulation, K split across the two thread slices of a block, across
-//                      blocks (deterministic: the last block to arrive sums the partials in split
-//                      order) and the fused bias / activation / residual / KV-cache epilogue.
+//                      tiled nibbles with 128-bit coalesced loads (two K blocks per thread in
+//                      flight, the first ones issued before the wait on the preceding kernel:
+//                      weights do not depend on it), in-register dequantisation, f32 accumulation.
+//                      K is split four ways inside a block and up to eight ways across the blocks of
+//                      a thread-block cluster; the cluster's partial sums are reduced through
+//                      distributed shared memory by the cluster's first block (fixed order, no
+//                      global scratch, no atomics), which then runs the fused bias / activation /
+//                      residual / KV-cache epilogue.
 //   int4_naive_kernel  any K%8==0 and any group size, reference layout, one thread per output as
 //                      crates/kernel/gpu-kernel-compute/src/compute_gemm.rs:2849-2910 does.
 //
 // Both compute y[m,n] = sum_k x[m,k] * (nibble(k,n)-8) * scale[k/group,n] (+ bias[n]).
+#include <cooperative_groups.h>
+
 #include "device_utils.cuh"
 
+namespace cg = cooperative_groups;
+
+static constexpr int GEMV_THREADS = 512; // 128 weight rows x 4 K slices
+static constexpr int GEMV_SLICES = 4;
+
+template <int MT>
+__device__ __forceinline__ void gemv_block_fma(const uint4 &wa, const uint4 &wb, float s, const float *xb, int len,
+                                               float (&acc)[MT]) {
+    const uint32_t w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+    float part[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) part[m] = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        __half2 q[4];
+        unpack8_int4(w[j], q);
+        const float2 f0 = __half22float2(q[0]), f1 = __half22float2(q[1]);
+        const float2 f2 = __half22float2(q[2]), f3 = __half22float2(q[3]);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            const float4 xa = *reinterpret_cast<const float4 *>(xb + m * len + 8 * j);
+            const float4 xc = *reinterpret_cast<const float4 *>(xb + m * len + 8 * j + 4);
+            float p = part[m];
+            p = fmaf(xa.x, f0.x, p); p = fmaf(xa.y, f0.y, p);
+            p = fmaf(xa.z, f1.x, p); p = fmaf(xa.w, f1.y, p);
+            p = fmaf(xc.x, f2.x, p); p = fmaf(xc.y, f2.y, p);
+            p = fmaf(xc.z, f3.x, p); p = fmaf(xc.w, f3.y, p);
+            part[m] = p;
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[m] = fmaf(s, part[m], acc[m]);
+}
+
+// grid (n_tiles, splits), cluster (1, splits, 1): the blocks of a cluster share one 128-row tile.
 template <int MT, typename XT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(GEMV_THREADS)
 int4_gemv_kernel(const uint4 *__restrict__ tiles, const __half *__restrict__ scales, const XT *__restrict__ x,
                  int m_valid, int m0, int K, int N, int k_blocks, int n_pad, int group, int kb_per_split,
-                 Epilogue epi, float *__restrict__ scratch, unsigned *__restrict__ counters) {
-    extern __shared__ float xs[]; // [MT][kb_per_split*64], then the cross-slice buffer [MT][128]
-    __shared__ int is_last;
+                 Epilogue epi) {
+    extern __shared__ float smem_f[];
+    cg::cluster_group cluster = cg::this_cluster();
     const int nt = blockIdx.x, split = blockIdx.y, splits = gridDim.y;
     const int tid = threadIdx.x, r = tid & 127, slice = tid >> 7;
     const int kb0 = split * kb_per_split;
     const int kb1 = min(kb0 + kb_per_split, k_blocks);
     const int len = kb_per_split * 64;
     const int n = nt * TILE_N + r;
+    float *xs = smem_f;                       // [MT][len] activations of this block's K range
+    float *red = smem_f + MT * len;           // [GEMV_SLICES][MT][128] slice sums
+    float *part = red + GEMV_SLICES * MT * 128; // [MT][128] this block's partial tile (read by the cluster)
     pdl_trigger();
-    pdl_wait();
 
-    for (int i = tid; i < MT * len; i += 256) {
-        int m = i / len, kk = i - m * len;
-        int k = kb0 * 64 + kk;
+    // weights and scales of the first two K blocks of this thread: issued before the wait on the
+    // previous kernel (they are constants), so that their DRAM latency overlaps its tail
+    const uint4 *tile0 = tiles + (size_t)nt * k_blocks * (TILE_BYTES / 16);
+    auto load_block = [&](int kb, uint4 &a, uint4 &b, float &s) {
+        const uint4 *tp = tile0 + (size_t)kb * (TILE_BYTES / 16);
+        a = __ldg(tp + r);
+        b = __ldg(tp + 128 + r);
+        s = __half2float(scales[(size_t)((kb * 64) / group) * n_pad + n]);
+    };
+    int kb = kb0 + slice;
+    uint4 a0 = make_uint4(0, 0, 0, 0), b0 = a0, a1 = a0, b1 = a0;
+    float s0 = 0.0f, s1 = 0.0f;
+    bool v0 = kb < kb1, v1 = kb + GEMV_SLICES < kb1;
+    if (v0) load_block(kb, a0, b0, s0);
+    if (v1) load_block(kb + GEMV_SLICES, a1, b1, s1);
+
+    pdl_wait();
+    for (int i = tid; i < MT * len; i += GEMV_THREADS) {
+        const int m = i / len, kk = i - m * len;
+        const int k = kb0 * 64 + kk;
         xs[i] = (m < m_valid && k < kb1 * 64) ? load_as_float<XT>(x, (size_t)m * K + k) : 0.0f;
     }
     __syncthreads();
@@ -37,82 +97,41 @@ int4_gemv_kernel(const uint4 *__restrict__ tiles, const __half *__restrict__ sca
     float acc[MT];
 #pragma unroll
     for (int m = 0; m < MT; ++m) acc[m] = 0.0f;
-
-    for (int kb = kb0 + slice; kb < kb1; kb += 2) {
-        const uint4 *tp = tiles + ((size_t)nt * k_blocks + kb) * (TILE_BYTES / 16);
-        uint4 wa = tp[r], wb = tp[128 + r];
-        float s = __half2float(scales[(size_t)((kb * 64) / group) * n_pad + n]);
-        uint32_t w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
-        float part[MT];
-#pragma unroll
-        for (int m = 0; m < MT; ++m) part[m] = 0.0f;
-        const float *xb = xs + (kb - kb0) * 64;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            __half2 q[4];
-            unpack8_int4(w[j], q);
-            float2 f0 = __half22float2(q[0]), f1 = __half22float2(q[1]);
-            float2 f2 = __half22float2(q[2]), f3 = __half22float2(q[3]);
-#pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                const float4 xa = *reinterpret_cast<const float4 *>(xb + m * len + 8 * j);
-                const float4 xc = *reinterpret_cast<const float4 *>(xb + m * len + 8 * j + 4);
-                float p = part[m];
-                p = fmaf(xa.x, f0.x, p); p = fmaf(xa.y, f0.y, p);
-                p = fmaf(xa.z, f1.x, p); p = fmaf(xa.w, f1.y, p);
-                p = fmaf(xc.x, f2.x, p); p = fmaf(xc.y, f2.y, p);
-                p = fmaf(xc.z, f3.x, p); p = fmaf(xc.w, f3.y, p);
-                part[m] = p;
-            }
-        }
-#pragma unroll
-        for (int m = 0; m < MT; ++m) acc[m] = fmaf(s, part[m], acc[m]);
+    while (v0) {
+        const uint4 ca = a0, cb = b0;
+        const float cs = s0;
+        const int ckb = kb;
+        a0 = a1; b0 = b1; s0 = s1; v0 = v1;
+        kb += GEMV_SLICES;
+        v1 = kb + GEMV_SLICES < kb1;
+        if (v1) load_block(kb + GEMV_SLICES, a1, b1, s1); // stays two K blocks ahead
+        gemv_block_fma<MT>(ca, cb, cs, xs + (ckb - kb0) * 64, len, acc);
     }
 
-    // slice 1 hands its sums to slice 0
-    float *xred = xs + MT * len;
-    if (slice == 1) {
 #pragma unroll
-        for (int m = 0; m < MT; ++m) xred[m * 128 + r] = acc[m];
-    }
+    for (int m = 0; m < MT; ++m) red[(slice * MT + m) * 128 + r] = acc[m];
     __syncthreads();
     if (slice == 0) {
 #pragma unroll
-        for (int m = 0; m < MT; ++m) acc[m] += xred[m * 128 + r];
-    }
-
-    if (splits == 1) {
-        if (slice == 0 && n < N) {
+        for (int m = 0; m < MT; ++m) {
+            float t = 0.0f;
 #pragma unroll
-            for (int m = 0; m < MT; ++m)
-                if (m < m_valid) epi_apply(epi, m0 + m, n, acc[m]);
+            for (int sl = 0; sl < GEMV_SLICES; ++sl) t += red[(sl * MT + m) * 128 + r];
+            part[m * 128 + r] = t;
         }
-        return;
     }
-    // partial sums -> scratch [split][MT][n_pad]; the last block of this tile reduces them
-    if (slice == 0) {
-#pragma unroll
-        for (int m = 0; m < MT; ++m) scratch[((size_t)split * MT + m) * n_pad + n] = acc[m];
-    }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        unsigned prev = atomicAdd(&counters[nt], 1u);
-        is_last = (prev == (unsigned)(splits - 1));
-        if (is_last) counters[nt] = 0u;
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    if (slice == 0 && n < N) {
+    cluster.sync(); // every block's partial tile is in its shared memory
+    if (cluster.block_rank() == 0 && slice == 0 && n < N) {
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             if (m >= m_valid) break;
             float t = 0.0f;
-            for (int sp = 0; sp < splits; ++sp) t += __ldcg(&scratch[((size_t)sp * MT + m) * n_pad + n]);
+            for (int sp = 0; sp < splits; ++sp) // fixed order: the result does not depend on timing
+                t += cluster.map_shared_rank(part, sp)[m * 128 + r];
             epi_apply(epi, m0 + m, n, t);
         }
     }
+    cluster.sync(); // no block leaves while its shared memory may still be read
 }
 
 template <typename XT>
@@ -156,22 +175,37 @@ int launch_int4_naive(b200nn_ctx *ctx, const Int4Weight &w, const void *x, bool 
 
 template <int MT, typename XT>
 static int gemv_chunk(b200nn_ctx *ctx, const Int4Weight &w, const XT *x, int m_valid, int m0, const Epilogue &epi) {
-    // choose the K split so that the grid is about two waves of blocks and a split is <= 16 blocks
-    int target = 2 * ctx->sm_count;
-    int splits = (target + w.n_tiles - 1) / w.n_tiles;
-    if (splits > w.k_blocks) splits = w.k_blocks;
-    if (splits < 1) splits = 1;
-    int per = (w.k_blocks + splits - 1) / splits;
-    if (per > 16) per = 16;
-    if (per & 1) per += 1; // both slices get work
+    // K split across a cluster of up to eight blocks so that about one block per SM is resident
+    int splits = (ctx->sm_count + w.n_tiles - 1) / w.n_tiles;
+    splits = std::max(1, std::min(splits, 8));
+    splits = std::min(splits, std::max(1, w.k_blocks / GEMV_SLICES));
+    const int per = (w.k_blocks + splits - 1) / splits;
     splits = (w.k_blocks + per - 1) / per;
-    size_t smem = (size_t)MT * per * 64 * 4 + (size_t)MT * 128 * 4;
-    if (splits > 1) TRY(ensure_scratch(ctx, (size_t)splits * MT * w.n_pad * 4, (size_t)w.n_tiles));
-    dim3 grid(w.n_tiles, splits);
-    PREFER_SMEM_ONCE((int4_gemv_kernel<MT, XT>));
-    launch_pdl(ctx, int4_gemv_kernel<MT, XT>, grid, dim3(256), smem, (const uint4 *)w.tiled->p,
-               (const __half *)w.scales_h->p, x, m_valid, m0, w.K, w.N, w.k_blocks, w.n_pad, w.group, per, epi, ctx->scratch,
-               ctx->counters);
+    const size_t smem = ((size_t)MT * per * 64 + (size_t)(GEMV_SLICES + 1) * MT * 128) * sizeof(float);
+    auto kern = int4_gemv_kernel<MT, XT>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        CK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        prefer_max_smem(kern);
+        attr_done = true;
+    }
+    if (smem > 200 * 1024) return set_error(ctx, B200NN_ERR_UNSUPPORTED, "int4 GEMV: K too large for one cluster");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(w.n_tiles, splits);
+    cfg.blockDim = dim3(GEMV_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = splits;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->pdl ? 2 : 1;
+    CK(ctx, cudaLaunchKernelEx(&cfg, kern, (const uint4 *)w.tiled->p, (const __half *)w.scales_h->p, x, m_valid, m0, w.K,
+                               w.N, w.k_blocks, w.n_pad, w.group, per, epi));
     CK_LAUNCH(ctx, "int4_gemv_kernel");
     return B200NN_OK;
 }

@@ -141,6 +141,48 @@ def run_reference(args):
     return 0
 
 
+def gemv_bandwidth(reg, cfg, hbm_peak, iters=96):
+    """Dequant-GEMV (one input row, CUDA cores) HBM bandwidth on the model's four Linear shapes: each
+    launch reads a different copy of the weight (copies add up to more than the L2), launches are
+    back to back on the library's stream between two CUDA events.  Bytes per launch are algorithmic:
+    nibbles + fp16 scales + input row + output row."""
+    import torch
+    import b200nn
+    from b200nn import synth
+    d = cfg.n_embd
+    stream = torch.cuda.ExternalStream(reg.stream)
+    out = {}
+    for name, (k, n) in {"qkv": (d, 3 * d), "proj": (d, d), "fc": (d, 4 * d), "fcproj": (4 * d, d)}.items():
+        packed, scales, _, _ = synth.int4_linear_case(11, 1, k, n, 128)
+        copies = max(2, int(256e6 // (k * n / 2)))
+        lins = [b200nn.Int4Linear(packed, scales, None, k, n, 128, reg) for _ in range(copies)]
+        x = torch.randn(1, k, device="cuda")
+        y = torch.empty(1, n, device="cuda")
+        for l in lins:
+            l.forward_dev(x.data_ptr(), 1, y.data_ptr())
+        reg.synchronize()
+        # the launches are captured into one CUDA graph so that the host's launch rate is not what
+        # is being measured
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
+            for i in range(iters):
+                lins[i % copies].forward_dev(x.data_ptr(), 1, y.data_ptr())
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            g.replay()
+            e0.record(stream)
+            g.replay()
+            e1.record(stream)
+        torch.cuda.synchronize()
+        del g
+        us = e0.elapsed_time(e1) / iters * 1e3
+        nbytes = k * n // 2 + ((k + 127) // 128) * n * 2 + k * 4 + n * 4
+        out[name] = {"k": k, "n": n, "us_per_launch": round(us, 2), "GBps": round(nbytes / us / 1e3, 1),
+                     "frac_of_hbm_peak": round(nbytes / us / 1e3 / hbm_peak, 4)}
+        del lins
+    return out
+
+
 def run_b200(args):
     import torch
     import torch.distributed as dist
@@ -165,6 +207,8 @@ def run_b200(args):
     if args.batch:
         total = args.batch
     cfg = getattr(Gpt2Config, preset)()
+    if args.layers:
+        cfg.n_layer = args.layers  # reduced depth: for profiler captures only, never a benchmark number
     lo, hi = shard_bounds(total, world, rank)
     batch = hi - lo
     reg = b200nn.KernelRegistry(local)
@@ -283,6 +327,11 @@ def run_b200(args):
                    "model_build_s": round(build_s, 1)},
         "roofline": roof, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
     }
+    if args.layers:
+        line["config"]["layers_override"] = args.layers
+        line["config"]["note"] = "reduced depth for a profiler capture: not a benchmark number"
+    if rank == 0 and not args.no_gemv:
+        line["gemv"] = gemv_bandwidth(reg, cfg, hbm_peak)
     if world == 1 and not args.no_cpu_baseline:
         wq = build_int4_oracle_weights(cfg, w)
         steps = args.cpu_steps
@@ -305,6 +354,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="gpt2-xl-int4-b256", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=0, help="override the total number of sequences")
+    ap.add_argument("--layers", type=int, default=0, help="profiling aid: build only this many layers")
+    ap.add_argument("--no-gemv", action="store_true", help="skip the dequant-GEMV bandwidth measurement")
     ap.add_argument("--e2e-runs", type=int, default=2)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-steps", type=int, default=8)

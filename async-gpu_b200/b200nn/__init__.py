@@ -131,6 +131,8 @@ def load_library() -> C.CDLL:
             "b200nn_session_tokens": (i32, [vp, _u32p, sz, szp]), "b200nn_session_logits": (i32, [vp, _f32p]),
             "b200nn_session_profile_step": (i32, [vp, _f32p, C.POINTER(C.c_uint64)]),
             "b200nn_session_time_family": (i32, [vp, i32, i32, _f32p, C.POINTER(C.c_uint64)]),
+            "b200nn_decode_attention_noalloc": (i32, [i32, vp, vp, vp, vp, i32, i32, i32, i32, vp]),
+            "b200nn_noalloc_last_error": (C.c_char_p, []),
             "b200nn_session_destroy": (None, [vp]),
         }
         for name, (res, args) in sig.items():

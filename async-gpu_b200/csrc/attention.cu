@@ -309,3 +309,101 @@ int launch_prefill_attention(b200nn_ctx *ctx, const void *q, bool q_half, int ld
     CK_LAUNCH(ctx, "prefill_attn_kernel");
     return B200NN_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Decode attention for callers that must not allocate device memory.
+//
+// The split-context form of decode_attn_kernel needs scratch: one (max, sum, output[64]) record per
+// (sequence, head, split) and one arrival counter per (sequence, head).  The regular entry points
+// take it from the context's scratch buffer, which grows with cudaMalloc on demand.  Some callers
+// cannot have that: code running in a real-time loop, where cudaMalloc would synchronise the
+// device and stall everything queued on it, or a host application whose memory budget is fixed up front and
+// that hands this library only the buffers it owns.  For them the scratch below lives in the
+// library's own image: two file-scope __device__ arrays of fixed size (about 4.2 MB, present on
+// every GPU that loads the library until the process exits).
+//
+// In host code the array names are host-side stand-ins, not device addresses; the device address
+// is obtained once per device with cudaGetSymbolAddress (with that device current) and passed to
+// the kernel.  That first call on a device is the set-up and should come before any stream
+// capture.  All calls share the arrays: the counters are cleared on the caller's stream before
+// every launch, the records are fully rewritten by each call, and two calls that overlap on the
+// GPU (different streams) race on them.
+// ---------------------------------------------------------------------------------------------
+static constexpr int NOALLOC_MAX_PAIRS = 4096;    // sequences x heads
+static constexpr int NOALLOC_MAX_RECORDS = 16384; // sequences x heads x splits
+static __device__ __align__(256) float g_noalloc_records[NOALLOC_MAX_RECORDS * 66];
+static __device__ __align__(256) unsigned g_noalloc_counters[NOALLOC_MAX_PAIRS];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+struct NoAllocDevice {
+    bool ready = false;
+    float *records = nullptr;
+    unsigned *counters = nullptr;
+    int sm_count = 0;
+};
+NoAllocDevice g_noalloc_dev[NOALLOC_MAX_DEVICES];
+thread_local char g_noalloc_error[256] = "";
+
+int noalloc_fail(int code, const char *msg, cudaError_t e = cudaSuccess) {
+    if (e != cudaSuccess)
+        snprintf(g_noalloc_error, sizeof(g_noalloc_error), "%s: %s", msg, cudaGetErrorString(e));
+    else
+        snprintf(g_noalloc_error, sizeof(g_noalloc_error), "%s", msg);
+    return code;
+}
+}  // namespace
+
+extern "C" const char *b200nn_noalloc_last_error(void) { return g_noalloc_error; }
+
+extern "C" int32_t b200nn_decode_attention_noalloc(int32_t device, void *stream, const float *q_dev,
+                                                   const void *k_cache_dev, const void *v_cache_dev, int32_t batch,
+                                                   int32_t n_heads, int32_t capacity, int32_t ctx_len, float *out_dev) {
+    if (!q_dev || !k_cache_dev || !v_cache_dev || !out_dev) return noalloc_fail(B200NN_ERR_ARG, "null buffer");
+    if (device < 0 || device >= NOALLOC_MAX_DEVICES) return noalloc_fail(B200NN_ERR_ARG, "device ordinal out of range");
+    if (batch <= 0 || n_heads <= 0 || capacity <= 0 || ctx_len <= 0 || ctx_len > capacity)
+        return noalloc_fail(B200NN_ERR_SHAPE, "batch, n_heads, capacity must be positive and 1 <= ctx_len <= capacity");
+    const long long pairs = (long long)batch * n_heads;
+    if (pairs > NOALLOC_MAX_PAIRS)
+        return noalloc_fail(B200NN_ERR_SHAPE, "batch * n_heads exceeds the fixed scratch (4096 pairs)");
+    int prev = -1;
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return noalloc_fail(B200NN_ERR_CUDA, "cudaGetDevice", e);
+    if (prev != device && (e = cudaSetDevice(device)) != cudaSuccess) return noalloc_fail(B200NN_ERR_CUDA, "cudaSetDevice", e);
+    int rc = B200NN_OK;
+    NoAllocDevice &D = g_noalloc_dev[device];
+    if (!D.ready) { // set-up, once per device, with that device current
+        void *rp = nullptr, *cp = nullptr;
+        if ((e = cudaGetSymbolAddress(&rp, g_noalloc_records)) != cudaSuccess)
+            rc = noalloc_fail(B200NN_ERR_CUDA, "cudaGetSymbolAddress(records)", e);
+        else if ((e = cudaGetSymbolAddress(&cp, g_noalloc_counters)) != cudaSuccess)
+            rc = noalloc_fail(B200NN_ERR_CUDA, "cudaGetSymbolAddress(counters)", e);
+        else if ((e = cudaDeviceGetAttribute(&D.sm_count, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess)
+            rc = noalloc_fail(B200NN_ERR_CUDA, "cudaDeviceGetAttribute", e);
+        else {
+            D.records = static_cast<float *>(rp);
+            D.counters = static_cast<unsigned *>(cp);
+            D.ready = true;
+        }
+    }
+    if (rc == B200NN_OK) {
+        // same split rule as the regular path, bounded by the fixed scratch
+        int n_splits = (int)((4LL * D.sm_count + pairs - 1) / pairs);
+        n_splits = std::min(n_splits, (ctx_len + 63) / 64);
+        n_splits = std::min(n_splits, 32);
+        n_splits = std::min(n_splits, (int)(NOALLOC_MAX_RECORDS / pairs));
+        n_splits = std::max(n_splits, 1);
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        if ((e = cudaMemsetAsync(D.counters, 0, (size_t)pairs * sizeof(unsigned), st)) != cudaSuccess)
+            rc = noalloc_fail(B200NN_ERR_CUDA, "cudaMemsetAsync(counters)", e);
+        else {
+            dim3 grid(n_heads, batch, n_splits);
+            decode_attn_kernel<float, float><<<grid, 128, 0, st>>>(
+                q_dev, n_heads * 64, static_cast<const __half *>(k_cache_dev), static_cast<const __half *>(v_cache_dev),
+                n_heads, capacity, nullptr, ctx_len - 1, out_dev, n_heads * 64, D.records, D.counters);
+            if ((e = cudaPeekAtLastError()) != cudaSuccess) rc = noalloc_fail(B200NN_ERR_CUDA, "kernel launch", e);
+        }
+    }
+    if (prev != device && prev >= 0) cudaSetDevice(prev);
+    return rc;
+}

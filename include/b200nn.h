@@ -301,6 +301,28 @@ B200NN_API int32_t b200nn_session_time_family(b200nn_session *s, int32_t family,
                                               uint64_t *launches);
 B200NN_API void b200nn_session_destroy(b200nn_session *s);
 
+/* ---- decode attention without any allocation ----------------------------------------------------
+ * This entry point has no counterpart in the reference.  It is for callers that cannot let the
+ * library call cudaMalloc: a host that has handed out its whole device-memory budget, or code that
+ * runs where an allocation would synchronise the device (inside a latency-critical loop).
+ * It needs no context: the caller passes the device ordinal, its own
+ * stream (NULL = default stream), and device buffers it owns:
+ *   q_dev   [batch, n_heads*64] f32    one query row per sequence
+ *   k_cache_dev, v_cache_dev  fp16 [batch][n_heads][capacity][64], positions [0, ctx_len) filled
+ *   out_dev [batch, n_heads*64] f32
+ * and gets softmax(q.K^T/8).V per (sequence, head) over the first ctx_len positions, computed by
+ * the same kernel as the regular decode path.  The kernel's split-context scratch is a fixed
+ * array inside the library image (about 4.2 MB per GPU, held until the process exits), so
+ * batch*n_heads must not exceed 4096; larger requests return B200NN_ERR_SHAPE.  The first call on
+ * a device looks up the array's device address; make that call before capturing a stream.  All
+ * calls share the array: calls that overlap on the GPU (different streams) race.  No cudaMalloc,
+ * cudaFree or allocating library routine is called.  b200nn_noalloc_last_error() gives the text of
+ * the calling thread's last failure. */
+B200NN_API int32_t b200nn_decode_attention_noalloc(int32_t device, void *stream, const float *q_dev,
+                                                   const void *k_cache_dev, const void *v_cache_dev, int32_t batch,
+                                                   int32_t n_heads, int32_t capacity, int32_t ctx_len, float *out_dev);
+B200NN_API const char *b200nn_noalloc_last_error(void);
+
 #ifdef __cplusplus
 }
 #endif

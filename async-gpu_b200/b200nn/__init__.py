@@ -70,6 +70,7 @@ def load_library() -> C.CDLL:
             "b200nn_version": (C.c_char_p, []),
             "b200nn_ctx_create": (i32, [i32, vpp]), "b200nn_ctx_destroy": (None, [vp]),
             "b200nn_ctx_synchronize": (i32, [vp]), "b200nn_ctx_stream": (vp, [vp]),
+            "b200nn_ctx_trim": (i32, [vp]),
             "b200nn_last_error_message": (C.c_char_p, [vp]), "b200nn_last_cuda_error": (i32, [vp]),
             "b200nn_ctx_device_error": (i32, [vp, _u32p]), "b200nn_ctx_launch_count": (C.c_uint64, [vp]),
             "b200nn_ctx_set_gemv_max_rows": (i32, [vp, i32]),
@@ -181,6 +182,10 @@ class KernelRegistry:
 
     def synchronize(self):
         self.check(self.lib.b200nn_ctx_synchronize(self.h))
+
+    def trim(self):
+        """Returns the device blocks the context keeps for reuse to the driver."""
+        self.check(self.lib.b200nn_ctx_trim(self.h))
 
     @property
     def stream(self) -> int:

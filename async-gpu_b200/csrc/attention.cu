@@ -293,6 +293,8 @@ prefill_attn_kernel(const QT *__restrict__ q, int ldq, const __half *__restrict_
 int launch_prefill_attention(b200nn_ctx *ctx, const void *q, bool q_half, int ldq, const __half *kc,
                              const __half *vc, int B, int H, int cap, int S, int past, void *out, bool out_half) {
     if (B <= 0 || S <= 0) return B200NN_OK;
+    if (q_half && out_half && ctx->attn_tc && (ldq & 7) == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0)
+        return launch_prefill_attention_tc(ctx, (const __half *)q, ldq, kc, vc, B, H, cap, S, past, (__half *)out);
     dim3 grid((S + 63) / 64, H, B);
     int ldo = H * 64;
 #define PA(QT, OT)                                                                                                \

@@ -6,17 +6,32 @@
 
 #include <cstdint>
 #include <cstdio>
+#include <map>
 #include <memory>
+#include <mutex>
 #include <string>
 #include <vector>
 
 #include "b200nn.h"
+
+// Device blocks released by tensors, workspaces and KV caches are kept for reuse instead of going
+// back to the driver: cudaMalloc / cudaFree of a multi-gigabyte KV cache cost tens of milliseconds
+// and synchronise the device, which a generate call per request cannot afford.  Shared between the
+// context and its buffers so that a buffer may outlive the context (it then frees directly).
+struct DevPool {
+    std::mutex mu;
+    std::multimap<size_t, void *> free_blocks; // by size
+    size_t held_bytes = 0;
+    bool alive = true;                          // false once the context is gone
+    static constexpr size_t MAX_HELD = (size_t)64 << 30;
+};
 
 // ---------------------------------------------------------------------------------------------
 // context
 // ---------------------------------------------------------------------------------------------
 struct b200nn_ctx {
     int device = 0;
+    std::shared_ptr<DevPool> pool = std::make_shared<DevPool>();
     cudaStream_t stream = nullptr;
     std::string last_error;
     int last_cuda = 0;
@@ -33,6 +48,7 @@ struct b200nn_ctx {
     int tc_mb = 0, tc_splits = 0, tc_min_kb = 4; // tensor-core GEMM tuning overrides (0 = automatic)
     long long *trace = nullptr;   // optional device buffer for in-kernel time stamps (measurement aid)
     uint32_t fam_mask = 0xffffffffu; // kernel families run_blocks / run_head launch (timing aid)
+    int attn_tc = 1;              // prefill attention with fp16 q and output runs on the tensor cores
     int pdl = 1;                  // launch the decode-step kernels with programmatic dependent launch
     bool capturing = false;       // true while a decode step is being captured into a graph
 };
@@ -100,9 +116,12 @@ struct DevBuf {
     void *p = nullptr;
     size_t bytes = 0;
     int device = 0;
+    size_t block_bytes = 0;        // size of the underlying allocation (>= bytes)
+    std::shared_ptr<DevPool> pool; // where the block goes when the buffer dies
     ~DevBuf();
 };
 int dev_alloc(b200nn_ctx *ctx, size_t bytes, std::shared_ptr<DevBuf> *out);
+void pool_trim(b200nn_ctx *ctx); // returns every kept block to the driver
 
 struct b200nn_tensor {
     b200nn_ctx *ctx = nullptr;
@@ -208,6 +227,9 @@ int launch_decode_attention(b200nn_ctx *ctx, const void *q, bool q_half, int ldq
 // Prefill attention: S query rows per sequence at absolute positions past..past+S-1, causal.
 int launch_prefill_attention(b200nn_ctx *ctx, const void *q, bool q_half, int ldq, const __half *kc,
                              const __half *vc, int B, int H, int cap, int S, int past, void *out, bool out_half);
+// The tensor-core form of the above for fp16 q and output (ldq a multiple of 8 halves).
+int launch_prefill_attention_tc(b200nn_ctx *ctx, const __half *q, int ldq, const __half *kc, const __half *vc, int B, int H,
+                                int cap, int S, int past, __half *out);
 // f32 [H,len,64] (public op layout) -> fp16 cache layout [1][H][cap][64]
 int launch_pack_kv(b200nn_ctx *ctx, const float *src, int H, int len, int cap, __half *dst);
 

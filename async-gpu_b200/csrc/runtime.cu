@@ -22,22 +22,71 @@ int set_cuda_error(b200nn_ctx *ctx, cudaError_t e, const char *what) {
     return B200NN_ERR_CUDA;
 }
 
-DevBuf::~DevBuf() {
-    if (p) {
-        int cur = -1;
-        cudaGetDevice(&cur);
-        if (cur != device) cudaSetDevice(device);
-        cudaFree(p);
-        if (cur >= 0 && cur != device) cudaSetDevice(cur);
-    }
+static void free_on_device(void *p, int device) {
+    int cur = -1;
+    cudaGetDevice(&cur);
+    if (cur != device) cudaSetDevice(device);
+    cudaFree(p);
+    if (cur >= 0 && cur != device) cudaSetDevice(cur);
 }
 
+DevBuf::~DevBuf() {
+    if (!p) return;
+    if (pool) {
+        std::lock_guard<std::mutex> g(pool->mu);
+        if (pool->alive && pool->held_bytes + block_bytes <= DevPool::MAX_HELD) {
+            pool->free_blocks.emplace(block_bytes, p);
+            pool->held_bytes += block_bytes;
+            return;
+        }
+    }
+    free_on_device(p, device);
+}
+
+void pool_trim(b200nn_ctx *ctx) {
+    std::lock_guard<std::mutex> g(ctx->pool->mu);
+    for (auto &kv : ctx->pool->free_blocks) free_on_device(kv.second, ctx->device);
+    ctx->pool->free_blocks.clear();
+    ctx->pool->held_bytes = 0;
+}
+
+// A kept block is reused when it is at least as large as the request and at most a quarter
+// larger.  All of the library's device work runs on the context's stream, so a reused block is
+// ordered after its previous owner's kernels there; synchronous copies from the host are not
+// stream-ordered, hence the synchronise on reuse (the stream is idle at that point in practice).
 int dev_alloc(b200nn_ctx *ctx, size_t bytes, std::shared_ptr<DevBuf> *out) {
     auto b = std::make_shared<DevBuf>();
     b->device = ctx->device;
     b->bytes = bytes;
+    b->pool = ctx->pool;
+    const size_t want = bytes ? (bytes + 255) & ~(size_t)255 : 256;
     CK(ctx, cudaSetDevice(ctx->device));
-    CK(ctx, cudaMalloc(&b->p, bytes ? bytes : 16));
+    {
+        std::lock_guard<std::mutex> g(ctx->pool->mu);
+        auto it = ctx->pool->free_blocks.lower_bound(want);
+        if (it != ctx->pool->free_blocks.end() && it->first <= want + want / 4) {
+            b->p = it->second;
+            b->block_bytes = it->first;
+            ctx->pool->held_bytes -= it->first;
+            ctx->pool->free_blocks.erase(it);
+        }
+    }
+    if (b->p) {
+        if (!ctx->capturing) CK(ctx, cudaStreamSynchronize(ctx->stream));
+        *out = b;
+        return B200NN_OK;
+    }
+    cudaError_t e = cudaMalloc(&b->p, want);
+    if (e == cudaErrorMemoryAllocation) { // give the kept blocks back and try once more
+        cudaGetLastError();
+        pool_trim(ctx);
+        e = cudaMalloc(&b->p, want);
+    }
+    if (e != cudaSuccess) {
+        b->p = nullptr;
+        return set_cuda_error(ctx, e, "cudaMalloc");
+    }
+    b->block_bytes = want;
     *out = b;
     return B200NN_OK;
 }

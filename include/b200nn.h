@@ -75,6 +75,10 @@ B200NN_API const char *b200nn_version(void);
 B200NN_API int32_t b200nn_ctx_create(int32_t device_ordinal, b200nn_ctx **out);
 B200NN_API void b200nn_ctx_destroy(b200nn_ctx *ctx);
 B200NN_API int32_t b200nn_ctx_synchronize(b200nn_ctx *ctx);
+/* Device blocks released by tensors, workspaces and KV caches are kept by the context for reuse
+ * (up to 64 GB; an allocation failure also releases them).  This hands them back to the driver.
+ * The reference frees eagerly through cudarc's Drop; there is nothing to replace. */
+B200NN_API int32_t b200nn_ctx_trim(b200nn_ctx *ctx);
 /* cudaStream_t of the context, for callers that record their own events on it. */
 B200NN_API void *b200nn_ctx_stream(b200nn_ctx *ctx);
 B200NN_API const char *b200nn_last_error_message(b200nn_ctx *ctx);
@@ -88,7 +92,8 @@ B200NN_API uint64_t b200nn_ctx_launch_count(b200nn_ctx *ctx);
 B200NN_API int32_t b200nn_ctx_set_gemv_max_rows(b200nn_ctx *ctx, int32_t rows);
 /* Tuning overrides of the tensor-core GEMM's launch policy, for measurements: "tc_mb" (cap of the
  * token-tile width: 16..256, 0 = default), "tc_splits" (K splits, 0 = automatic), "tc_min_kb"
- * (fewest 64-wide K blocks per split), "gemv_max_rows". */
+ * (fewest 64-wide K blocks per split), "gemv_max_rows", "pdl" (programmatic dependent launch on/off),
+ * "attn_tc" (0 = run fp16 prefill attention on the CUDA cores instead of the tensor cores). */
 B200NN_API int32_t b200nn_ctx_set_tuning(b200nn_ctx *ctx, const char *key, int32_t value);
 /* Measurement aid: after set_tuning("trace", 1) the first block of the next tensor-core GEMM
  * writes SM-clock stamps of its pipeline events into a 256-slot buffer; this copies it out. */

@@ -143,6 +143,34 @@ def test_generate_batch_equals_single_and_session(reg):
     assert reg.device_error() == 0
 
 
+def test_int4_prefill_attention_tensor_core_long_sequences(reg):
+    """The tensor-core prefill attention (fp16 activations) over several 128-query and 128-key tiles:
+    a 300-token forward and a cached forward in two uneven pieces (past = 150, not a tile multiple),
+    each against the oracle; and the CUDA-core kernel as a second opinion."""
+    cfg = _mini(n_layer=2, d=128, vocab=257, npos=320)
+    w = synth.gpt2_weights(cfg, base_seed=65, std=0.08, random_ln=True)
+    m = Int4Gpt2Model.from_weights(w, cfg, reg)
+    om = oracle.Model(cfg.as_dict(), _int4_oracle_weights(m, cfg, w, False))
+    toks = synth.token_ids(8, (2, 300), cfg.vocab_size)
+    refs = [om.forward(toks[b], flags=oracle.KV_FP16) for b in range(2)]
+    full = m.forward(toks[0]).to_host()
+    _check_logits(full, refs[0])
+    cache = KvCache(m, batch=2, capacity=304)
+    first = m.forward_cached(toks[:, :150], 150, cache).to_host().reshape(2, 150, -1)
+    rest = m.forward_cached(toks[:, 150:], 150, cache).to_host().reshape(2, 150, -1)
+    for b in range(2):
+        _check_logits(first[b], refs[b][:150])
+        _check_logits(rest[b], refs[b][150:])
+    reg.set_tuning("attn_tc", 0)
+    try:
+        simt = m.forward(toks[0]).to_host()
+    finally:
+        reg.set_tuning("attn_tc", 1)
+    _check_logits(simt, refs[0])
+    assert np.abs(simt - full).max() < 5e-3
+    assert reg.device_error() == 0
+
+
 def test_eos_stops_before_append(reg):
     # a vocabulary large enough to contain id 50256, with the head biased so that it wins
     cfg = Gpt2Config(n_layer=1, n_embd=64, n_head=1, vocab_size=50257, n_positions=32)

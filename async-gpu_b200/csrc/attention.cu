@@ -13,6 +13,7 @@
 //
 // Scores are q.k/sqrt(64); softmax is computed with exp2 on scores pre-multiplied by log2(e).
 #include "device_utils.cuh"
+#include "tc_ptx.cuh"
 
 static constexpr float ATT_SCALE_LOG2E = 0.125f * 1.4426950408889634f;
 static constexpr float NEG_BIG = -1.0e30f;
@@ -163,11 +164,243 @@ decode_attn_kernel(const QT *__restrict__ q, int ldq, const __half *__restrict__
     if constexpr (sizeof(OT) == 2) out[oi] = __float2half_rn(r); else out[oi] = r;
 }
 
+// ---------------------------------------------------------------------------------------------
+// decode_attn_stream_kernel: the same computation for many (sequence, head) pairs, fed by TMA.
+//
+// One persistent block per SM, eight warps, each warp an independent pipeline: it takes whole
+// (sequence, head) items from a device-side work counter and streams the item's K and V rows
+// through its own ring of shared-memory stages with bulk async copies (32 rows of K + 32 rows of V
+// per stage, 8 KB, plus the query row with the item's first stage), always two stages ahead of the
+// rows it is working on.  The memory system therefore sees ~128 KB in flight per SM regardless of
+// what the arithmetic is doing, where the plain-load kernel above stalls its loads behind its own
+// shuffles and exponentials.  A warp keeps the online-softmax state of its item in registers
+// (4 lane groups x 8 lanes, merged with shuffles at the end), so there is no block-level
+// synchronisation at all after start-up.  Every mbarrier wait is bounded.
+// ---------------------------------------------------------------------------------------------
+namespace stream_attn {
+constexpr int WARPS = 8, NST = 3, ROWS = 32;
+constexpr int STAGE_BYTES = 2 * ROWS * 128 + 256; // K rows, V rows, query row (fp16 or f32)
+constexpr int SMEM_BYTES = WARPS * NST * STAGE_BYTES + 128;
+constexpr uint32_t ERR_FULL = 0x51;
+}  // namespace stream_attn
+
+template <typename QT, typename OT>
+__global__ void __launch_bounds__(256, 1)
+decode_attn_stream_kernel(const QT *__restrict__ q, int ldq, const __half *__restrict__ kc,
+                          const __half *__restrict__ vc, int H, int cap, const int *__restrict__ pos_ptr, int pos_off,
+                          OT *__restrict__ out, int ldo, int n_items, unsigned *__restrict__ work,
+                          uint32_t *__restrict__ dev_err) {
+    using namespace stream_attn;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[WARPS][NST];
+    __shared__ int2 meta[WARPS][NST]; // (item, chunk) held by each stage
+    __shared__ int abort_flag;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 3, c = lane & 7;
+    if (tid == 0) abort_flag = 0;
+    if (lane == 0) {
+        for (int s = 0; s < NST; ++s) tc::mbar_init(tc::smem_u32(&full_bar[warp][s]), 1);
+        tc::fence_mbar_init();
+    }
+    __syncthreads();
+    pdl_trigger();
+    pdl_wait();
+    int ctx = (pos_ptr ? *pos_ptr : 0) + pos_off + 1;
+    if (ctx > cap) ctx = cap;
+    const int nch = (ctx + ROWS - 1) / ROWS;
+    const uint32_t ring = ((tc::smem_u32(smem_raw) + 127u) & ~127u) + warp * NST * STAGE_BYTES;
+    uint8_t *ring_gen = smem_raw + (ring - tc::smem_u32(smem_raw));
+
+    auto fetch = [&]() -> int {
+        unsigned v = 0;
+        if (lane == 0) v = atomicAdd(&work[0], 1u);
+        v = __shfl_sync(0xffffffffu, v, 0);
+        return v < (unsigned)n_items ? (int)v : n_items;
+    };
+
+    int p_item = fetch(), p_ch = 0; // next chunk to request
+    int issued = 0, consumed = 0;   // chunks requested / finished by this warp
+    float m = NEG_BIG, l = 0.0f, acc[8], qf[8];
+    bool ok = true;
+
+    while (true) {
+        // keep NST stages requested
+        while (issued - consumed < NST && p_item < n_items) {
+            const int s = issued % NST;
+            if (lane == 0) {
+                const int rows = min(ROWS, ctx - p_ch * ROWS);
+                const uint32_t bar = tc::smem_u32(&full_bar[warp][s]), dst = ring + s * STAGE_BYTES;
+                const size_t off = ((size_t)p_item * cap + (size_t)p_ch * ROWS) * 64;
+                tc::mbar_expect_tx(bar, rows * 256 + (p_ch == 0 ? 64 * (uint32_t)sizeof(QT) : 0u));
+                tc::tma_load_1d(dst, kc + off, rows * 128, bar);
+                tc::tma_load_1d(dst + ROWS * 128, vc + off, rows * 128, bar);
+                if (p_ch == 0) {
+                    const int pb = p_item / H, ph = p_item - pb * H;
+                    tc::tma_load_1d(dst + 2 * ROWS * 128, q + (size_t)pb * ldq + ph * 64, 64 * (uint32_t)sizeof(QT), bar);
+                }
+                meta[warp][s] = make_int2(p_item, p_ch);
+            }
+            ++issued;
+            if (++p_ch == nch) {
+                p_ch = 0;
+                p_item = fetch();
+            }
+        }
+        if (consumed == issued) break;
+        const int s = consumed % NST;
+        ok = tc::mbar_wait(tc::smem_u32(&full_bar[warp][s]), (consumed / NST) & 1, &abort_flag, dev_err, ERR_FULL);
+        if (!ok) break;
+        __syncwarp();
+        const int2 mt = meta[warp][s];
+        const uint8_t *st = ring_gen + s * STAGE_BYTES;
+        if (mt.y == 0) {
+            m = NEG_BIG;
+            l = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+            const QT *qs = reinterpret_cast<const QT *>(st + 2 * ROWS * 128);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) qf[i] = load_as_float<QT>(qs, c * 8 + i) * ATT_SCALE_LOG2E;
+        }
+        const int rows = min(ROWS, ctx - mt.y * ROWS);
+        const uint4 *ks = reinterpret_cast<const uint4 *>(st);
+        const uint4 *vs = reinterpret_cast<const uint4 *>(st + ROWS * 128);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            constexpr int R = 4;
+            uint4 kr[R], vr[R];
+            bool valid[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int row = half * 16 + r * 4 + g;
+                valid[r] = row < rows;
+                kr[r] = make_uint4(0, 0, 0, 0);
+                vr[r] = kr[r];
+                if (valid[r]) {
+                    kr[r] = ks[row * 8 + c];
+                    vr[r] = vs[row * 8 + c];
+                }
+            }
+            float sc[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                float kf[8];
+                half8_to_float(kr[r], kf);
+                float t = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) t = fmaf(qf[i], kf[i], t);
+                sc[r] = t;
+            }
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) {
+#pragma unroll
+                for (int r = 0; r < R; ++r) sc[r] += __shfl_xor_sync(0xffffffffu, sc[r], o);
+            }
+            float m_new = m;
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+                if (valid[r]) m_new = fmaxf(m_new, sc[r]);
+            const float corr = exp2f(m - m_new);
+            l *= corr;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] *= corr;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const float p = valid[r] ? exp2f(sc[r] - m_new) : 0.0f;
+                l += p;
+                float vf[8];
+                half8_to_float(vr[r], vf);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] = fmaf(p, vf[i], acc[i]);
+            }
+            m = m_new;
+        }
+        __syncwarp(); // every lane has read the stage: it may be requested again
+        ++consumed;
+        if (mt.y == nch - 1) {
+            // merge the four lane groups (lanes 8 and 16 apart hold the same 8 dims)
+#pragma unroll
+            for (int off = 8; off <= 16; off <<= 1) {
+                const float m_o = __shfl_xor_sync(0xffffffffu, m, off), l_o = __shfl_xor_sync(0xffffffffu, l, off);
+                const float m_n = fmaxf(m, m_o);
+                const float ws = exp2f(m - m_n), wo = exp2f(m_o - m_n);
+                l = l * ws + l_o * wo;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float a_o = __shfl_xor_sync(0xffffffffu, acc[i], off);
+                    acc[i] = acc[i] * ws + a_o * wo;
+                }
+                m = m_n;
+            }
+            if (g == 0) {
+                const float inv = 1.0f / l;
+                const int ob = mt.x / H, oh = mt.x - ob * H;
+                OT *dst = out + (size_t)ob * ldo + oh * 64 + c * 8;
+                if constexpr (sizeof(OT) == 2) {
+                    uint4 v;
+                    __half2 h0 = __floats2half2_rn(acc[0] * inv, acc[1] * inv), h1 = __floats2half2_rn(acc[2] * inv, acc[3] * inv);
+                    __half2 h2 = __floats2half2_rn(acc[4] * inv, acc[5] * inv), h3 = __floats2half2_rn(acc[6] * inv, acc[7] * inv);
+                    v.x = *reinterpret_cast<uint32_t *>(&h0);
+                    v.y = *reinterpret_cast<uint32_t *>(&h1);
+                    v.z = *reinterpret_cast<uint32_t *>(&h2);
+                    v.w = *reinterpret_cast<uint32_t *>(&h3);
+                    *reinterpret_cast<uint4 *>(dst) = v;
+                } else {
+                    *reinterpret_cast<float4 *>(dst) = make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
+                    *reinterpret_cast<float4 *>(dst + 4) = make_float4(acc[4] * inv, acc[5] * inv, acc[6] * inv, acc[7] * inv);
+                }
+            }
+        }
+    }
+    // Copies still in flight into this block's shared memory must land before the block exits.
+    if (!ok) {
+        for (; consumed < issued; ++consumed) {
+            const uint32_t bar = tc::smem_u32(&full_bar[warp][consumed % NST]);
+            const long long t0 = clock64();
+            while (!tc::mbar_test(bar, (consumed / NST) & 1) && clock64() - t0 < tc::WAIT_CYCLES) { }
+        }
+    }
+    // the last warp of the grid to finish puts the work counters back to zero for the next launch
+    if (lane == 0) {
+        __threadfence();
+        const unsigned done = atomicAdd(&work[1], 1u);
+        if (done == gridDim.x * WARPS - 1) {
+            work[0] = 0u;
+            work[1] = 0u;
+            __threadfence();
+        }
+    }
+}
+
 int launch_decode_attention(b200nn_ctx *ctx, const void *q, bool q_half, int ldq, const __half *kc,
                             const __half *vc, int B, int H, int cap, const int *pos_ptr, int pos_off, void *out,
                             bool out_half, int max_ctx_hint) {
     if (B <= 0) return B200NN_OK;
     int pairs = B * H;
+    const size_t q_elem = q_half ? 2 : 4;
+    if (ctx->attn_stream && pairs >= 3 * ctx->sm_count * stream_attn::WARPS && ((uintptr_t)q & 15) == 0 &&
+        (ldq * q_elem) % 16 == 0 && ((uintptr_t)out & 15) == 0) {
+        const int ldo_s = H * 64;
+        unsigned *work = reinterpret_cast<unsigned *>(ctx->dev_err) + 2;
+#define DS(QT, OT)                                                                                                   \
+    {                                                                                                                \
+        static bool attr_done[16] = {};                                                                              \
+        if (!attr_done[ctx->device & 15]) {                                                                          \
+            CK(ctx, cudaFuncSetAttribute(decode_attn_stream_kernel<QT, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         stream_attn::SMEM_BYTES));                                                  \
+            prefer_max_smem(decode_attn_stream_kernel<QT, OT>);                                                      \
+            attr_done[ctx->device & 15] = true;                                                                      \
+        }                                                                                                            \
+        launch_pdl(ctx, decode_attn_stream_kernel<QT, OT>, dim3(ctx->sm_count), dim3(256), stream_attn::SMEM_BYTES,  \
+                   (const QT *)q, ldq, kc, vc, H, cap, pos_ptr, pos_off, (OT *)out, ldo_s, pairs, work, ctx->dev_err); \
+    }
+        if (q_half && out_half) DS(__half, __half)
+        else if (q_half) DS(__half, float)
+        else if (out_half) DS(float, __half)
+        else DS(float, float)
+#undef DS
+        CK_LAUNCH(ctx, "decode_attn_stream_kernel");
+        return B200NN_OK;
+    }
     int n_splits = (4 * ctx->sm_count + pairs - 1) / pairs;
     int max_splits = (max_ctx_hint + 63) / 64;
     if (n_splits > max_splits) n_splits = max_splits;

@@ -32,8 +32,9 @@ extern "C" int32_t b200nn_ctx_create(int32_t device, b200nn_ctx **out) {
     }
     ctx->sm_count = prop.multiProcessorCount;
     if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess) return fail(e);
-    if ((e = cudaMalloc(&ctx->dev_err, sizeof(uint32_t))) != cudaSuccess) return fail(e);
-    if ((e = cudaMemset(ctx->dev_err, 0, sizeof(uint32_t))) != cudaSuccess) return fail(e);
+    // word 0: device error word; words 2,3: the streaming decode attention's work counters (zero at rest)
+    if ((e = cudaMalloc(&ctx->dev_err, 4 * sizeof(uint32_t))) != cudaSuccess) return fail(e);
+    if ((e = cudaMemset(ctx->dev_err, 0, 4 * sizeof(uint32_t))) != cudaSuccess) return fail(e);
     cudaDriverEntryPointQueryResult qres;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ctx->encode_tiled, cudaEnableDefault, &qres) != cudaSuccess ||
         qres != cudaDriverEntryPointSuccess)
@@ -90,6 +91,7 @@ extern "C" int32_t b200nn_ctx_set_tuning(b200nn_ctx *ctx, const char *key, int32
     else if (!strcmp(key, "tc_min_kb")) ctx->tc_min_kb = value < 1 ? 1 : value;
     else if (!strcmp(key, "pdl")) ctx->pdl = value ? 1 : 0;
     else if (!strcmp(key, "attn_tc")) ctx->attn_tc = value ? 1 : 0;
+    else if (!strcmp(key, "attn_stream")) ctx->attn_stream = value ? 1 : 0;
     else if (!strcmp(key, "trace")) { // value != 0: allocate (once) and clear a 256-slot stamp buffer
         if (value && !ctx->trace && cudaMalloc(&ctx->trace, 256 * sizeof(long long)) != cudaSuccess) return B200NN_ERR_CUDA;
         if (ctx->trace) cudaMemset(ctx->trace, 0, 256 * sizeof(long long));

@@ -49,6 +49,7 @@ struct b200nn_ctx {
     long long *trace = nullptr;   // optional device buffer for in-kernel time stamps (measurement aid)
     uint32_t fam_mask = 0xffffffffu; // kernel families run_blocks / run_head launch (timing aid)
     int attn_tc = 1;              // prefill attention with fp16 q and output runs on the tensor cores
+    int attn_stream = 1;          // decode attention over many (sequence, head) pairs uses the TMA-fed kernel
     int pdl = 1;                  // launch the decode-step kernels with programmatic dependent launch
     bool capturing = false;       // true while a decode step is being captured into a graph
 };

@@ -279,7 +279,8 @@ def run_b200(args):
     attn_bytes_launch = batch * H * ctx_mid * 64 * 2 * 2 + 2 * batch * d * act_b
     lin_flops = sum(2 * batch * k * n for k, n in ((d, 3 * d), (d, d), (d, 4 * d), (4 * d, d))) * L
     roofs = {
-        "attention": {"kernel": "decode_attn_kernel", "bound": "hbm", "unit": "GB/s", "peak": hbm_peak,
+        "attention": {"kernel": "decode_attn_stream_kernel" if batch * H >= 3 * 148 * 8 else "decode_attn_kernel",
+                      "bound": "hbm", "unit": "GB/s", "peak": hbm_peak,
                       "achieved": attn_bytes_launch * L / (fam["attention"] * 1e-3) / 1e9 if fam["attention"] else 0.0},
         "linear": {"kernel": "int4 Linear kernels (4 per layer)", "bound": "hbm", "unit": "GB/s", "peak": hbm_peak,
                    "achieved": lin_bytes / (fam["linear"] * 1e-3) / 1e9 if fam["linear"] else 0.0,

@@ -171,6 +171,41 @@ def test_int4_prefill_attention_tensor_core_long_sequences(reg):
     assert reg.device_error() == 0
 
 
+def test_decode_attention_streaming_kernel_many_sequences(reg):
+    """Enough (sequence, head) pairs to take the TMA-fed decode-attention kernel: 1800 sequences x 2
+    heads, contexts 38..42 (not multiples of the 32-row stage).  Checked against the oracle on a few
+    sequences and against the plain-load kernel on all of them."""
+    cfg = _mini(n_layer=2, d=128, vocab=257, npos=48)
+    w = synth.gpt2_weights(cfg, base_seed=67, std=0.08, random_ln=True)
+    m = Int4Gpt2Model.from_weights(w, cfg, reg)
+    om = oracle.Model(cfg.as_dict(), _int4_oracle_weights(m, cfg, w, False))
+    B, P, N = 1800, 37, 5
+    prompts = synth.token_ids(9, (B, P), cfg.vocab_size)
+
+    def run():
+        s = DecodeSession(m, batch=B, capacity=P + N + 1)
+        s.prefill(prompts)
+        s.step(1)      # eager
+        s.step(N - 2)  # captured and replayed
+        return s.tokens(), s.logits()
+
+    tok_s, lg_s = run()
+    reg.set_tuning("attn_stream", 0)
+    try:
+        tok_p, lg_p = run()
+    finally:
+        reg.set_tuning("attn_stream", 1)
+    assert reg.device_error() == 0
+    assert np.abs(lg_s - lg_p).max() < 2e-3
+    assert (tok_s != tok_p).mean() < 0.01  # near-ties only
+    for b in (0, 1, 777, B - 1):
+        ref, lg = om.generate_cached(prompts[b], N, flags=oracle.KV_FP16, want_logits=True)
+        _check_tokens(np.concatenate([prompts[b], tok_s[b]]), ref, lg, P)
+    # a second session right away: the kernel's work counters must be back at zero
+    tok_again, _ = run()
+    assert np.array_equal(tok_again, tok_s)
+
+
 def test_eos_stops_before_append(reg):
     # a vocabulary large enough to contain id 50256, with the head biased so that it wins
     cfg = Gpt2Config(n_layer=1, n_embd=64, n_head=1, vocab_size=50257, n_positions=32)

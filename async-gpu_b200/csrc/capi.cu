@@ -88,8 +88,7 @@ extern "C" int32_t b200nn_ctx_set_tuning(b200nn_ctx *ctx, const char *key, int32
     if (!ctx || !key) return B200NN_ERR_ARG;
     if (!strcmp(key, "tc_mb")) ctx->tc_mb = value;
     else if (!strcmp(key, "tc_splits")) ctx->tc_splits = value;
-    else if (!strcmp(key, "tc_min_kb")) ctx->tc_min_kb = value < 1 ? 1 : value;
-    else if (!strcmp(key, "pdl")) ctx->pdl = value ? 1 : 0;
+    else if (!strcmp(key, "tc_min_kb")) ctx->tc_min_kb = value < 1 ? 1 : value;    else if (!strcmp(key, "pdl")) ctx->pdl = value ? 1 : 0;
     else if (!strcmp(key, "attn_tc")) ctx->attn_tc = value ? 1 : 0;
     else if (!strcmp(key, "attn_stream")) ctx->attn_stream = value ? 1 : 0;
     else if (!strcmp(key, "trace")) { // value != 0: allocate (once) and clear a 256-slot stamp buffer

@@ -352,12 +352,15 @@ template <int MB, int NS, int NP, int NG, int TC>
 int launch_cfg(b200nn_ctx *ctx, const Int4Weight &w, const __half *x, int M, const Epilogue &epi) {
     constexpr size_t ring = (size_t)NS * MB * 128 + (size_t)NP * TILE_BYTES;
     static_assert(ring >= (size_t)MB * TILE_N * sizeof(float), "epilogue stage must fit in the operand rings");
-    constexpr size_t smem = 1024 + ring + 256 + (size_t)kMaxScaleGroups * TILE_N * sizeof(__half);
-    static_assert(smem <= 227 * 1024, "shared memory budget exceeded");
+    // barriers behind the rings: NP*16 + NS*24 + 16 bytes, then 16-byte alignment of the scale buffer
+    constexpr size_t bar_bytes = 512;
+    static_assert(NP * 16 + NS * 24 + 16 + 16 <= bar_bytes, "barrier area too small");
+    constexpr size_t smem_max = 1024 + ring + bar_bytes + (size_t)kMaxScaleGroups * TILE_N * sizeof(__half);
+    static_assert(smem_max <= 227 * 1024, "shared memory budget exceeded");
     static bool attr_done[16] = {};
     auto kern = int4_gemm_tc_kernel<MB, NS, NP, NG, TC>;
     if (!attr_done[ctx->device & 15]) {
-        CK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        CK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
         prefer_max_smem(kern);
         attr_done[ctx->device & 15] = true;
     }
@@ -374,15 +377,18 @@ int launch_cfg(b200nn_ctx *ctx, const Int4Weight &w, const __half *x, int M, con
 
     const int m_tiles = (M + MB - 1) / MB;
     const int base_ctas = w.n_tiles * m_tiles;
-    const int ctas_per_sm = (smem <= 113 * 1024 && 2 * TC <= 512) ? 2 : 1;
+    // shared memory without the scale buffer, which is sized per launch below; two blocks share an SM
+    // when both their shared memory and their TMEM columns fit twice
+    constexpr size_t smem_fixed = 1024 + ring + bar_bytes;
+    const int ctas_per_sm = (smem_fixed + 8192 <= 113 * 1024 && 2 * TC <= 512) ? 2 : 1;
     // K split: fills the GPU when there are few (feature tile x token tile) pairs.  The residual
     // epilogue reduces its splits with L2 vector adds, which is cheap, so it splits down to
     // tc_min_kb K blocks per block; the other epilogues pay a second pass by the last block and
     // split only when fewer than a quarter of the SMs would otherwise have work.
     const int target = ctx->sm_count * ctas_per_sm;
     int splits = 1;
-    if (epi.mode == EPI_RESID)
-        splits = std::min((target + base_ctas - 1) / base_ctas, std::max(1, w.k_blocks / ctx->tc_min_kb));
+    if (epi.mode == EPI_RESID) // rounded down: one block more than the SMs can hold costs a whole second wave
+        splits = std::min(std::max(1, target / base_ctas), std::max(1, w.k_blocks / ctx->tc_min_kb));
     else if (base_ctas * 4 <= target)
         splits = std::min(target / (2 * base_ctas), std::max(1, w.k_blocks / (2 * ctx->tc_min_kb)));
     splits = std::max(1, std::min(splits, 32));
@@ -393,6 +399,9 @@ int launch_cfg(b200nn_ctx *ctx, const Int4Weight &w, const __half *x, int M, con
     splits = (w.k_blocks + per - 1) / per;
     if (splits > 1 && epi.mode != EPI_RESID)
         TRY(ensure_scratch(ctx, (size_t)base_ctas * splits * MB * TILE_N * sizeof(float), (size_t)base_ctas));
+    // group scales of one block's K range (one extra group on either side for ranges that start or end inside a group)
+    const int sc_groups = std::min(kMaxScaleGroups, per * TILE_K / w.group + 2);
+    const size_t smem = smem_fixed + (size_t)sc_groups * TILE_N * sizeof(__half);
     dim3 grid(w.n_tiles, splits, m_tiles);
     CK(ctx, launch_pdl(ctx, kern, grid, dim3(96 + 128 * NG), smem, (const uint8_t *)w.tiled->p,
                        (const __half *)w.scales_h->p, tmap, M, w.N, w.k_blocks, w.n_pad, w.group, per, epi, ctx->scratch,

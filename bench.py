@@ -212,6 +212,9 @@ def run_b200(args):
     lo, hi = shard_bounds(total, world, rank)
     batch = hi - lo
     reg = b200nn.KernelRegistry(local)
+    for kv in args.tune:
+        key, val = kv.split("=")
+        reg.set_tuning(key, int(val))
     w = synth.gpt2_weights(cfg)
     t0 = time.time()
     model = Int4Gpt2Model.from_weights(w, cfg, reg, flags=b200nn.QUANT_LM_HEAD, group_size=128)
@@ -330,6 +333,8 @@ def run_b200(args):
     }
     if args.layers:
         line["config"]["layers_override"] = args.layers
+    if args.tune:
+        line["config"]["tuning_overrides"] = args.tune
         line["config"]["note"] = "reduced depth for a profiler capture: not a benchmark number"
     if rank == 0 and not args.no_gemv:
         line["gemv"] = gemv_bandwidth(reg, cfg, hbm_peak)
@@ -359,6 +364,8 @@ def main():
     ap.add_argument("--no-gemv", action="store_true", help="skip the dequant-GEMV bandwidth measurement")
     ap.add_argument("--e2e-runs", type=int, default=2)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
+                    help="measurement aid: b200nn_ctx_set_tuning override, e.g. --tune attn_stream=0 (repeatable)")
     ap.add_argument("--cpu-steps", type=int, default=8)
     ap.add_argument("--cpu-prompt", type=int, default=32)
     ap.add_argument("--cpu-max-steps", type=int, default=64)

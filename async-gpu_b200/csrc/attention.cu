@@ -167,8 +167,9 @@ decode_attn_kernel(const QT *__restrict__ q, int ldq, const __half *__restrict__
 // ---------------------------------------------------------------------------------------------
 // decode_attn_stream_kernel: the same computation for many (sequence, head) pairs, fed by TMA.
 //
-// One persistent block per SM, eight warps, each warp an independent pipeline: it takes whole
-// (sequence, head) items from a device-side work counter and streams the item's K and V rows
+// One persistent block per SM, eight warps, each warp an independent pipeline: it takes
+// (sequence, head) items from a device-side work counter (whole items, then half-items for the
+// units the grid finishes on, merged through a small scratch record) and streams the item's K and V rows
 // through its own ring of shared-memory stages with bulk async copies (32 rows of K + 32 rows of V
 // per stage, 8 KB, plus the query row with the item's first stage), always two stages ahead of the
 // rows it is working on.  The memory system therefore sees ~128 KB in flight per SM regardless of
@@ -182,14 +183,15 @@ constexpr int WARPS = 8, NST = 3, ROWS = 32;
 constexpr int STAGE_BYTES = 2 * ROWS * 128 + 256; // K rows, V rows, query row (fp16 or f32)
 constexpr int SMEM_BYTES = WARPS * NST * STAGE_BYTES + 128;
 constexpr uint32_t ERR_FULL = 0x51;
+constexpr int REC_FLOATS = 80; // half-item record: [0] max, [1] sum, [8..71] output (16-byte aligned parts)
 }  // namespace stream_attn
 
 template <typename QT, typename OT>
 __global__ void __launch_bounds__(256, 1)
 decode_attn_stream_kernel(const QT *__restrict__ q, int ldq, const __half *__restrict__ kc,
                           const __half *__restrict__ vc, int H, int cap, const int *__restrict__ pos_ptr, int pos_off,
-                          OT *__restrict__ out, int ldo, int n_items, unsigned *__restrict__ work,
-                          uint32_t *__restrict__ dev_err) {
+                          OT *__restrict__ out, int ldo, int n_items, int pf_items, int split_items,
+                          unsigned *__restrict__ work, float *__restrict__ scratch, unsigned *__restrict__ counters, uint32_t *__restrict__ dev_err) {
     using namespace stream_attn;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[WARPS][NST];
@@ -203,6 +205,21 @@ decode_attn_stream_kernel(const QT *__restrict__ q, int ldq, const __half *__res
     }
     __syncthreads();
     pdl_trigger();
+    // Cached rows older than this step never change, and the projection that runs before this
+    // kernel leaves HBM idle: ask for the K and V rows of the items the grid will work on first to
+    // be brought into L2 while that projection is still running.  The position read here may be one
+    // step behind (the kernel that advances it may not have finished); fewer rows are harmless.
+    if (lane == 0 && pf_items > 0) {
+        int old_rows = (pos_ptr ? *reinterpret_cast<const volatile int *>(pos_ptr) : 0) + pos_off;
+        old_rows = min(max(old_rows, 0), cap);
+        if (old_rows > 0) {
+            const int n_w = gridDim.x * WARPS;
+            for (int it = blockIdx.x * WARPS + warp; it < pf_items; it += n_w) {
+                tc::bulk_prefetch_l2(kc + (size_t)it * cap * 64, (uint32_t)old_rows * 128u);
+                tc::bulk_prefetch_l2(vc + (size_t)it * cap * 64, (uint32_t)old_rows * 128u);
+            }
+        }
+    }
     pdl_wait();
     int ctx = (pos_ptr ? *pos_ptr : 0) + pos_off + 1;
     if (ctx > cap) ctx = cap;
@@ -210,49 +227,78 @@ decode_attn_stream_kernel(const QT *__restrict__ q, int ldq, const __half *__res
     const uint32_t ring = ((tc::smem_u32(smem_raw) + 127u) & ~127u) + warp * NST * STAGE_BYTES;
     uint8_t *ring_gen = smem_raw + (ring - tc::smem_u32(smem_raw));
 
-    auto fetch = [&]() -> int {
-        unsigned v = 0;
-        if (lane == 0) v = atomicAdd(&work[0], 1u);
-        v = __shfl_sync(0xffffffffu, v, 0);
-        return v < (unsigned)n_items ? (int)v : n_items;
+    // Work units, handed out in this order: whole items 0 .. n_full-1, then the last n_warps items
+    // as two half-items each (chunk ranges [0, mid) and [mid, nch)), so that the units the grid
+    // finishes on are half as long and the warps end closer together.  A warp's first unit is its own
+    // index in the grid (what the prefetch before the dependency wait assumed); the rest come from
+    // the shared counter, requested one unit ahead so that the atomic's round trip is never waited for.
+    const int n_warps = gridDim.x * WARPS, gw = blockIdx.x * WARPS + warp;
+    const int n_split = min(split_items, n_items - n_warps); // items handed out as halves
+    const int n_full = n_items - n_split, n_units = n_items + n_split, mid = (nch + 1) / 2;
+    unsigned next_raw = 0; // lane 0: the unit after the current one, already requested
+    if (lane == 0) next_raw = atomicAdd(&work[0], 1u) + (unsigned)n_warps;
+    // the unit being requested: item, chunk range, part (0 whole item, 1 head half, 2 tail half)
+    int p_item = 0, p_ch = 0, p_end = 0, p_part = 0;
+    bool p_valid = false;
+    auto open_unit = [&](unsigned u) {
+        p_valid = u < (unsigned)n_units;
+        if (!p_valid) return;
+        if ((int)u < n_full) {
+            p_item = (int)u; p_ch = 0; p_end = nch; p_part = 0;
+        } else {
+            const int k = (int)u - n_full, half = k & 1;
+            p_item = n_full + (k >> 1);
+            if (nch < 2) { // nothing to halve: the head half is the whole item, the tail half is empty
+                p_ch = 0; p_end = half ? 0 : nch; p_part = 0;
+            } else {
+                p_ch = half ? mid : 0; p_end = half ? nch : mid; p_part = 1 + half;
+            }
+        }
     };
-
-    int p_item = fetch(), p_ch = 0; // next chunk to request
+    auto next_unit = [&]() {
+        do {
+            const unsigned u = __shfl_sync(0xffffffffu, next_raw, 0);
+            if (lane == 0 && u < (unsigned)n_units) next_raw = atomicAdd(&work[0], 1u) + (unsigned)n_warps;
+            open_unit(u);
+        } while (p_valid && p_ch >= p_end); // skip empty units
+    };
+    open_unit((unsigned)gw);
     int issued = 0, consumed = 0;   // chunks requested / finished by this warp
     float m = NEG_BIG, l = 0.0f, acc[8], qf[8];
     bool ok = true;
 
     while (true) {
         // keep NST stages requested
-        while (issued - consumed < NST && p_item < n_items) {
+        while (issued - consumed < NST && p_valid) {
             const int s = issued % NST;
+            const bool first = (p_ch == 0) || (p_part == 2 && p_ch == mid), last = (p_ch == p_end - 1);
             if (lane == 0) {
                 const int rows = min(ROWS, ctx - p_ch * ROWS);
                 const uint32_t bar = tc::smem_u32(&full_bar[warp][s]), dst = ring + s * STAGE_BYTES;
                 const size_t off = ((size_t)p_item * cap + (size_t)p_ch * ROWS) * 64;
-                tc::mbar_expect_tx(bar, rows * 256 + (p_ch == 0 ? 64 * (uint32_t)sizeof(QT) : 0u));
+                tc::mbar_expect_tx(bar, rows * 256 + (first ? 64 * (uint32_t)sizeof(QT) : 0u));
                 tc::tma_load_1d(dst, kc + off, rows * 128, bar);
                 tc::tma_load_1d(dst + ROWS * 128, vc + off, rows * 128, bar);
-                if (p_ch == 0) {
+                if (first) {
                     const int pb = p_item / H, ph = p_item - pb * H;
                     tc::tma_load_1d(dst + 2 * ROWS * 128, q + (size_t)pb * ldq + ph * 64, 64 * (uint32_t)sizeof(QT), bar);
                 }
-                meta[warp][s] = make_int2(p_item, p_ch);
+                meta[warp][s] = make_int2(p_item, p_ch | (first ? 0x100 : 0) | (last ? 0x200 : 0) | (p_part << 10));
             }
             ++issued;
-            if (++p_ch == nch) {
-                p_ch = 0;
-                p_item = fetch();
-            }
+            if (++p_ch == p_end) next_unit();
         }
         if (consumed == issued) break;
         const int s = consumed % NST;
         ok = tc::mbar_wait(tc::smem_u32(&full_bar[warp][s]), (consumed / NST) & 1, &abort_flag, dev_err, ERR_FULL);
         if (!ok) break;
         __syncwarp();
-        const int2 mt = meta[warp][s];
+        const int2 mraw = meta[warp][s];
+        const int2 mt = make_int2(mraw.x, mraw.y & 0xff); // (item, chunk)
+        const bool u_first = (mraw.y & 0x100) != 0, u_last = (mraw.y & 0x200) != 0;
+        const int u_part = mraw.y >> 10;
         const uint8_t *st = ring_gen + s * STAGE_BYTES;
-        if (mt.y == 0) {
+        if (u_first) {
             m = NEG_BIG;
             l = 0.0f;
 #pragma unroll
@@ -316,7 +362,7 @@ decode_attn_stream_kernel(const QT *__restrict__ q, int ldq, const __half *__res
         }
         __syncwarp(); // every lane has read the stage: it may be requested again
         ++consumed;
-        if (mt.y == nch - 1) {
+        if (u_last) {
             // merge the four lane groups (lanes 8 and 16 apart hold the same 8 dims)
 #pragma unroll
             for (int off = 8; off <= 16; off <<= 1) {
@@ -331,7 +377,42 @@ decode_attn_stream_kernel(const QT *__restrict__ q, int ldq, const __half *__res
                 }
                 m = m_n;
             }
-            if (g == 0) {
+            bool write_out = true;
+            if (u_part != 0) {
+                // half of an item: leave a (max, sum, output) record; the half that arrives second on
+                // the item's counter merges both and writes the result
+                const int slot = mt.x - n_full;
+                float *rec = scratch + ((size_t)slot * 2 + (u_part - 1)) * REC_FLOATS;
+                if (g == 0) {
+                    if (c == 0) { rec[0] = m; rec[1] = l; }
+                    *reinterpret_cast<float4 *>(rec + 8 + c * 8) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                    *reinterpret_cast<float4 *>(rec + 12 + c * 8) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+                }
+                __threadfence();
+                __syncwarp();
+                unsigned prev = 0;
+                if (lane == 0) {
+                    prev = atomicAdd(&counters[slot], 1u);
+                    if (prev == 1u) counters[slot] = 0u; // both halves are in: zero at rest again
+                }
+                prev = __shfl_sync(0xffffffffu, prev, 0);
+                write_out = (prev == 1u);
+                if (write_out) {
+                    __threadfence();
+                    const float *oth = scratch + ((size_t)slot * 2 + (2 - u_part)) * REC_FLOATS;
+                    const float m_o = __ldcg(oth), l_o = __ldcg(oth + 1);
+                    const float4 a0 = __ldcg(reinterpret_cast<const float4 *>(oth + 8 + c * 8));
+                    const float4 a1 = __ldcg(reinterpret_cast<const float4 *>(oth + 12 + c * 8));
+                    const float ao[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                    const float m_n = fmaxf(m, m_o);
+                    const float ws = exp2f(m - m_n), wo = exp2f(m_o - m_n);
+                    // separately rounded products and a plain add: the same bits whichever half merges
+                    l = __fadd_rn(__fmul_rn(l, ws), __fmul_rn(l_o, wo));
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(__fmul_rn(acc[i], ws), __fmul_rn(ao[i], wo));
+                }
+            }
+            if (g == 0 && write_out) {
                 const float inv = 1.0f / l;
                 const int ob = mt.x / H, oh = mt.x - ob * H;
                 OT *dst = out + (size_t)ob * ldo + oh * 64 + c * 8;
@@ -377,11 +458,18 @@ int launch_decode_attention(b200nn_ctx *ctx, const void *q, bool q_half, int ldq
     if (B <= 0) return B200NN_OK;
     int pairs = B * H;
     const size_t q_elem = q_half ? 2 : 4;
-    if (ctx->attn_stream && pairs >= 3 * ctx->sm_count * stream_attn::WARPS && ((uintptr_t)q & 15) == 0 &&
+    if (ctx->attn_stream && pairs >= 3 * ctx->sm_count * stream_attn::WARPS && cap <= 255 * stream_attn::ROWS &&
+        ((uintptr_t)q & 15) == 0 &&
         (ldq * q_elem) % 16 == 0 && ((uintptr_t)out & 15) == 0) {
         const int ldo_s = H * 64;
         unsigned *work = reinterpret_cast<unsigned *>(ctx->dev_err) + 2;
-#define DS(QT, OT)                                                                                                   \
+        // records and counters of the half-items the grid finishes on (two halves of n_warps items)
+        const size_t n_w = (size_t)ctx->sm_count * stream_attn::WARPS;
+        TRY(ensure_scratch(ctx, n_w * 2 * stream_attn::REC_FLOATS * sizeof(float), n_w));
+        // items whose cached rows are requested into L2 ahead of the dependency wait
+        const size_t item_bytes = (size_t)2 * cap * 128;
+        const int pf_items = (int)std::min<size_t>((size_t)pairs, ((size_t)ctx->kv_prefetch_mb << 20) / item_bytes);
+#define DS(QT, OT)                                                                                                  \
     {                                                                                                                \
         static bool attr_done[16] = {};                                                                              \
         if (!attr_done[ctx->device & 15]) {                                                                          \
@@ -391,7 +479,9 @@ int launch_decode_attention(b200nn_ctx *ctx, const void *q, bool q_half, int ldq
             attr_done[ctx->device & 15] = true;                                                                      \
         }                                                                                                            \
         launch_pdl(ctx, decode_attn_stream_kernel<QT, OT>, dim3(ctx->sm_count), dim3(256), stream_attn::SMEM_BYTES,  \
-                   (const QT *)q, ldq, kc, vc, H, cap, pos_ptr, pos_off, (OT *)out, ldo_s, pairs, work, ctx->dev_err); \
+                   (const QT *)q, ldq, kc, vc, H, cap, pos_ptr, pos_off, (OT *)out, ldo_s, pairs, pf_items,          \
+                   std::min(ctx->attn_split_items, (int)n_w), work,                                                  \
+                   ctx->scratch, ctx->counters, ctx->dev_err);                                                       \
     }
         if (q_half && out_half) DS(__half, __half)
         else if (q_half) DS(__half, float)

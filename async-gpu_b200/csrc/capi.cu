@@ -54,6 +54,7 @@ extern "C" void b200nn_ctx_destroy(b200nn_ctx *ctx) {
     if (ctx->dev_err) cudaFree(ctx->dev_err);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->counters) cudaFree(ctx->counters);
+    for (void *p : ctx->retired) cudaFree(p);
     pool_trim(ctx);
     {
         std::lock_guard<std::mutex> g(ctx->pool->mu);
@@ -88,9 +89,12 @@ extern "C" int32_t b200nn_ctx_set_tuning(b200nn_ctx *ctx, const char *key, int32
     if (!ctx || !key) return B200NN_ERR_ARG;
     if (!strcmp(key, "tc_mb")) ctx->tc_mb = value;
     else if (!strcmp(key, "tc_splits")) ctx->tc_splits = value;
-    else if (!strcmp(key, "tc_min_kb")) ctx->tc_min_kb = value < 1 ? 1 : value;    else if (!strcmp(key, "pdl")) ctx->pdl = value ? 1 : 0;
+    else if (!strcmp(key, "tc_min_kb")) ctx->tc_min_kb = value < 1 ? 1 : value;
+    else if (!strcmp(key, "pdl")) ctx->pdl = value ? 1 : 0;
     else if (!strcmp(key, "attn_tc")) ctx->attn_tc = value ? 1 : 0;
     else if (!strcmp(key, "attn_stream")) ctx->attn_stream = value ? 1 : 0;
+    else if (!strcmp(key, "kv_prefetch_mb")) ctx->kv_prefetch_mb = value < 0 ? 0 : value;
+    else if (!strcmp(key, "attn_split_items")) ctx->attn_split_items = value < 0 ? 0 : value;
     else if (!strcmp(key, "trace")) { // value != 0: allocate (once) and clear a 256-slot stamp buffer
         if (value && !ctx->trace && cudaMalloc(&ctx->trace, 256 * sizeof(long long)) != cudaSuccess) return B200NN_ERR_CUDA;
         if (ctx->trace) cudaMemset(ctx->trace, 0, 256 * sizeof(long long));

@@ -27,10 +27,13 @@
 //
 // Every wait on an mbarrier is bounded: when it runs out the block records a code in the device
 // error word, all roles leave their loops, TMEM is freed and the kernel returns.
+#include <cooperative_groups.h>
 #include <cuda.h>
 
 #include "device_utils.cuh"
 #include "tc_ptx.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -56,11 +59,11 @@ __device__ __forceinline__ float4 f4_add(float4 a, float4 b) {
 // MB: token-tile width; NS: operand stages (activation tiles in shared memory, dequantised weight
 // tiles in TMEM); NP: packed-weight stages; NG: dequant groups; TC: TMEM columns to allocate.
 template <int MB, int NS, int NP, int NG, int TC>
-__global__ void __launch_bounds__(96 + 128 * NG, 1)
+__global__ void __launch_bounds__(96 + 128 * NG, NG == 2 ? 2 : 1)
 int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict__ scales,
                     const __grid_constant__ CUtensorMap tmap_x, int M, int N, int k_blocks, int n_pad, int group,
-                    int kb_per_split, Epilogue epi, float *__restrict__ scratch, unsigned *__restrict__ counters,
-                    uint32_t *__restrict__ dev_err, long long *__restrict__ trace) {
+                    int kb_per_split, int cluster_mode, Epilogue epi, float *__restrict__ scratch,
+                    unsigned *__restrict__ counters, uint32_t *__restrict__ dev_err, long long *__restrict__ trace) {
 #ifdef B200NN_TRACE
 #define TRACE(slot)                                                                                     \
     do {                                                                                                \
@@ -298,6 +301,10 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
                         if (n4 + 3 < N) atomicAdd(dst + 3, v.w);
                     }
                 }
+            } else if (cluster_mode) {
+                // the K splits of this tile are one thread-block cluster: their staged partial tiles are
+                // summed through distributed shared memory below, where every thread of the block can
+                // take part in the cluster barrier
             } else {
                 float4 *part4 = reinterpret_cast<float4 *>(scratch + (((size_t)tile_lin * splits + split) * MB) * TILE_N);
                 for (int c = w8; c < rows; c += NW) part4[c * 32 + lane] = stage4[c * 32 + lane];
@@ -330,6 +337,37 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
             }
             if (t == 0) TRACE(5);
         }
+    }
+
+    // ---- split K inside a cluster: block `split` finishes the token rows c = split, split+splits, ...
+    //      of the tile, adding the partial rows of all blocks in split order (deterministic).  Both
+    //      cluster barriers are reached by every thread on every path, aborted or not. ----
+    if (cluster_mode) {
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync(); // every block of the cluster has staged its partial tile
+        if (warp >= 3 && !abort_flag) {
+            constexpr int NW = 4 * NG;
+            const int w8 = warp - 3, n4 = nt * TILE_N + lane * 4;
+            float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (epi.bias) {
+                if (n4 < N) b4.x = epi.bias[n4];
+                if (n4 + 1 < N) b4.y = epi.bias[n4 + 1];
+                if (n4 + 2 < N) b4.z = epi.bias[n4 + 2];
+                if (n4 + 3 < N) b4.w = epi.bias[n4 + 3];
+            }
+            Epilogue e2 = epi;
+            if (epi.mode == EPI_QKV && epi.pos_ptr) e2.pos_off = epi.pos_off + *epi.pos_ptr;
+            e2.pos_ptr = nullptr;
+            const float4 *stage4 = reinterpret_cast<const float4 *>(gen_base);
+            const int rows = min(MB, M - mt * MB);
+            for (int c = split + splits * w8; c < rows; c += splits * NW) {
+                float4 sum = b4;
+                for (int sp = 0; sp < splits; ++sp)
+                    sum = f4_add(sum, cluster.map_shared_rank(stage4, sp)[c * 32 + lane]);
+                epi_store4(e2, mt * MB + c, n4, sum, N);
+            }
+        }
+        cluster.sync(); // no block leaves while its shared memory may still be read
     }
 
     // ---- teardown (also the path taken after a wait gave up) ----
@@ -377,35 +415,61 @@ int launch_cfg(b200nn_ctx *ctx, const Int4Weight &w, const __half *x, int M, con
 
     const int m_tiles = (M + MB - 1) / MB;
     const int base_ctas = w.n_tiles * m_tiles;
-    // shared memory without the scale buffer, which is sized per launch below; two blocks share an SM
-    // when both their shared memory and their TMEM columns fit twice
+    // shared memory without the scale buffer, which is sized per launch below
     constexpr size_t smem_fixed = 1024 + ring + bar_bytes;
-    const int ctas_per_sm = (smem_fixed + 8192 <= 113 * 1024 && 2 * TC <= 512) ? 2 : 1;
-    // K split: fills the GPU when there are few (feature tile x token tile) pairs.  The residual
-    // epilogue reduces its splits with L2 vector adds, which is cheap, so it splits down to
-    // tc_min_kb K blocks per block; the other epilogues pay a second pass by the last block and
-    // split only when fewer than a quarter of the SMs would otherwise have work.
+    // Blocks an SM holds at once: two for the variants with two dequant groups (352 threads, built
+    // for at most 93 registers) when their shared memory and TMEM columns fit twice, else one.
+    const int ctas_per_sm = (NG == 2 && smem_fixed + 8192 <= 113 * 1024 && 2 * TC <= 512) ? 2 : 1;
+    // K split: fills the GPU when there are few (feature tile x token tile) pairs.  The count is
+    // rounded down, because one block more than the SMs can hold costs a whole second wave.  The
+    // residual epilogue reduces its splits with L2 vector adds, which is cheap, so it splits down to
+    // tc_min_kb K blocks per block.  The other epilogues need the complete sum: up to eight splits
+    // run as one thread-block cluster and add their partial tiles through distributed shared memory
+    // (a cluster barrier and a few shared-memory reads); more splits than a cluster holds (only by
+    // override) go through scratch, where the last block to arrive makes a second pass.
     const int target = ctx->sm_count * ctas_per_sm;
     int splits = 1;
-    if (epi.mode == EPI_RESID) // rounded down: one block more than the SMs can hold costs a whole second wave
+    if (epi.mode == EPI_RESID)
         splits = std::min(std::max(1, target / base_ctas), std::max(1, w.k_blocks / ctx->tc_min_kb));
-    else if (base_ctas * 4 <= target)
-        splits = std::min(target / (2 * base_ctas), std::max(1, w.k_blocks / (2 * ctx->tc_min_kb)));
+    else
+        splits = std::min(std::min(8, std::max(1, target / base_ctas)), std::max(1, w.k_blocks / (2 * ctx->tc_min_kb)));
     splits = std::max(1, std::min(splits, 32));
     if (ctx->tc_splits > 0) splits = std::min(ctx->tc_splits, w.k_blocks);
     int per = (w.k_blocks + splits - 1) / splits;
     const int per_max = std::max(1, (kMaxScaleGroups - 2) * w.group / TILE_K); // scales must fit their buffer
     per = std::min(per, per_max);
     splits = (w.k_blocks + per - 1) / per;
-    if (splits > 1 && epi.mode != EPI_RESID)
+    const int cluster_mode = (splits > 1 && splits <= 8 && epi.mode != EPI_RESID) ? 1 : 0;
+    if (splits > 1 && epi.mode != EPI_RESID && !cluster_mode)
         TRY(ensure_scratch(ctx, (size_t)base_ctas * splits * MB * TILE_N * sizeof(float), (size_t)base_ctas));
     // group scales of one block's K range (one extra group on either side for ranges that start or end inside a group)
     const int sc_groups = std::min(kMaxScaleGroups, per * TILE_K / w.group + 2);
     const size_t smem = smem_fixed + (size_t)sc_groups * TILE_N * sizeof(__half);
     dim3 grid(w.n_tiles, splits, m_tiles);
-    CK(ctx, launch_pdl(ctx, kern, grid, dim3(96 + 128 * NG), smem, (const uint8_t *)w.tiled->p,
-                       (const __half *)w.scales_h->p, tmap, M, w.N, w.k_blocks, w.n_pad, w.group, per, epi, ctx->scratch,
-                       ctx->counters, ctx->dev_err, ctx->trace));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(96 + 128 * NG);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (cluster_mode) { // the K splits of one tile form a cluster
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1;
+        attr[na].val.clusterDim.y = splits;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    if (ctx->pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    CK(ctx, cudaLaunchKernelEx(&cfg, kern, (const uint8_t *)w.tiled->p, (const __half *)w.scales_h->p, tmap, M, w.N,
+                               w.k_blocks, w.n_pad, w.group, per, cluster_mode, epi, ctx->scratch, ctx->counters,
+                               ctx->dev_err, ctx->trace));
     CK_LAUNCH(ctx, "int4_gemm_tc_kernel");
     return B200NN_OK;
 }

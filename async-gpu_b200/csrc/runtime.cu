@@ -120,7 +120,8 @@ int ensure_scratch(b200nn_ctx *ctx, size_t bytes, size_t counters) {
     if (bytes > ctx->scratch_bytes) {
         if (ctx->capturing) return set_error(ctx, B200NN_ERR_UNSUPPORTED, "scratch would grow during graph capture");
         CK(ctx, cudaStreamSynchronize(ctx->stream));
-        if (ctx->scratch) CK(ctx, cudaFree(ctx->scratch));
+        // a captured decode step may still name the old block: it stays allocated until the context goes
+        if (ctx->scratch) ctx->retired.push_back(ctx->scratch);
         ctx->scratch = nullptr;
         size_t nb = std::max(bytes, (size_t)8 << 20);
         CK(ctx, cudaMalloc(&ctx->scratch, nb));
@@ -129,7 +130,7 @@ int ensure_scratch(b200nn_ctx *ctx, size_t bytes, size_t counters) {
     if (counters > ctx->n_counters) {
         if (ctx->capturing) return set_error(ctx, B200NN_ERR_UNSUPPORTED, "counters would grow during graph capture");
         CK(ctx, cudaStreamSynchronize(ctx->stream));
-        if (ctx->counters) CK(ctx, cudaFree(ctx->counters));
+        if (ctx->counters) ctx->retired.push_back(ctx->counters);
         ctx->counters = nullptr;
         size_t nc = std::max(counters, (size_t)65536);
         CK(ctx, cudaMalloc(&ctx->counters, nc * sizeof(unsigned)));

@@ -115,6 +115,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void *tmap,
                  "l"(tmap), "r"(bar), "r"(x), "r"(y)
                  : "memory");
 }
+// Asks the memory system to bring [gsrc, gsrc+bytes) into L2 (16-byte aligned, size a multiple of
+// 16); nothing is written anywhere and nothing needs to be waited for.
+__device__ __forceinline__ void bulk_prefetch_l2(const void *gsrc, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gsrc), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void prefetch_tmap(const void *tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }

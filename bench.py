@@ -333,9 +333,9 @@ def run_b200(args):
     }
     if args.layers:
         line["config"]["layers_override"] = args.layers
+        line["config"]["note"] = "reduced depth for a profiler capture: not a benchmark number"
     if args.tune:
         line["config"]["tuning_overrides"] = args.tune
-        line["config"]["note"] = "reduced depth for a profiler capture: not a benchmark number"
     if rank == 0 and not args.no_gemv:
         line["gemv"] = gemv_bandwidth(reg, cfg, hbm_peak)
     if world == 1 and not args.no_cpu_baseline:

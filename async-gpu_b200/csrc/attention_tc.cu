@@ -21,7 +21,12 @@ namespace {
 constexpr float SCALE_LOG2E = 0.125f * 1.4426950408889634f;
 constexpr float NEG_BIG = -1.0e30f;
 constexpr uint32_t ERR_ATT_S = 0x41, ERR_ATT_O = 0x42;
-constexpr int TM_COLS = 256;               // S: 0..127, P: 128..191 (fp16 pairs), O_tile: 192..255
+// TMEM columns: S occupies 0..127.  P (fp16 pairs, 64 columns) is written over S's columns 0..63 as
+// the second softmax pass goes along: the 16 P columns of step c0 cover S columns c0/2 .. c0/2+15,
+// all of which that pass has already loaded (a thread only ever touches its own lane).  O_tile
+// takes S's columns 64..127 once every thread is past the softmax.  128 columns per block let the
+// register-limited three blocks per SM be resident.
+constexpr int TM_COLS = 128, P_COL = 0, O_COL = 64;
 constexpr int SMEM_BYTES = 3 * 16384 + 1024; // Q, K, V^T tiles + alignment slack
 
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
@@ -161,7 +166,7 @@ prefill_attn_tc_kernel(const __half *__restrict__ q, int ldq, const __half *__re
                 o[e >> 1] = w0;
                 o[8 + (e >> 1)] = w1;
             }
-            tc::tmem_st_x16(lane_base + 128 + (c0 >> 1), o);
+            tc::tmem_st_x16(lane_base + P_COL + (c0 >> 1), o);
         }
         tc::tmem_st_wait();
         tc::tc_fence_before_sync();
@@ -171,7 +176,7 @@ prefill_attn_tc_kernel(const __half *__restrict__ q, int ldq, const __half *__re
             if (tc::elect_one()) {
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
-                    tc::umma_f16_ts(tmem_base + 192, tmem_base + 128 + 8 * k, dv + (uint64_t)((k >> 2) * (8192 >> 4) + 2 * (k & 3)),
+                    tc::umma_f16_ts(tmem_base + O_COL, tmem_base + P_COL + 8 * k, dv + (uint64_t)((k >> 2) * (8192 >> 4) + 2 * (k & 3)),
                                     idesc_o, k != 0);
                 tc::umma_commit(bar_o);
             }
@@ -186,7 +191,7 @@ prefill_attn_tc_kernel(const __half *__restrict__ q, int ldq, const __half *__re
 #pragma unroll
         for (int c0 = 0; c0 < 64; c0 += 16) {
             uint32_t v[16];
-            tc::tmem_ld_x16(lane_base + 192 + c0, v);
+            tc::tmem_ld_x16(lane_base + O_COL + c0, v);
 #pragma unroll
             for (int e = 0; e < 16; ++e) acc[c0 + e] = fmaf(acc[c0 + e], corr, __uint_as_float(v[e]));
         }

@@ -152,7 +152,8 @@ def gemv_bandwidth(reg, cfg, hbm_peak, iters=96):
     d = cfg.n_embd
     stream = torch.cuda.ExternalStream(reg.stream)
     out = {}
-    for name, (k, n) in {"qkv": (d, 3 * d), "proj": (d, d), "fc": (d, 4 * d), "fcproj": (4 * d, d)}.items():
+    shapes = {"qkv": (d, 3 * d), "proj": (d, d), "fc": (d, 4 * d), "fcproj": (4 * d, d), "lm_head": (d, cfg.vocab_size)}
+    for name, (k, n) in shapes.items():
         packed, scales, _, _ = synth.int4_linear_case(11, 1, k, n, 128)
         copies = max(2, int(256e6 // (k * n / 2)))
         lins = [b200nn.Int4Linear(packed, scales, None, k, n, 128, reg) for _ in range(copies)]
@@ -292,7 +293,11 @@ def run_b200(args):
     dominant = max(("attention", "linear"), key=lambda k2: fam[k2])
     roof = dict(roofs[dominant])
     roof["frac"] = roof["achieved"] / roof["peak"] if roof["peak"] else None
-    roof["traffic"] = None
+    # DRAM bytes per launch: the ratio dram bytes / algorithmic bytes of the kernel's ncu capture on a
+    # smaller case of the same workload (2 layers, context 130: 218.1 MB moved for 213.0 MB), applied
+    # to this launch's algorithmic bytes -- the kernel streams, so its traffic grows with the rows read
+    roof["traffic"] = 1.024 * attn_bytes_launch if dominant == "attention" and batch * H >= 3 * 148 * 8 else None
+    roof["traffic_source"] = "ncu capture at context 130 scaled by rows" if roof["traffic"] else None
     roof["peak_source"] = peak_kind
     roof["launch_ms"] = fam[dominant] / max(1, fam_launches[dominant])
     roof["launches_per_step"] = fam_launches

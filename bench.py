@@ -117,6 +117,10 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
+    # torchrun pins OMP_NUM_THREADS=1 for its workers; this arm is the host-cores baseline and runs
+    # alone (the other ranks have exited), so it takes every core the process may run on.  Set before
+    # the OpenMP runtime of the oracle library is loaded.
+    os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
     from b200nn import synth  # seeded data generator only (numpy); no library code runs on this arm
     from b200nn.gpt2 import Gpt2Config
     preset, total, prompt_len, max_new = WORKLOADS[args.workload]

@@ -93,7 +93,10 @@ B200NN_API int32_t b200nn_ctx_set_gemv_max_rows(b200nn_ctx *ctx, int32_t rows);
 /* Tuning overrides of the tensor-core GEMM's launch policy, for measurements: "tc_mb" (cap of the
  * token-tile width: 16..256, 0 = default), "tc_splits" (K splits, 0 = automatic), "tc_min_kb"
  * (fewest 64-wide K blocks per split), "gemv_max_rows", "pdl" (programmatic dependent launch on/off),
- * "attn_tc" (0 = run fp16 prefill attention on the CUDA cores instead of the tensor cores). */
+ * "attn_tc" (0 = run fp16 prefill attention on the CUDA cores instead of the tensor cores),
+ * "attn_stream" (0 = never use the TMA-fed decode-attention kernel), "kv_prefetch_mb" (KV-cache
+ * megabytes that kernel asks into L2 before its dependency wait), "attn_split_items" (items it
+ * hands out as two halves at the end of the grid; 0 = none). */
 B200NN_API int32_t b200nn_ctx_set_tuning(b200nn_ctx *ctx, const char *key, int32_t value);
 /* Measurement aid: after set_tuning("trace", 1) the first block of the next tensor-core GEMM
  * writes SM-clock stamps of its pipeline events into a 256-slot buffer; this copies it out. */

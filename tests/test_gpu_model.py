@@ -204,6 +204,15 @@ def test_decode_attention_streaming_kernel_many_sequences(reg):
     # a second session right away: the kernel's work counters must be back at zero
     tok_again, _ = run()
     assert np.array_equal(tok_again, tok_s)
+    # the optional half-item hand-out at the end of the grid (two records merged through scratch)
+    reg.set_tuning("attn_split_items", 700)
+    try:
+        tok_h, lg_h = run()
+    finally:
+        reg.set_tuning("attn_split_items", 0)
+    assert np.abs(lg_h - lg_s).max() < 2e-3
+    assert (tok_h != tok_s).mean() < 0.01
+    assert reg.device_error() == 0
 
 
 def test_eos_stops_before_append(reg):

@@ -233,7 +233,7 @@ decode_attn_stream_kernel(const QT *__restrict__ q, int ldq, const __half *__res
     // index in the grid (what the prefetch before the dependency wait assumed); the rest come from
     // the shared counter, requested one unit ahead so that the atomic's round trip is never waited for.
     const int n_warps = gridDim.x * WARPS, gw = blockIdx.x * WARPS + warp;
-    const int n_split = min(split_items, n_items - n_warps); // items handed out as halves
+    const int n_split = max(0, min(split_items, n_items - n_warps)); // items handed out as halves
     const int n_full = n_items - n_split, n_units = n_items + n_split, mid = (nch + 1) / 2;
     unsigned next_raw = 0; // lane 0: the unit after the current one, already requested
     if (lane == 0) next_raw = atomicAdd(&work[0], 1u) + (unsigned)n_warps;
@@ -458,7 +458,8 @@ int launch_decode_attention(b200nn_ctx *ctx, const void *q, bool q_half, int ldq
     if (B <= 0) return B200NN_OK;
     int pairs = B * H;
     const size_t q_elem = q_half ? 2 : 4;
-    if (ctx->attn_stream && pairs >= 3 * ctx->sm_count * stream_attn::WARPS && cap <= 255 * stream_attn::ROWS &&
+    if (ctx->attn_stream && 10LL * pairs >= (long long)ctx->attn_stream_min10 * ctx->sm_count * stream_attn::WARPS &&
+        cap <= 255 * stream_attn::ROWS &&
         ((uintptr_t)q & 15) == 0 &&
         (ldq * q_elem) % 16 == 0 && ((uintptr_t)out & 15) == 0) {
         const int ldo_s = H * 64;

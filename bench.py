@@ -287,7 +287,7 @@ def run_b200(args):
     attn_bytes_launch = batch * H * ctx_mid * 64 * 2 * 2 + 2 * batch * d * act_b
     lin_flops = sum(2 * batch * k * n for k, n in ((d, 3 * d), (d, d), (d, 4 * d), (4 * d, d))) * L
     roofs = {
-        "attention": {"kernel": "decode_attn_stream_kernel" if batch * H >= 3 * 148 * 8 else "decode_attn_kernel",
+        "attention": {"kernel": "decode_attn_stream_kernel" if batch * H >= 2 * 148 * 8 else "decode_attn_kernel",
                       "bound": "hbm", "unit": "GB/s", "peak": hbm_peak,
                       "achieved": attn_bytes_launch * L / (fam["attention"] * 1e-3) / 1e9 if fam["attention"] else 0.0},
         "linear": {"kernel": "int4 Linear kernels (4 per layer)", "bound": "hbm", "unit": "GB/s", "peak": hbm_peak,
@@ -300,7 +300,7 @@ def run_b200(args):
     # DRAM bytes per launch: the ratio dram bytes / algorithmic bytes of the kernel's ncu capture on a
     # smaller case of the same workload (2 layers, context 130: 218.1 MB moved for 213.0 MB), applied
     # to this launch's algorithmic bytes -- the kernel streams, so its traffic grows with the rows read
-    roof["traffic"] = 1.024 * attn_bytes_launch if dominant == "attention" and batch * H >= 3 * 148 * 8 else None
+    roof["traffic"] = 1.024 * attn_bytes_launch if dominant == "attention" and batch * H >= 2 * 148 * 8 else None
     roof["traffic_source"] = "ncu capture at context 130 scaled by rows" if roof["traffic"] else None
     roof["peak_source"] = peak_kind
     roof["launch_ms"] = fam[dominant] / max(1, fam_launches[dominant])

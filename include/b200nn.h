@@ -94,7 +94,8 @@ B200NN_API int32_t b200nn_ctx_set_gemv_max_rows(b200nn_ctx *ctx, int32_t rows);
  * token-tile width: 16..256, 0 = default), "tc_splits" (K splits, 0 = automatic), "tc_min_kb"
  * (fewest 64-wide K blocks per split), "gemv_max_rows", "pdl" (programmatic dependent launch on/off),
  * "attn_tc" (0 = run fp16 prefill attention on the CUDA cores instead of the tensor cores),
- * "attn_stream" (0 = never use the TMA-fed decode-attention kernel), "kv_prefetch_mb" (KV-cache
+ * "attn_stream" (0 = never use the TMA-fed decode-attention kernel), "attn_stream_min10" (tenths of
+ * a (sequence, head) pair per warp of its grid from which it is used; default 20), "kv_prefetch_mb" (KV-cache
  * megabytes that kernel asks into L2 before its dependency wait), "attn_split_items" (items it
  * hands out as two halves at the end of the grid; 0 = none). */
 B200NN_API int32_t b200nn_ctx_set_tuning(b200nn_ctx *ctx, const char *key, int32_t value);

@@ -171,6 +171,21 @@ def test_int4_prefill_attention_tensor_core_long_sequences(reg):
     assert reg.device_error() == 0
 
 
+def test_prefill_attention_tensor_core_seq_1024_12_heads(reg):
+    """GPT-2 Small's attention shape at the longest context: 12 heads, 1024 tokens (8 query tiles x up to
+    8 key tiles per block), two sequences in one cached forward, against the oracle."""
+    cfg = Gpt2Config(n_layer=1, n_embd=768, n_head=12, vocab_size=211, n_positions=1024)
+    w = synth.gpt2_weights(cfg, base_seed=66, std=0.05, random_ln=True)
+    m = Int4Gpt2Model.from_weights(w, cfg, reg)
+    om = oracle.Model(cfg.as_dict(), _int4_oracle_weights(m, cfg, w, False))
+    toks = synth.token_ids(10, (2, 1024), cfg.vocab_size)
+    cache = KvCache(m, batch=2, capacity=1024)
+    got = m.forward_cached(toks, 1024, cache).to_host().reshape(2, 1024, -1)
+    for b in range(2):
+        _check_logits(got[b], om.forward(toks[b], flags=oracle.KV_FP16))
+    assert reg.device_error() == 0
+
+
 def test_decode_attention_streaming_kernel_many_sequences(reg):
     """Enough (sequence, head) pairs to take the TMA-fed decode-attention kernel: 1800 sequences x 2
     heads, contexts 38..42 (not multiples of the 32-row stage).  Checked against the oracle on a few
@@ -213,6 +228,41 @@ def test_decode_attention_streaming_kernel_many_sequences(reg):
     assert np.abs(lg_h - lg_s).max() < 2e-3
     assert (tok_h != tok_s).mean() < 0.01
     assert reg.device_error() == 0
+
+
+@pytest.mark.parametrize("B,P", [(300, 37), (230, 270)])
+def test_decode_attention_medium_batches_both_kernels(reg, B, P):
+    """600 / 460 (sequence, head) pairs, contexts 38.. and 271..: the split-context kernel (the default at
+    this size) against the oracle on a few sequences, and the TMA-fed kernel forced onto the same work
+    (fewer items than warps: some warps of its grid get nothing) against the split kernel on all."""
+    cfg = _mini(n_layer=2, d=128, vocab=257, npos=288)
+    w = synth.gpt2_weights(cfg, base_seed=68, std=0.08, random_ln=True)
+    m = Int4Gpt2Model.from_weights(w, cfg, reg)
+    om = oracle.Model(cfg.as_dict(), _int4_oracle_weights(m, cfg, w, False))
+    N = 5
+    prompts = synth.token_ids(11, (B, P), cfg.vocab_size)
+
+    def run():
+        s = DecodeSession(m, batch=B, capacity=P + N + 1)
+        s.prefill(prompts)
+        s.step(1)
+        s.step(N - 2)
+        return s.tokens(), s.logits()
+
+    tok_b, lg_b = run()
+    reg.set_tuning("attn_stream_min10", 1)
+    try:
+        tok_p, lg_p = run()
+    finally:
+        reg.set_tuning("attn_stream_min10", 20)
+    assert reg.device_error() == 0
+    assert np.abs(lg_b - lg_p).max() < 2e-3
+    assert (tok_b != tok_p).mean() < 0.01
+    for b in (0, B // 2, B - 1):
+        ref, lg = om.generate_cached(prompts[b], N, flags=oracle.KV_FP16, want_logits=True)
+        _check_tokens(np.concatenate([prompts[b], tok_b[b]]), ref, lg, P)
+    tok_again, _ = run()  # the work counters are back at zero
+    assert np.array_equal(tok_again, tok_b)
 
 
 def test_eos_stops_before_append(reg):

@@ -17,13 +17,14 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(os.path.dirname(_HERE), "libb200nn.so")
 
-OK, ERR_SHAPE, ERR_DIM, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE, ERR_ARG = range(7)
+OK, ERR_SHAPE, ERR_DIM, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE, ERR_ARG, ERR_IO, ERR_MISSING = range(9)
 ACT_NONE, ACT_GELU_TANH, ACT_GELU_SIGMOID, ACT_RELU = range(4)
 GELU_SIGMOID, QUANT_LM_HEAD, ARGMAX_LAST, STOP_ON_EOS = 1, 2, 4, 8
 PROF_NAMES = ("embed", "layernorm", "linear", "attention", "lm_head", "argmax")
 
 _KINDS = {ERR_SHAPE: "ShapeMismatch", ERR_DIM: "DimOutOfRange", ERR_UNSUPPORTED: "KernelNotFound",
-          ERR_CUDA: "Cuda", ERR_DEVICE: "DeviceTimeout", ERR_ARG: "InvalidArgument"}
+          ERR_CUDA: "Cuda", ERR_DEVICE: "DeviceTimeout", ERR_ARG: "InvalidArgument", ERR_IO: "Io",
+          ERR_MISSING: "MissingTensor"}
 
 
 class NnError(RuntimeError):
@@ -132,6 +133,14 @@ def load_library() -> C.CDLL:
             "b200nn_session_tokens": (i32, [vp, _u32p, sz, szp]), "b200nn_session_logits": (i32, [vp, _f32p]),
             "b200nn_session_profile_step": (i32, [vp, _f32p, C.POINTER(C.c_uint64)]),
             "b200nn_session_time_family": (i32, [vp, i32, i32, _f32p, C.POINTER(C.c_uint64)]),
+            "b200nn_safetensors_open": (i32, [C.c_char_p, vpp]), "b200nn_safetensors_close": (None, [vp]),
+            "b200nn_safetensors_count": (i32, [vp]),
+            "b200nn_safetensors_info": (i32, [vp, i32, C.POINTER(C.c_char_p), C.POINTER(C.c_char_p), szp, i32,
+                                              C.POINTER(i32), szp]),
+            "b200nn_safetensors_find": (i32, [vp, C.c_char_p]),
+            "b200nn_safetensors_read": (i32, [vp, i32, vp, sz]),
+            "b200nn_safetensors_last_error": (C.c_char_p, []),
+            "b200nn_gpt2_load_safetensors": (i32, [vp, C.c_char_p, C.POINTER(_Cfg), sz, u32, vpp]),
             "b200nn_decode_attention_noalloc": (i32, [i32, vp, vp, vp, vp, i32, i32, i32, i32, vp]),
             "b200nn_noalloc_last_error": (C.c_char_p, []),
             "b200nn_session_destroy": (None, [vp]),
@@ -278,3 +287,4 @@ def _out(reg, rc, h):
 from . import ops  # noqa: E402
 from .layers import Embedding, Int4Linear, LayerNorm, Linear, MultiHeadAttention, GELU  # noqa: E402
 from .gpt2 import Gpt2Config, Gpt2Model, Int4Gpt2Model, KvCache, DecodeSession  # noqa: E402
+from .checkpoint import SafeTensorsFile, TensorInfo, list_tensors, load_all_tensors, load_gpt2_weights  # noqa: E402

@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass
 
 import numpy as np
@@ -128,6 +129,24 @@ class Gpt2Model:
     @classmethod
     def from_weights(cls, weights, config, reg, **kw):
         return cls(weights, config, reg, **kw)
+
+    @classmethod
+    def from_safetensors(cls, path, reg: KernelRegistry, config: Gpt2Config | None = None, flags: int = 0,
+                         group_size: int = 128):
+        """``load_gpt2_weights`` (model.rs:308-386) + ``from_weights`` in the library: an F32 checkpoint
+        with Hugging Face key names.  ``config=None`` reads the shape off the file."""
+        self = cls.__new__(cls)
+        self.reg, self.flags, self._group_size = reg, flags, group_size
+        self.h = C.c_void_p()
+        cc = config._c() if config is not None else None
+        rc = reg.lib.b200nn_gpt2_load_safetensors(reg.h, os.fsencode(path), C.byref(cc) if cc is not None else None,
+                                                  group_size if cls._int4 else 0, flags, C.byref(self.h))
+        reg.check(rc)
+        got = _Cfg()
+        reg.check(reg.lib.b200nn_gpt2_get_config(self.h, C.byref(got)))
+        self.config = Gpt2Config(n_layer=got.n_layer, n_embd=got.n_embd, n_head=got.n_head, vocab_size=got.vocab_size,
+                                 n_positions=got.n_positions, layer_norm_epsilon=got.layer_norm_epsilon)
+        return self
 
     def forward(self, token_ids, seq_len=None) -> GpuTensor:
         t, tp = _u32(token_ids)

@@ -45,7 +45,9 @@ enum {
     B200NN_ERR_UNSUPPORTED = 3, /* NnError::KernelNotFound / unsupported shape */
     B200NN_ERR_CUDA = 4,        /* NnError::Cuda                               */
     B200NN_ERR_DEVICE = 5,      /* a kernel's bounded wait ran out             */
-    B200NN_ERR_ARG = 6          /* null handle / invalid argument              */
+    B200NN_ERR_ARG = 6,         /* null handle / invalid argument              */
+    B200NN_ERR_IO = 7,          /* ModelError::Io / ::SafeTensor (GH/model.rs:30-62): unreadable or malformed file */
+    B200NN_ERR_MISSING = 8      /* ModelError::MissingTensor                   */
 };
 
 /* Activation selector (GH/nn/layers/linear.rs:24-33 `Activation`). */
@@ -309,6 +311,36 @@ B200NN_API int32_t b200nn_session_profile_step(b200nn_session *s, float *times_m
 B200NN_API int32_t b200nn_session_time_family(b200nn_session *s, int32_t family, int32_t reps, float *ms_total,
                                               uint64_t *launches);
 B200NN_API void b200nn_session_destroy(b200nn_session *s);
+
+/* ---- checkpoints: the safetensors container and the GPT-2 loader (GH/model.rs) ------------------ */
+/* The reference reads checkpoints with the `safetensors` crate; these entry points read the same
+ * public format (8-byte little-endian header length, JSON header, raw little-endian data) on the
+ * host.  open() parses and validates the header only; tensors are listed sorted by name as
+ * list_tensors does (model.rs:201-221) and read on demand.  Host-only: no context needed; the text
+ * of the calling thread's last failure comes from b200nn_safetensors_last_error(). */
+typedef struct b200nn_safetensors b200nn_safetensors;
+B200NN_API int32_t b200nn_safetensors_open(const char *path, b200nn_safetensors **out);
+B200NN_API void b200nn_safetensors_close(b200nn_safetensors *st);
+B200NN_API int32_t b200nn_safetensors_count(const b200nn_safetensors *st);
+/* TensorInfo (model.rs:186-198): name, dtype string ("F32", "U32", ...), shape, size in bytes.  The
+ * strings stay valid until close(). */
+B200NN_API int32_t b200nn_safetensors_info(const b200nn_safetensors *st, int32_t index, const char **name,
+                                           const char **dtype, size_t *shape_out, int32_t shape_capacity, int32_t *ndim,
+                                           size_t *nbytes);
+B200NN_API int32_t b200nn_safetensors_find(const b200nn_safetensors *st, const char *name); /* index or -1 */
+/* Raw bytes of one tensor (load_all_tensors, model.rs:388-397, is this over every F32 tensor). */
+B200NN_API int32_t b200nn_safetensors_read(const b200nn_safetensors *st, int32_t index, void *out, size_t capacity_bytes);
+B200NN_API const char *b200nn_safetensors_last_error(void);
+/* load_gpt2_weights (model.rs:308-386) followed by Gpt2Model::from_weights / Int4Gpt2Model::from_weights:
+ * Hugging Face key names (wte.weight, wpe.weight, ln_f.*, h.{i}.ln_1.*, h.{i}.attn.c_attn.*,
+ * h.{i}.attn.c_proj.*, h.{i}.ln_2.*, h.{i}.mlp.c_fc.*, h.{i}.mlp.c_proj.*), every tensor F32 with
+ * exactly the shape the configuration implies (Conv1D weights [in,out]); a missing tensor returns
+ * B200NN_ERR_MISSING, another dtype B200NN_ERR_UNSUPPORTED, another shape B200NN_ERR_SHAPE.  The
+ * reference's loader is fixed to GPT-2 Small; here cfg may be any GPT-2 shape, or NULL to read it
+ * off the file (vocab, width and positions from wte / wpe, layers counted, heads = width / 64).
+ * int4_group 0 builds the f32 model, otherwise the int4 model quantised with that group size. */
+B200NN_API int32_t b200nn_gpt2_load_safetensors(b200nn_ctx *ctx, const char *path, const b200nn_gpt2_config *cfg,
+                                                size_t int4_group, uint32_t flags, b200nn_gpt2 **out);
 
 /* ---- decode attention without any allocation ----------------------------------------------------
  * This entry point has no counterpart in the reference.  It is for callers that cannot let the

@@ -1,0 +1,133 @@
+"""The safetensors reader of the library (host code: runs without a GPU), against files written by
+hand from the format's public description and, where the `safetensors` Python package is present,
+against files written by that package (the format's own implementation)."""
+import json
+import struct
+
+import numpy as np
+import pytest
+
+import b200nn
+from b200nn import checkpoint
+
+_DT = {np.dtype(np.float32): "F32", np.dtype(np.uint32): "U32", np.dtype(np.float16): "F16", np.dtype(np.int64): "I64",
+       np.dtype(np.uint8): "U8"}
+
+
+def write_safetensors(path, tensors, metadata=None, pad_header_to=None):
+    """8-byte little-endian header length, JSON header, raw little-endian data."""
+    header, blobs, off = {}, [], 0
+    if metadata is not None:
+        header["__metadata__"] = metadata
+    for name, a in tensors.items():
+        a = np.asarray(a)
+        b = a.tobytes()  # C order; a 0-d array keeps its empty shape
+        header[name] = {"dtype": _DT[a.dtype], "shape": list(a.shape), "data_offsets": [off, off + len(b)]}
+        blobs.append(b)
+        off += len(b)
+    h = json.dumps(header).encode()
+    if pad_header_to:
+        h += b" " * (pad_header_to - len(h))
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(h)) + h + b"".join(blobs))
+
+
+def _sample():
+    rng = np.random.default_rng(5)
+    return {
+        "wte.weight": rng.standard_normal((7, 4)).astype(np.float32),
+        "h.0.attn.c_attn.weight.int4_packed": rng.integers(0, 2**32, (3, 5), dtype=np.uint32),
+        "scalar": np.array(3.5, dtype=np.float32),
+        "empty": np.zeros((0, 4), dtype=np.float32),
+        'odd "name"\\ é': np.arange(6, dtype=np.int64).reshape(2, 3),
+        "bytes": np.arange(10, dtype=np.uint8),
+        "half": np.array([1.5, -2.0], dtype=np.float16),
+    }
+
+
+def test_list_and_read_hand_written_file(tmp_path):
+    p = tmp_path / "a.safetensors"
+    t = _sample()
+    write_safetensors(p, t, metadata={"format": "pt", "note": "x"}, pad_header_to=1000)
+    infos = checkpoint.list_tensors(p)
+    assert [i.name for i in infos] == sorted(t)  # list_tensors sorts by name
+    with checkpoint.SafeTensorsFile(p) as f:
+        assert len(f) == len(t)
+        for i, ti in enumerate(infos):
+            a = t[ti.name]
+            assert ti.shape == a.shape and ti.dtype == _DT[a.dtype]
+            assert ti.num_elements == a.size and ti.size_bytes == a.nbytes
+            got = f.read(i)
+            assert got.dtype == a.dtype and np.array_equal(got, a)
+            assert f.find(ti.name) == i
+        assert f.find("nope") == -1
+
+
+def test_load_all_tensors_is_f32_only(tmp_path):
+    p = tmp_path / "b.safetensors"
+    good = {"x": np.ones((2, 2), np.float32), "y": np.arange(3, dtype=np.float32)}
+    write_safetensors(p, good)
+    got = checkpoint.load_all_tensors(p)
+    assert set(got) == {"x", "y"} and np.array_equal(got["y"], good["y"])
+    write_safetensors(p, dict(good, z=np.zeros(2, np.float16)))
+    with pytest.raises(b200nn.NnError) as e:
+        checkpoint.load_all_tensors(p)
+    assert e.value.code == b200nn.ERR_UNSUPPORTED and "F16" in str(e.value)
+
+
+def test_reads_files_written_by_the_safetensors_package(tmp_path):
+    st = pytest.importorskip("safetensors.numpy")
+    p = tmp_path / "c.safetensors"
+    t = {k: v for k, v in _sample().items() if v.size}  # the package rejects nothing here; keep it simple
+    st.save_file(t, str(p), metadata={"made_by": "safetensors"})
+    with checkpoint.SafeTensorsFile(p) as f:
+        assert sorted(f.info(i).name for i in range(len(f))) == sorted(t)
+        for i in range(len(f)):
+            ti = f.info(i)
+            assert np.array_equal(f.read(i), t[ti.name]) and ti.shape == t[ti.name].shape
+    back = st.load_file(str(p))
+    assert all(np.array_equal(back[k], t[k]) for k in t)
+
+
+@pytest.mark.parametrize("case", ["missing", "short", "hdr_len", "not_json", "range", "size", "dtype", "dup", "no_offsets"])
+def test_malformed_files_are_rejected(tmp_path, case):
+    p = tmp_path / "bad.safetensors"
+    data = np.arange(4, dtype=np.float32).tobytes()
+
+    def put(header: bytes, body: bytes = data):
+        p.write_bytes(struct.pack("<Q", len(header)) + header + body)
+
+    if case == "missing":
+        pass
+    elif case == "short":
+        p.write_bytes(b"\x01\x02")
+    elif case == "hdr_len":
+        p.write_bytes(struct.pack("<Q", 10**6) + b"{}")
+    elif case == "not_json":
+        put(b"[1,2,3]")
+    elif case == "range":
+        put(json.dumps({"a": {"dtype": "F32", "shape": [8], "data_offsets": [0, 32]}}).encode())
+    elif case == "size":
+        put(json.dumps({"a": {"dtype": "F32", "shape": [3], "data_offsets": [0, 16]}}).encode())
+    elif case == "dtype":
+        put(json.dumps({"a": {"dtype": "Q4", "shape": [4], "data_offsets": [0, 16]}}).encode())
+    elif case == "dup":
+        put(b'{"a":{"dtype":"F32","shape":[2],"data_offsets":[0,8]},"a":{"dtype":"F32","shape":[2],"data_offsets":[8,16]}}')
+    elif case == "no_offsets":
+        put(json.dumps({"a": {"dtype": "F32", "shape": [4]}}).encode())
+    with pytest.raises(b200nn.NnError) as e:
+        checkpoint.SafeTensorsFile(p)
+    assert e.value.code == b200nn.ERR_IO and str(e.value)
+
+
+def test_load_gpt2_weights_key_names(tmp_path):
+    """The dict has the checkpoint's Hugging Face names, with wte / wpe as from_weights expects them."""
+    from b200nn import Gpt2Config, synth
+    cfg = Gpt2Config(n_layer=2, n_embd=64, n_head=1, vocab_size=50, n_positions=16)
+    w = synth.gpt2_weights(cfg, base_seed=3)
+    p = tmp_path / "m.safetensors"
+    write_safetensors(p, {("wte.weight" if k == "wte" else "wpe.weight" if k == "wpe" else k): v for k, v in w.items()})
+    got = checkpoint.load_gpt2_weights(p)
+    assert set(got) == set(w)
+    assert all(np.array_equal(got[k], np.asarray(w[k], np.float32).reshape(got[k].shape)) for k in w)
+    assert got["h.1.mlp.c_fc.weight"].shape == (64, 256)  # Conv1D layout [in,out] kept

@@ -306,6 +306,70 @@ def test_model_errors(reg):
         Gpt2Model.from_weights(w, cfg, reg)
 
 
+def _save_checkpoint(path, w, drop=(), replace=None):
+    """An F32 checkpoint with Hugging Face key names (8-byte header length, JSON header, data)."""
+    import json
+    import struct
+    header, blobs, off = {}, [], 0
+    for k, v in w.items():
+        name = "wte.weight" if k == "wte" else "wpe.weight" if k == "wpe" else k
+        if name in drop:
+            continue
+        a = np.asarray((replace or {}).get(name, v))
+        dt = {np.dtype(np.float32): "F32", np.dtype(np.float16): "F16"}[a.dtype]
+        b = a.tobytes()
+        header[name] = {"dtype": dt, "shape": list(a.shape), "data_offsets": [off, off + len(b)]}
+        blobs.append(b)
+        off += len(b)
+    h = json.dumps(header).encode()
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(h)) + h + b"".join(blobs))
+
+
+def test_models_from_safetensors_checkpoint(reg, tmp_path):
+    """load_gpt2_weights + from_weights inside the library: the same logits as the model built
+    from the same arrays in memory; configuration given or read off the file; the loader's errors."""
+    cfg = _mini(n_layer=2, d=128, vocab=307, npos=40)
+    w = {k: np.asarray(v, np.float32) for k, v in synth.gpt2_weights(cfg, base_seed=95, std=0.08, random_ln=True).items()}
+    d = cfg.n_embd
+    shaped = dict(w)
+    for i in range(cfg.n_layer):  # the checkpoint stores Conv1D weights as [in,out] matrices
+        for nm, (k, n) in {"attn.c_attn.weight": (d, 3 * d), "attn.c_proj.weight": (d, d), "mlp.c_fc.weight": (d, 4 * d),
+                           "mlp.c_proj.weight": (4 * d, d)}.items():
+            shaped[f"h.{i}.{nm}"] = w[f"h.{i}.{nm}"].reshape(k, n)
+    shaped["wte"] = w["wte"].reshape(cfg.vocab_size, d)
+    shaped["wpe"] = w["wpe"].reshape(cfg.n_positions, d)
+    p = tmp_path / "model.safetensors"
+    _save_checkpoint(p, shaped)
+    toks = synth.token_ids(12, (20,), cfg.vocab_size)
+    for cls in (Gpt2Model, Int4Gpt2Model):
+        ref = cls.from_weights(w, cfg, reg).forward(toks).to_host()
+        a = cls.from_safetensors(p, reg, config=cfg)
+        b = cls.from_safetensors(p, reg)  # configuration read off the tensor shapes
+        assert b.config.as_dict() == pytest.approx(cfg.as_dict())
+        # f32: bit for bit; int4: the residual GEMM adds its K splits in arrival order, so last bits move
+        same = np.array_equal if cls is Gpt2Model else (lambda x, y: np.abs(x - y).max() < 1e-4)
+        assert same(a.forward(toks).to_host(), ref)
+        assert same(b.forward(toks).to_host(), ref)
+    assert Int4Gpt2Model.from_safetensors(p, reg).quantized_memory_bytes() > 0
+    # errors of the reference's loader (ModelError, model.rs:30-62)
+    with pytest.raises(b200nn.NnError) as e:
+        Gpt2Model.from_safetensors(tmp_path / "absent.safetensors", reg)
+    assert e.value.code == b200nn.ERR_IO
+    _save_checkpoint(p, shaped, drop=("h.1.mlp.c_proj.bias",))
+    with pytest.raises(b200nn.NnError) as e:
+        Gpt2Model.from_safetensors(p, reg)
+    assert e.value.code == b200nn.ERR_MISSING and "h.1.mlp.c_proj.bias" in str(e.value)
+    _save_checkpoint(p, shaped, replace={"ln_f.bias": shaped["ln_f.bias"].astype(np.float16)})
+    with pytest.raises(b200nn.NnError) as e:
+        Gpt2Model.from_safetensors(p, reg)
+    assert e.value.code == b200nn.ERR_UNSUPPORTED and "F16" in str(e.value)
+    _save_checkpoint(p, shaped, replace={"h.0.attn.c_attn.weight": shaped["h.0.attn.c_attn.weight"].T.copy()})
+    with pytest.raises(b200nn.NnError) as e:
+        Gpt2Model.from_safetensors(p, reg)
+    assert e.value.code == b200nn.ERR_SHAPE
+
+
 def test_gpt2_small_shapes_subset(reg):
     """GPT-2 Small dimensions (d 768, 12 heads, vocab 50257) with 2 layers: int4 + quantised head,
     2 sequences x 6 decode steps against the oracle."""

@@ -133,6 +133,14 @@ def load_library() -> C.CDLL:
             "b200nn_session_tokens": (i32, [vp, _u32p, sz, szp]), "b200nn_session_logits": (i32, [vp, _f32p]),
             "b200nn_session_profile_step": (i32, [vp, _f32p, C.POINTER(C.c_uint64)]),
             "b200nn_session_time_family": (i32, [vp, i32, i32, _f32p, C.POINTER(C.c_uint64)]),
+            "b200nn_simple_rng_new": (C.c_uint64, [C.c_uint64]),
+            "b200nn_simple_rng_next_f32": (C.c_float, [C.POINTER(C.c_uint64)]),
+            "b200nn_top_k_sample": (i32, [_f32p, sz, sz, C.c_float, C.POINTER(C.c_uint64), _u32p]),
+            "b200nn_gpt2_generate_cached_sampling": (i32, [vp, _u32p, sz, sz, sz, C.c_float, C.POINTER(C.c_uint64), _u32p,
+                                                           szp]),
+            "b200nn_gpt2_forward_early_exit": (i32, [vp, _u32p, sz, C.c_float, vpp, C.POINTER(i32)]),
+            "b200nn_gpt2_generate_cached_early_exit": (i32, [vp, _u32p, sz, sz, C.c_float, _u32p, szp, C.POINTER(i32),
+                                                             szp]),
             "b200nn_safetensors_open": (i32, [C.c_char_p, vpp]), "b200nn_safetensors_close": (None, [vp]),
             "b200nn_safetensors_count": (i32, [vp]),
             "b200nn_safetensors_info": (i32, [vp, i32, C.POINTER(C.c_char_p), C.POINTER(C.c_char_p), szp, i32,
@@ -287,4 +295,5 @@ def _out(reg, rc, h):
 from . import ops  # noqa: E402
 from .layers import Embedding, Int4Linear, LayerNorm, Linear, MultiHeadAttention, GELU  # noqa: E402
 from .gpt2 import Gpt2Config, Gpt2Model, Int4Gpt2Model, KvCache, DecodeSession  # noqa: E402
+from .sampling import SimpleRng, top_k_sample  # noqa: E402
 from .checkpoint import SafeTensorsFile, TensorInfo, list_tensors, load_all_tensors, load_gpt2_weights  # noqa: E402

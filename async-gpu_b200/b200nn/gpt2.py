@@ -175,6 +175,35 @@ class Gpt2Model:
     def generate_cached(self, prompt_tokens, max_new_tokens, flags: int = 8):
         return self._gen(self.reg.lib.b200nn_gpt2_generate_cached, prompt_tokens, max_new_tokens, flags)
 
+    def generate_cached_sampling(self, prompt_tokens, max_new_tokens, top_k, temperature, rng: "SimpleRng"):
+        """``generate_cached_sampling`` (gpt2.rs:933-977); ``rng`` advances one draw per token."""
+        p, pp = _u32(prompt_tokens)
+        out = np.zeros(p.size + max_new_tokens, dtype=np.uint32)
+        n = C.c_size_t()
+        self.reg.check(self.reg.lib.b200nn_gpt2_generate_cached_sampling(
+            self.h, pp, p.size, max_new_tokens, top_k, temperature, C.byref(rng.state), out.ctypes.data_as(_u32p),
+            C.byref(n)))
+        return out[: n.value]
+
+    def forward_early_exit(self, token_ids, threshold):
+        """``forward_early_exit`` (gpt2.rs:797-830) -> (logits tensor [seq,vocab], layers used)."""
+        t, tp = _u32(token_ids)
+        h, used = C.c_void_p(), C.c_int32()
+        self.reg.check(self.reg.lib.b200nn_gpt2_forward_early_exit(self.h, tp, t.size, threshold, C.byref(h),
+                                                                   C.byref(used)))
+        return GpuTensor(self.reg, h), int(used.value)
+
+    def generate_cached_early_exit(self, prompt_tokens, max_new_tokens, threshold):
+        """``generate_cached_early_exit`` (gpt2.rs:837-924) -> (tokens, layers used per step, prefill first)."""
+        p, pp = _u32(prompt_tokens)
+        out = np.zeros(p.size + max_new_tokens, dtype=np.uint32)
+        layers = np.zeros(1 + max_new_tokens, dtype=np.int32)
+        n, steps = C.c_size_t(), C.c_size_t()
+        self.reg.check(self.reg.lib.b200nn_gpt2_generate_cached_early_exit(
+            self.h, pp, p.size, max_new_tokens, threshold, out.ctypes.data_as(_u32p), C.byref(n),
+            layers.ctypes.data_as(C.POINTER(C.c_int32)), C.byref(steps)))
+        return out[: n.value], layers[: steps.value]
+
     def generate_batch(self, prompts, max_new_tokens, flags: int = 0):
         """prompts [batch, prompt_len] -> (tokens [batch, prompt_len+max_new], lengths [batch])."""
         p = np.ascontiguousarray(prompts, dtype=np.uint32)

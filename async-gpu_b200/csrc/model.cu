@@ -182,10 +182,15 @@ static inline void prof_mark(b200nn_ctx *ctx, StepProfile *p, int fam) {
 
 int run_blocks(b200nn_gpt2 *m, Workspace &ws, b200nn_kvcache &kv, int B, int S, const int *pos_ptr, int pos_off,
                bool act_half, StepProfile *prof) {
+    return run_blocks_range(m, ws, kv, B, S, pos_ptr, pos_off, act_half, prof, 0, m->cfg.n_layer);
+}
+
+int run_blocks_range(b200nn_gpt2 *m, Workspace &ws, b200nn_kvcache &kv, int B, int S, const int *pos_ptr, int pos_off,
+                     bool act_half, StepProfile *prof, int layer_begin, int layer_end) {
     b200nn_ctx *ctx = m->ctx;
     const int d = m->cfg.n_embd, H = m->cfg.n_head, T = B * S;
     float *x = (float *)ws.x->p;
-    for (int l = 0; l < m->cfg.n_layer; ++l) {
+    for (int l = layer_begin; l < layer_end; ++l) {
         const BlockW &b = m->blocks[l];
         if (ctx->fam_mask & (1u << B200NN_PROF_LAYERNORM)) TRY(launch_layernorm(ctx, x, nullptr, nullptr, (const float *)b.ln1_g->p, (const float *)b.ln1_b->p,
                              m->cfg.layer_norm_epsilon, T, d, ws.ln->p, act_half));

@@ -87,6 +87,9 @@ struct StepProfile {
 // sequence t/S at position pos(t) = *pos_ptr + pos_off + t%S; K and V go straight into `kv`.
 int run_blocks(b200nn_gpt2 *m, Workspace &ws, b200nn_kvcache &kv, int B, int S, const int *pos_ptr, int pos_off,
                bool act_half, StepProfile *prof);
+// The same for blocks [layer_begin, layer_end) only (data-dependent depth: early exit).
+int run_blocks_range(b200nn_gpt2 *m, Workspace &ws, b200nn_kvcache &kv, int B, int S, const int *pos_ptr, int pos_off,
+                     bool act_half, StepProfile *prof, int layer_begin, int layer_end);
 // Final LayerNorm + LM head over `rows` rows of `x` -> ws.logits [rows, vocab].
 int run_head(b200nn_gpt2 *m, Workspace &ws, const float *x, int rows, bool act_half, StepProfile *prof);
 bool model_act_half(const b200nn_gpt2 *m, int rows);

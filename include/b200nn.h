@@ -279,6 +279,35 @@ B200NN_API int32_t b200nn_gpt2_generate_cached(b200nn_gpt2 *m, const uint32_t *p
 B200NN_API int32_t b200nn_gpt2_generate_batch(b200nn_gpt2 *m, const uint32_t *prompts, size_t batch, size_t prompt_len,
                                               size_t max_new, uint32_t flags, uint32_t *out_tokens, size_t *out_lens);
 
+/* ---- data-dependent decoding (gpt2.rs:785-1058) ------------------------------------------------ */
+/* SimpleRng (gpt2.rs:1000-1023): xorshift64; the state is a plain u64 the caller keeps.  _new maps
+ * seed 0 to the reference's fixed non-zero constant; _next_f32 advances the state and returns
+ * (state >> 40) / 2^24 in [0,1). */
+B200NN_API uint64_t b200nn_simple_rng_new(uint64_t seed);
+B200NN_API float b200nn_simple_rng_next_f32(uint64_t *state);
+/* top_k_sample (gpt2.rs:1029-1058) on a host logits vector: logits / max(temperature, 1e-8), the k
+ * largest in the order of a stable descending sort, f32 softmax over them, one draw, cumulative search. */
+B200NN_API int32_t b200nn_top_k_sample(const float *logits, size_t n, size_t k, float temperature, uint64_t *rng_state,
+                                       uint32_t *token_out);
+/* Gpt2Model::generate_cached_sampling (gpt2.rs:933-977): KV-cached decoding of one sequence, every
+ * token drawn with top_k_sample; stops before appending token 50256.  The k candidates are selected
+ * on the device; the draw is the host code above.  out_tokens holds prompt_len+max_new entries. */
+B200NN_API int32_t b200nn_gpt2_generate_cached_sampling(b200nn_gpt2 *m, const uint32_t *prompt, size_t prompt_len,
+                                                        size_t max_new, size_t top_k, float temperature,
+                                                        uint64_t *rng_state, uint32_t *out_tokens, size_t *n_out);
+/* Gpt2Model::forward_early_exit (gpt2.rs:797-830): returns the logits [seq_len,vocab] of the first
+ * block (probed through LN_f + LM head after every block but the last) at which the largest softmax
+ * probability of the last position reaches `threshold`, and the number of blocks run (1..n_layer). */
+B200NN_API int32_t b200nn_gpt2_forward_early_exit(b200nn_gpt2 *m, const uint32_t *ids_host, size_t seq_len,
+                                                  float threshold, b200nn_tensor **logits, int32_t *layers_used);
+/* Gpt2Model::generate_cached_early_exit (gpt2.rs:837-924): greedy (last maximum on ties), prefill with
+ * every layer, each decode step with as many blocks as the probe's confidence asks for; the skipped
+ * layers get zero K/V rows for that position.  layers_per_step holds 1+max_new entries (the prefill
+ * first); *n_steps is how many were written. */
+B200NN_API int32_t b200nn_gpt2_generate_cached_early_exit(b200nn_gpt2 *m, const uint32_t *prompt, size_t prompt_len,
+                                                          size_t max_new, float threshold, uint32_t *out_tokens,
+                                                          size_t *n_out, int32_t *layers_per_step, size_t *n_steps);
+
 /* ---- decode session: the batched generate loop in pieces, state resident on the device -------- */
 /* A session owns a KV cache for `batch` sequences of up to `capacity` positions plus the step
  * buffers.  prefill() runs the prompts and picks the first token; step() runs n greedy decode

@@ -717,3 +717,200 @@ ORC_API void orc_mha_f64(const float *q, size_t q_stride, const float *kc, const
             free(sc);
         }
 }
+
+/* ------------------------------------------------------------------------- */
+/* Data-dependent decoding: sampling and early exit (gpt2.rs:785-1058)        */
+/* ------------------------------------------------------------------------- */
+
+/* SimpleRng (gpt2.rs:1000-1023): xorshift64, seed 0 replaced by a fixed constant. */
+ORC_API uint64_t orc_rng_new(uint64_t seed) { return seed ? seed : 0xDEADBEEFCAFE1234ull; }
+ORC_API float orc_rng_next_f32(uint64_t *s) {
+    uint64_t x = *s;
+    x ^= x << 13;
+    x ^= x >> 7;
+    x ^= x << 17;
+    *s = x;
+    return (float)(x >> 40) / (float)(1ull << 24);
+}
+
+typedef struct { float v; uint32_t i; } orc_cand;
+/* the order a stable descending sort by value leaves: equal values by ascending index */
+static int cand_cmp(const void *a, const void *b) {
+    const orc_cand *x = (const orc_cand *)a, *y = (const orc_cand *)b;
+    if (x->v > y->v) return -1;
+    if (x->v < y->v) return 1;
+    return (x->i > y->i) - (x->i < y->i);
+}
+
+/* top_k_sample (gpt2.rs:1029-1058), f32 as there.  *margin, if non-NULL, receives how far the draw
+ * was from the nearest boundary of the cumulative distribution it fell between (a small margin means
+ * that logits differing in the last bits may pick a neighbouring token). */
+ORC_API uint32_t orc_top_k_sample(const float *logits, size_t n, size_t k, float temperature, uint64_t *rng,
+                                  float *margin) {
+    float temp = temperature < 1e-8f ? 1e-8f : temperature;
+    orc_cand *c = (orc_cand *)malloc(n * sizeof(orc_cand));
+    for (size_t i = 0; i < n; ++i) { c[i].v = logits[i] / temp; c[i].i = (uint32_t)i; }
+    qsort(c, n, sizeof(orc_cand), cand_cmp);
+    if (k > n) k = n;
+    float max_val = c[0].v, sum = 0.0f;
+    float *p = (float *)malloc(k * sizeof(float));
+    for (size_t i = 0; i < k; ++i) { p[i] = expf(c[i].v - max_val); sum += p[i]; }
+    float r = orc_rng_next_f32(rng), cum = 0.0f, prev = 0.0f;
+    uint32_t pick = c[k - 1].i;
+    float mg = 1.0f;
+    for (size_t i = 0; i < k; ++i) {
+        prev = cum;
+        cum += p[i] / sum;
+        if (r < cum) {
+            pick = c[i].i;
+            mg = fminf(r - prev, cum - r);
+            if (i == 0) mg = cum - r;
+            break;
+        }
+    }
+    if (margin) *margin = mg;
+    free(p);
+    free(c);
+    return pick;
+}
+
+/* softmax_max_prob (gpt2.rs:980-985): 1 / sum exp(x - max), f32, summed in index order. */
+ORC_API float orc_softmax_max_prob(const float *x, size_t n) {
+    float mx = -INFINITY, s = 0.0f;
+    for (size_t i = 0; i < n; ++i) if (x[i] > mx) mx = x[i];
+    for (size_t i = 0; i < n; ++i) s += expf(x[i] - mx);
+    return 1.0f / s;
+}
+
+static void logits_row_f32(const orc_model *m, const double *h_row, double *lnf, double *lg, float *out) {
+    size_t d = (size_t)m->cfg.n_embd, V = (size_t)m->cfg.vocab_size;
+    ln_d(h_row, m->lnf_g, m->lnf_b, 1, d, (double)m->cfg.layer_norm_epsilon, lnf);
+    lm_head_row(m, lnf, lg);
+    for (size_t i = 0; i < V; ++i) out[i] = (float)lg[i];
+}
+
+/* generate_cached_sampling (gpt2.rs:933-977).  step_logits [max_new,vocab] f32 and margins [max_new]
+ * are optional. */
+ORC_API int orc_generate_cached_sampling(const orc_model *m, const uint32_t *prompt, int32_t prompt_len,
+                                         int32_t max_new, int32_t top_k, float temperature, uint64_t *rng,
+                                         uint32_t flags, uint32_t *out_tokens, float *step_logits, float *margins) {
+    size_t V = (size_t)m->cfg.vocab_size;
+    if (prompt_len <= 0 || prompt_len + max_new > m->cfg.n_positions || top_k <= 0) return -1;
+    memcpy(out_tokens, prompt, (size_t)prompt_len * sizeof(uint32_t));
+    int n = prompt_len;
+    orc_kv kv;
+    if (kv_alloc(m, (size_t)(prompt_len + max_new), &kv)) return -2;
+    double *lg = (double *)malloc(V * sizeof(double));
+    float *lf = (float *)malloc(V * sizeof(float));
+    for (int step = 0; step < max_new; ++step) {
+        if (step == 0)
+            forward_rows(m, out_tokens, (size_t)n, &kv, (size_t)n - 1, lg, flags);
+        else
+            forward_rows(m, out_tokens + n - 1, 1, &kv, 0, lg, flags);
+        for (size_t i = 0; i < V; ++i) lf[i] = (float)lg[i];
+        if (step_logits) memcpy(step_logits + (size_t)step * V, lf, V * sizeof(float));
+        float mg = 0.0f;
+        uint32_t t = orc_top_k_sample(lf, V, (size_t)top_k, temperature, rng, &mg);
+        if (margins) margins[step] = mg;
+        if (t == 50256u) break;
+        out_tokens[n++] = t;
+    }
+    free(lg);
+    free(lf);
+    kv_free(&kv);
+    return n;
+}
+
+/* forward_early_exit (gpt2.rs:797-830): logits [seq,vocab] f32 of the exit layer; *layers_used in
+ * 1..n_layer; confidences [n_layer-1] (optional) receives the probe value after every block reached. */
+ORC_API int orc_forward_early_exit(const orc_model *m, const uint32_t *tokens, int32_t seq, float threshold,
+                                   uint32_t flags, float *logits_out, int32_t *layers_used, float *confidences) {
+    if (seq <= 0 || seq > m->cfg.n_positions) return -1;
+    size_t d = (size_t)m->cfg.n_embd, H = (size_t)m->cfg.n_head, dh = d / H, V = (size_t)m->cfg.vocab_size, n = (size_t)seq;
+    int L = m->cfg.n_layer;
+    orc_kv kv;
+    if (kv_alloc(m, n, &kv)) return -2;
+    double *h = (double *)malloc(n * d * sizeof(double));
+    double *lnf = (double *)malloc(d * sizeof(double));
+    double *lg = (double *)malloc(V * sizeof(double));
+    embed(m, tokens, n, 0, h);
+    size_t per_layer = H * kv.cap * dh;
+    int used = L;
+    for (int l = 0; l < L; ++l) {
+        block_forward(m, &m->layers[l], h, n, 0, kv.k + (size_t)l * per_layer, kv.v + (size_t)l * per_layer, kv.cap, flags);
+        if (l < L - 1) {
+            logits_row_f32(m, h + (n - 1) * d, lnf, lg, logits_out + (n - 1) * V);
+            float conf = orc_softmax_max_prob(logits_out + (n - 1) * V, V);
+            if (confidences) confidences[l] = conf;
+            if (conf >= threshold) { used = l + 1; break; }
+        }
+    }
+    for (size_t r = 0; r < n; ++r) logits_row_f32(m, h + r * d, lnf, lg, logits_out + r * V);
+    *layers_used = used;
+    free(h); free(lnf); free(lg);
+    kv_free(&kv);
+    return 0;
+}
+
+/* generate_cached_early_exit (gpt2.rs:837-924).  layers_per_step holds 1+max_new entries; returns the
+ * token count, *n_steps the entries written.  min_gap (optional) receives the smallest distance
+ * |confidence - threshold| met, so that a caller can tell a robust run from a borderline one. */
+ORC_API int orc_generate_cached_early_exit(const orc_model *m, const uint32_t *prompt, int32_t prompt_len,
+                                           int32_t max_new, float threshold, uint32_t flags, uint32_t *out_tokens,
+                                           int32_t *layers_per_step, int32_t *n_steps, float *step_logits,
+                                           float *min_gap) {
+    size_t d = (size_t)m->cfg.n_embd, H = (size_t)m->cfg.n_head, dh = d / H, V = (size_t)m->cfg.vocab_size;
+    int L = m->cfg.n_layer;
+    if (prompt_len <= 0 || prompt_len + max_new > m->cfg.n_positions) return -1;
+    memcpy(out_tokens, prompt, (size_t)prompt_len * sizeof(uint32_t));
+    int n = prompt_len, steps = 0;
+    float gap = INFINITY;
+    *n_steps = 0;
+    if (max_new <= 0) return n;
+    orc_kv kv;
+    if (kv_alloc(m, (size_t)(prompt_len + max_new), &kv)) return -2;
+    size_t per_layer = H * kv.cap * dh;
+    double *lg = (double *)malloc(V * sizeof(double));
+    double *lnf = (double *)malloc(d * sizeof(double));
+    double *h = (double *)malloc(d * sizeof(double));
+    float *lf = (float *)malloc(V * sizeof(float));
+    forward_rows(m, out_tokens, (size_t)n, &kv, (size_t)n - 1, lg, flags);
+    layers_per_step[steps++] = L;
+    for (int step = 0;; ++step) {
+        if (step_logits && step < max_new)
+            for (size_t i = 0; i < V; ++i) step_logits[(size_t)step * V + i] = (float)lg[i];
+        uint32_t t = argmax_d(lg, V, 1); /* the model's argmax keeps the last maximum (gpt2.rs:991-997) */
+        if (t == 50256u) break;
+        out_tokens[n++] = t;
+        if (step + 1 >= max_new) break;
+        size_t pos = kv.len;
+        embed(m, &t, 1, pos, h);
+        int used = L;
+        for (int l = 0; l < L; ++l) {
+            block_forward(m, &m->layers[l], h, 1, pos, kv.k + (size_t)l * per_layer, kv.v + (size_t)l * per_layer, kv.cap, flags);
+            if (l < L - 1) {
+                logits_row_f32(m, h, lnf, lg, lf);
+                float conf = orc_softmax_max_prob(lf, V);
+                if (fabsf(conf - threshold) < gap) gap = fabsf(conf - threshold);
+                if (conf >= threshold) {
+                    for (int j = l + 1; j < L; ++j) /* zero K/V rows for the skipped layers (gpt2.rs:897-904) */
+                        for (size_t hh = 0; hh < H; ++hh) {
+                            memset(kv.k + (size_t)j * per_layer + (hh * kv.cap + pos) * dh, 0, dh * sizeof(double));
+                            memset(kv.v + (size_t)j * per_layer + (hh * kv.cap + pos) * dh, 0, dh * sizeof(double));
+                        }
+                    used = l + 1;
+                    break;
+                }
+            }
+        }
+        kv.len += 1;
+        layers_per_step[steps++] = used;
+        ln_d(h, m->lnf_g, m->lnf_b, 1, d, (double)m->cfg.layer_norm_epsilon, lnf);
+        lm_head_row(m, lnf, lg);
+    }
+    *n_steps = steps;
+    if (min_gap) *min_gap = gap;
+    free(lg); free(lnf); free(h); free(lf);
+    kv_free(&kv);
+    return n;
+}

@@ -85,6 +85,23 @@ def lib() -> C.CDLL:
                                       C.POINTER(C.c_double), u32p]
         L.orc_time_decode.restype = C.c_int
         L.orc_mha_f64.argtypes = [f32p, sz, f32p, f32p, sz, sz, sz, sz, sz, f32p]
+        u64p, i32p = C.POINTER(C.c_uint64), C.POINTER(C.c_int32)
+        L.orc_rng_new.argtypes = [C.c_uint64]
+        L.orc_rng_new.restype = C.c_uint64
+        L.orc_rng_next_f32.argtypes = [u64p]
+        L.orc_rng_next_f32.restype = C.c_float
+        L.orc_top_k_sample.argtypes = [f32p, sz, sz, C.c_float, u64p, f32p]
+        L.orc_top_k_sample.restype = C.c_uint32
+        L.orc_softmax_max_prob.argtypes = [f32p, sz]
+        L.orc_softmax_max_prob.restype = C.c_float
+        L.orc_generate_cached_sampling.argtypes = [C.c_void_p, u32p, C.c_int32, C.c_int32, C.c_int32, C.c_float, u64p,
+                                                   C.c_uint32, u32p, f32p, f32p]
+        L.orc_generate_cached_sampling.restype = C.c_int
+        L.orc_forward_early_exit.argtypes = [C.c_void_p, u32p, C.c_int32, C.c_float, C.c_uint32, f32p, i32p, f32p]
+        L.orc_forward_early_exit.restype = C.c_int
+        L.orc_generate_cached_early_exit.argtypes = [C.c_void_p, u32p, C.c_int32, C.c_int32, C.c_float, C.c_uint32, u32p,
+                                                     i32p, i32p, f32p, f32p]
+        L.orc_generate_cached_early_exit.restype = C.c_int
         _lib = L
     return _lib
 
@@ -301,3 +318,68 @@ class Model:
         if rc != 0:
             raise RuntimeError(f"orc_time_decode rc={rc}")
         return float(sec.value), toks
+
+    def generate_cached_sampling(self, prompt, max_new, top_k, temperature, rng: "SimpleRng", flags=0):
+        """generate_cached_sampling (gpt2.rs:933-977) -> (tokens, step logits, margin of every draw)."""
+        p, pp = _u32(prompt)
+        out = np.zeros(p.size + max_new, dtype=np.uint32)
+        lg = np.zeros((max_new, self.vocab), dtype=np.float32)
+        mg = np.ones(max_new, dtype=np.float32)
+        n = lib().orc_generate_cached_sampling(self._h, pp, p.size, max_new, top_k, temperature, C.byref(rng.state), flags,
+                                               out.ctypes.data_as(C.POINTER(C.c_uint32)),
+                                               lg.ctypes.data_as(C.POINTER(C.c_float)),
+                                               mg.ctypes.data_as(C.POINTER(C.c_float)))
+        if n < 0:
+            raise RuntimeError(f"orc_generate_cached_sampling rc={n}")
+        return out[:n], lg, mg
+
+    def forward_early_exit(self, tokens, threshold, flags=0):
+        """forward_early_exit (gpt2.rs:797-830) -> (logits [seq,vocab], layers used, probe confidences)."""
+        t, tp = _u32(tokens)
+        out = np.empty((t.size, self.vocab), dtype=np.float32)
+        used = C.c_int32()
+        conf = np.full(max(self.cfg.n_layer - 1, 1), np.nan, dtype=np.float32)
+        rc = lib().orc_forward_early_exit(self._h, tp, t.size, threshold, flags, out.ctypes.data_as(C.POINTER(C.c_float)),
+                                          C.byref(used), conf.ctypes.data_as(C.POINTER(C.c_float)))
+        if rc != 0:
+            raise RuntimeError(f"orc_forward_early_exit rc={rc}")
+        return out, int(used.value), conf
+
+    def generate_cached_early_exit(self, prompt, max_new, threshold, flags=0):
+        """generate_cached_early_exit (gpt2.rs:837-924) -> (tokens, layers per step, step logits, smallest
+        |confidence - threshold| met)."""
+        p, pp = _u32(prompt)
+        out = np.zeros(p.size + max_new, dtype=np.uint32)
+        layers = np.zeros(1 + max_new, dtype=np.int32)
+        steps, gap = C.c_int32(), C.c_float()
+        lg = np.zeros((max(max_new, 1), self.vocab), dtype=np.float32)
+        n = lib().orc_generate_cached_early_exit(self._h, pp, p.size, max_new, threshold, flags,
+                                                 out.ctypes.data_as(C.POINTER(C.c_uint32)),
+                                                 layers.ctypes.data_as(C.POINTER(C.c_int32)), C.byref(steps),
+                                                 lg.ctypes.data_as(C.POINTER(C.c_float)), C.byref(gap))
+        if n < 0:
+            raise RuntimeError(f"orc_generate_cached_early_exit rc={n}")
+        return out[:n], layers[: steps.value], lg, float(gap.value)
+
+
+class SimpleRng:
+    """SimpleRng (gpt2.rs:1000-1023)."""
+
+    def __init__(self, seed: int):
+        self.state = C.c_uint64(lib().orc_rng_new(seed))
+
+    def next_f32(self) -> float:
+        return float(lib().orc_rng_next_f32(C.byref(self.state)))
+
+
+def top_k_sample(logits, k, temperature, rng: SimpleRng):
+    """top_k_sample (gpt2.rs:1029-1058) -> (token, margin of the draw)."""
+    a, ap = _f32(logits)
+    mg = C.c_float()
+    t = lib().orc_top_k_sample(ap, a.size, k, temperature, C.byref(rng.state), C.byref(mg))
+    return int(t), float(mg.value)
+
+
+def softmax_max_prob(logits):
+    a, ap = _f32(logits)
+    return float(lib().orc_softmax_max_prob(ap, a.size))

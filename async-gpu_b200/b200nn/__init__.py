@@ -133,6 +133,9 @@ def load_library() -> C.CDLL:
             "b200nn_session_tokens": (i32, [vp, _u32p, sz, szp]), "b200nn_session_logits": (i32, [vp, _f32p]),
             "b200nn_session_profile_step": (i32, [vp, _f32p, C.POINTER(C.c_uint64)]),
             "b200nn_session_time_family": (i32, [vp, i32, i32, _f32p, C.POINTER(C.c_uint64)]),
+            "b200nn_gpt2_forward_features": (i32, [vp, _u32p, sz, vpp]),
+            "b200nn_gpt2_embedding_table": (i32, [vp, vpp, vpp]),
+            "b200nn_gpt2_forward_profiled": (i32, [vp, _u32p, sz, vpp, _f32p, i32, C.POINTER(i32)]),
             "b200nn_simple_rng_new": (C.c_uint64, [C.c_uint64]),
             "b200nn_simple_rng_next_f32": (C.c_float, [C.POINTER(C.c_uint64)]),
             "b200nn_top_k_sample": (i32, [_f32p, sz, sz, C.c_float, C.POINTER(C.c_uint64), _u32p]),

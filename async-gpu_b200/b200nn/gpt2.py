@@ -155,6 +155,33 @@ class Gpt2Model:
         self.reg.check(self.reg.lib.b200nn_gpt2_forward(self.h, tp, n, C.byref(h)))
         return GpuTensor(self.reg, h)
 
+    def forward_auto_fused(self, token_ids, seq_len=None) -> GpuTensor:
+        """``forward_auto_fused`` (gpt2.rs:500-522): here every forward already runs the fused epilogues."""
+        return self.forward(token_ids, seq_len)
+
+    def forward_features(self, token_ids) -> GpuTensor:
+        """``forward_features`` (gpt2.rs:570-581): [seq, n_embd] after the final LayerNorm."""
+        t, tp = _u32(token_ids)
+        h = C.c_void_p()
+        self.reg.check(self.reg.lib.b200nn_gpt2_forward_features(self.h, tp, t.size, C.byref(h)))
+        return GpuTensor(self.reg, h)
+
+    def embedding_table(self):
+        """``embedding_table`` (gpt2.rs:584-586) -> (wte [vocab,d], wpe [positions,d]) on the device."""
+        a, b = C.c_void_p(), C.c_void_p()
+        self.reg.check(self.reg.lib.b200nn_gpt2_embedding_table(self.h, C.byref(a), C.byref(b)))
+        return GpuTensor(self.reg, a), GpuTensor(self.reg, b)
+
+    def forward_profiled(self, token_ids):
+        """``forward_profiled`` (gpt2.rs:529-568) -> (logits, [(component, milliseconds), ...])."""
+        t, tp = _u32(token_ids)
+        n_max = self.config.n_layer + 3
+        times = (C.c_float * n_max)()
+        h, n = C.c_void_p(), C.c_int32()
+        self.reg.check(self.reg.lib.b200nn_gpt2_forward_profiled(self.h, tp, t.size, C.byref(h), times, n_max, C.byref(n)))
+        names = ["embedding"] + [f"block_{i}" for i in range(self.config.n_layer)] + ["ln_f", "lm_head"]
+        return GpuTensor(self.reg, h), list(zip(names, [float(times[i]) for i in range(n.value)]))
+
     def forward_cached(self, token_ids, new_len, cache: KvCache) -> GpuTensor:
         t, tp = _u32(token_ids)
         h = C.c_void_p()

@@ -391,3 +391,112 @@ extern "C" int32_t b200nn_gpt2_generate_cached_early_exit(b200nn_gpt2 *m, const 
     *n_steps = steps;
     return B200NN_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// forward_features, embedding_table, forward_profiled (gpt2.rs:529-590)
+// ---------------------------------------------------------------------------------------------
+
+// Gpt2Model::forward_features (gpt2.rs:570-581): the hidden states after every block and the final
+// LayerNorm, [seq_len, n_embd] f32, for callers that bring their own head.
+extern "C" int32_t b200nn_gpt2_forward_features(b200nn_gpt2 *m, const uint32_t *ids_host, size_t seq_len,
+                                                b200nn_tensor **features) {
+    if (!m || !ids_host || !features) return B200NN_ERR_ARG;
+    b200nn_ctx *ctx = m->ctx;
+    if (seq_len == 0 || seq_len > (size_t)m->cfg.n_positions)
+        return set_error(ctx, B200NN_ERR_DIM, "forward_features: seq_len must be in [1, n_positions]");
+    CK(ctx, cudaSetDevice(ctx->device));
+    const int S = (int)seq_len, d = m->cfg.n_embd;
+    CacheGuard g;
+    TRY(b200nn_kvcache_create(m, 1, seq_len, &g.c));
+    Workspace ws;
+    TRY(workspace_alloc(m, seq_len, 1, &ws));
+    TRY(embed_one(m, ws, ids_host, S, 0));
+    TRY(run_blocks(m, ws, *g.c, 1, S, nullptr, 0, model_act_half(m, S), nullptr));
+    b200nn_tensor *t = nullptr;
+    TRY(tensor_alloc(ctx, {seq_len, (size_t)d}, false, &t));
+    int rc = launch_layernorm(ctx, (const float *)ws.x->p, nullptr, nullptr, (const float *)m->lnf_g->p,
+                              (const float *)m->lnf_b->p, m->cfg.layer_norm_epsilon, S, d, t->buf->p, false);
+    cudaError_t e = rc == B200NN_OK ? cudaStreamSynchronize(ctx->stream) : cudaSuccess;
+    if (rc != B200NN_OK || e != cudaSuccess) {
+        delete t;
+        return rc != B200NN_OK ? rc : set_cuda_error(ctx, e, "forward_features");
+    }
+    *features = t;
+    return B200NN_OK;
+}
+
+// Gpt2Model::embedding_table (gpt2.rs:584-586): the token and position tables as tensors sharing the
+// model's device buffers ([vocab, n_embd] and [n_positions, n_embd]); destroy them like any tensor.
+extern "C" int32_t b200nn_gpt2_embedding_table(b200nn_gpt2 *m, b200nn_tensor **wte, b200nn_tensor **wpe) {
+    if (!m || !wte || !wpe) return B200NN_ERR_ARG;
+    const size_t d = (size_t)m->cfg.n_embd;
+    auto view = [&](const std::shared_ptr<DevBuf> &buf, size_t rows) {
+        auto *t = new b200nn_tensor();
+        t->ctx = m->ctx;
+        t->buf = buf;
+        t->shape = {rows, d};
+        t->numel = rows * d;
+        return t;
+    };
+    *wte = view(m->wte, (size_t)m->cfg.vocab_size);
+    *wpe = view(m->wpe, (size_t)m->cfg.n_positions);
+    return B200NN_OK;
+}
+
+// Gpt2Model::forward_profiled (gpt2.rs:529-568): forward with the device time of every component,
+// in the reference's order: embedding, block_0 .. block_{L-1}, ln_f, lm_head (CUDA events on the
+// context's stream instead of the reference's host clock around synchronisations).
+extern "C" int32_t b200nn_gpt2_forward_profiled(b200nn_gpt2 *m, const uint32_t *ids_host, size_t seq_len,
+                                                b200nn_tensor **logits, float *times_ms, int32_t capacity,
+                                                int32_t *n_times) {
+    if (!m || !ids_host || !logits || !times_ms || !n_times) return B200NN_ERR_ARG;
+    b200nn_ctx *ctx = m->ctx;
+    const int L = m->cfg.n_layer, S = (int)seq_len, V = m->cfg.vocab_size;
+    if (seq_len == 0 || seq_len > (size_t)m->cfg.n_positions)
+        return set_error(ctx, B200NN_ERR_DIM, "forward_profiled: seq_len must be in [1, n_positions]");
+    if (capacity < L + 3) return set_error(ctx, B200NN_ERR_SHAPE, "forward_profiled: times_ms needs n_layer + 3 entries");
+    CK(ctx, cudaSetDevice(ctx->device));
+    CacheGuard g;
+    TRY(b200nn_kvcache_create(m, 1, seq_len, &g.c));
+    Workspace ws;
+    TRY(workspace_alloc(m, seq_len, seq_len, &ws));
+    const bool ah = model_act_half(m, S);
+    std::vector<cudaEvent_t> ev((size_t)L + 4);
+    for (auto &e : ev) CK(ctx, cudaEventCreate(&e));
+    auto cleanup = [&]() { for (auto &e : ev) cudaEventDestroy(e); };
+    int rc = B200NN_OK;
+    size_t k = 0;
+    auto mark = [&]() { cudaEventRecord(ev[k++], ctx->stream); };
+    mark();
+    rc = embed_one(m, ws, ids_host, S, 0);
+    mark();
+    for (int l = 0; l < L && rc == B200NN_OK; ++l) {
+        rc = run_blocks_range(m, ws, *g.c, 1, S, nullptr, 0, ah, nullptr, l, l + 1);
+        mark();
+    }
+    StepProfile head; // run_head marks after the final LayerNorm and after the LM head
+    if (rc == B200NN_OK) rc = run_head(m, ws, (const float *)ws.x->p, S, ah, &head);
+    b200nn_tensor *t = nullptr;
+    if (rc == B200NN_OK) rc = tensor_alloc(ctx, {seq_len, (size_t)V}, false, &t);
+    if (rc == B200NN_OK) {
+        cudaError_t e = cudaMemcpyAsync(t->buf->p, ws.logits->p, t->numel * 4, cudaMemcpyDeviceToDevice, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) rc = set_cuda_error(ctx, e, "forward_profiled copy");
+    }
+    if (rc == B200NN_OK && head.ev.size() == 2) {
+        for (int i = 0; i < L + 1; ++i) cudaEventElapsedTime(&times_ms[i], ev[i], ev[i + 1]);
+        cudaEventElapsedTime(&times_ms[L + 1], ev[L + 1], head.ev[0]);
+        cudaEventElapsedTime(&times_ms[L + 2], head.ev[0], head.ev[1]);
+        *n_times = L + 3;
+    } else if (rc == B200NN_OK) {
+        rc = set_error(ctx, B200NN_ERR_CUDA, "forward_profiled: missing head events");
+    }
+    for (auto &e : head.ev) cudaEventDestroy(e);
+    cleanup();
+    if (rc != B200NN_OK) {
+        delete t;
+        return rc;
+    }
+    *logits = t;
+    return B200NN_OK;
+}

@@ -279,6 +279,20 @@ B200NN_API int32_t b200nn_gpt2_generate_cached(b200nn_gpt2 *m, const uint32_t *p
 B200NN_API int32_t b200nn_gpt2_generate_batch(b200nn_gpt2 *m, const uint32_t *prompts, size_t batch, size_t prompt_len,
                                               size_t max_new, uint32_t flags, uint32_t *out_tokens, size_t *out_lens);
 
+/* Gpt2Model::forward_features (gpt2.rs:570-581): hidden states after every block and the final
+ * LayerNorm, [seq_len, n_embd] f32, for callers that bring their own head (LoRA, retrieval). */
+B200NN_API int32_t b200nn_gpt2_forward_features(b200nn_gpt2 *m, const uint32_t *ids_host, size_t seq_len,
+                                                b200nn_tensor **features);
+/* Gpt2Model::embedding_table (gpt2.rs:584-586): wte [vocab,n_embd] and wpe [n_positions,n_embd] as
+ * tensors that share the model's device buffers; destroy them with b200nn_tensor_destroy. */
+B200NN_API int32_t b200nn_gpt2_embedding_table(b200nn_gpt2 *m, b200nn_tensor **wte, b200nn_tensor **wpe);
+/* Gpt2Model::forward_profiled (gpt2.rs:529-568): forward plus the device time in milliseconds of
+ * every component in the reference's order: embedding, block_0 .. block_{L-1}, ln_f, lm_head
+ * (n_layer + 3 values; `capacity` is the length of times_ms). */
+B200NN_API int32_t b200nn_gpt2_forward_profiled(b200nn_gpt2 *m, const uint32_t *ids_host, size_t seq_len,
+                                                b200nn_tensor **logits, float *times_ms, int32_t capacity,
+                                                int32_t *n_times);
+
 /* ---- data-dependent decoding (gpt2.rs:785-1058) ------------------------------------------------ */
 /* SimpleRng (gpt2.rs:1000-1023): xorshift64; the state is a plain u64 the caller keeps.  _new maps
  * seed 0 to the reference's fixed non-zero constant; _next_f32 advances the state and returns

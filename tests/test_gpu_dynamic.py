@@ -78,6 +78,36 @@ def test_sampling_stops_before_eos(reg):
     assert np.array_equal(got, ref) and 50256 not in got.tolist() and len(got) < 9
 
 
+def test_forward_features_embedding_table_and_profiled(reg):
+    """forward_features (gpt2.rs:570-581), embedding_table (584-586), forward_profiled (529-568)."""
+    cfg = _mini(n_layer=3)
+    w = synth.gpt2_weights(cfg, base_seed=107, std=0.1, random_ln=True)
+    m = Gpt2Model.from_weights(w, cfg, reg)
+    toks = synth.token_ids(24, (13,), cfg.vocab_size)
+    logits = m.forward(toks).to_host()
+    wte_t, wpe_t = m.embedding_table()
+    wte = np.asarray(w["wte"], np.float32).reshape(cfg.vocab_size, cfg.n_embd)
+    assert wte_t.shape() == (cfg.vocab_size, cfg.n_embd) and np.array_equal(wte_t.to_host(), wte)
+    assert np.array_equal(wpe_t.to_host(), np.asarray(w["wpe"], np.float32).reshape(cfg.n_positions, cfg.n_embd))
+    feats = m.forward_features(toks)
+    assert feats.shape() == (13, cfg.n_embd)
+    # the tied LM head applied by hand to the features gives the model's logits
+    by_hand = feats.to_host().astype(np.float64) @ wte.astype(np.float64).T
+    assert np.abs(by_hand - logits).max() < 1e-3
+    # and the features are the oracle's last hidden state: check through the oracle's logits
+    ref = oracle.Model(cfg.as_dict(), w).forward(toks, flags=oracle.KV_FP16)
+    assert np.abs(by_hand - ref).max() < 2e-2 and np_ref.rel_rms(by_hand.astype(np.float32), ref) < 1e-3
+    lg, timings = m.forward_profiled(toks)
+    assert [n for n, _ in timings] == ["embedding", "block_0", "block_1", "block_2", "ln_f", "lm_head"]
+    assert all(t > 0 for _, t in timings)
+    assert np.abs(lg.to_host() - logits).max() < 1e-5
+    assert np.array_equal(m.forward_auto_fused(toks).to_host(), logits)
+    with pytest.raises(b200nn.NnError):
+        m.forward_features(np.zeros(cfg.n_positions + 1, np.uint32))
+    del wte_t, wpe_t  # views on the model's buffers: the model stays usable
+    assert np.array_equal(m.forward(toks).to_host(), logits)
+
+
 @pytest.mark.parametrize("int4", [False, True])
 def test_forward_early_exit(reg, int4):
     cfg, m, om, oflags = _models(reg, int4, 103)

@@ -75,6 +75,13 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
     constexpr int X_BYTES = MB * 128;
     constexpr int DQ = 128 * NG; // dequant / epilogue threads
     static_assert(MB + NS * A_COLS <= TC, "TMEM budget exceeded");
+    // A dequant group waits for "the MMAs of K block i-NS have retired" by the phase parity of that
+    // stage's barrier.  Parity only tells the last two phases apart, so the barrier must never be two
+    // phases behind the waiter: the group's previous K block (i-NG) has already waited for the MMAs of
+    // K block i-NG-NS, MMAs retire in order, hence K block i-2*NS has retired whenever NS >= NG.
+    // (With 3 operand stages and 4 groups a group that ran ahead took the phase before last for its
+    // own, overwrote a live TMEM stage and unbalanced the barrier's transaction count: the launch failed.)
+    static_assert(NS >= NG && NP >= NG, "fewer stages than dequant groups: phase parity would alias");
     extern __shared__ uint8_t smem_raw[];
     __shared__ int abort_flag;
     __shared__ int is_last;

@@ -21,6 +21,18 @@ tokens = synth.token_ids(77, (10,), TINY["vocab_size"])
 logits = m.forward(tokens)
 generated, _ = m.generate_cached(tokens[:5], 8)
 p, s = oracle.quantize_weight_int4(w["h.0.mlp.c_fc.weight"], 128, 512, 128)
+# data-dependent decoding: one sampled run and one early-exit run (threshold = the median probe confidence)
+sampled, _, _ = m.generate_cached_sampling(tokens[:5], 10, 20, 0.8, oracle.SimpleRng(2026))
+rng = oracle.SimpleRng(7)
+rng_draws = np.array([rng.next_f32() for _ in range(8)], dtype=np.float32)
+conf = m.forward_early_exit(tokens, 2.0)[2]
+for factor in (1.0, 0.9, 0.8, 0.7, 0.6, 0.5, 1.2, 1.5):  # the first threshold that gives steps of both depths
+    threshold = np.float32(np.median(conf) * factor)
+    ee_tokens, ee_layers, _, gap = m.generate_cached_early_exit(tokens[:5], 10, float(threshold))
+    if len(set(ee_layers[1:].tolist())) == 2 and gap > 1e-4:
+        break
 np.savez_compressed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "tiny_gpt2_golden.npz"),
-                    seed=SEED, tokens=tokens, logits=logits, generated=generated, fc_packed=p, fc_scales=s)
-print("written", logits.shape, generated)
+                    seed=SEED, tokens=tokens, logits=logits, generated=generated, fc_packed=p, fc_scales=s,
+                    sampled=sampled, rng_draws=rng_draws, probe_conf=conf, ee_threshold=threshold,
+                    ee_tokens=ee_tokens, ee_layers=ee_layers)
+print("written", logits.shape, generated, sampled, ee_layers)

@@ -130,7 +130,9 @@ def test_forward_early_exit(reg, int4):
         got = t.to_host()
         assert np.abs(got - ref).max() < 2e-2 and np_ref.rel_rms(got, ref) < 1e-3
     full = m.forward(toks).to_host()
-    assert np.abs(m.forward_early_exit(toks, 2.0)[0].to_host() - full).max() < 1e-4
+    # int4: the residual GEMM adds its K splits in arrival order, so two runs differ in the last bits,
+    # which the fp16 activations downstream then round differently
+    assert np.abs(m.forward_early_exit(toks, 2.0)[0].to_host() - full).max() < (2e-3 if int4 else 1e-4)
 
 
 @pytest.mark.parametrize("int4", [False, True])

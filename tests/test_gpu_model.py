@@ -348,7 +348,7 @@ def test_models_from_safetensors_checkpoint(reg, tmp_path):
         b = cls.from_safetensors(p, reg)  # configuration read off the tensor shapes
         assert b.config.as_dict() == pytest.approx(cfg.as_dict())
         # f32: bit for bit; int4: the residual GEMM adds its K splits in arrival order, so last bits move
-        same = np.array_equal if cls is Gpt2Model else (lambda x, y: np.abs(x - y).max() < 1e-4)
+        same = np.array_equal if cls is Gpt2Model else (lambda x, y: np.abs(x - y).max() < 2e-3)
         assert same(a.forward(toks).to_host(), ref)
         assert same(b.forward(toks).to_host(), ref)
     assert Int4Gpt2Model.from_safetensors(p, reg).quantized_memory_bytes() > 0

@@ -205,3 +205,35 @@ def test_golden_fixture():
     assert np.array_equal(toks, g["generated"])
     p, s = oracle.quantize_weight_int4(w["h.0.mlp.c_fc.weight"], 128, 512, 128)
     assert np.array_equal(p, g["fc_packed"]) and np.array_equal(s, g["fc_scales"])
+    # data-dependent decoding
+    rng = oracle.SimpleRng(7)
+    assert np.array_equal(np.array([rng.next_f32() for _ in range(8)], np.float32), g["rng_draws"])
+    sampled, _, _ = m.generate_cached_sampling(g["tokens"][:5], 10, 20, 0.8, oracle.SimpleRng(2026))
+    assert np.array_equal(sampled, g["sampled"])
+    np.testing.assert_allclose(m.forward_early_exit(g["tokens"], 2.0)[2], g["probe_conf"], rtol=1e-5)
+    toks, layers, _, _ = m.generate_cached_early_exit(g["tokens"][:5], 10, float(g["ee_threshold"]))
+    assert np.array_equal(toks, g["ee_tokens"]) and np.array_equal(layers, g["ee_layers"])
+
+
+def test_sampling_and_early_exit_reduce_to_greedy():
+    """Limits of the dynamic loops (gpt2.rs:785-977): k = 1 samples the maximum; a threshold nothing
+    reaches runs every layer and equals the cached greedy loop with the model's last-maximum tie rule;
+    threshold 0 leaves after the first block at every decode step, the prefill excepted."""
+    from b200nn import synth
+    w = _tiny_weights(33)
+    m = oracle.Model(TINY, w)
+    prompt = synth.token_ids(5, (6,), TINY["vocab_size"])
+    greedy, _ = m.generate_cached(prompt, 9)
+    k1, _, _ = m.generate_cached_sampling(prompt, 9, 1, 0.7, oracle.SimpleRng(3))
+    assert np.array_equal(k1, greedy)
+    never, layers, _, _ = m.generate_cached_early_exit(prompt, 9, 2.0)
+    assert np.array_equal(never, m.generate_cached(prompt, 9, flags=oracle.ARGMAX_LAST)[0])
+    assert layers.tolist() == [TINY["n_layer"]] * 9
+    _, always, _, _ = m.generate_cached_early_exit(prompt, 9, 0.0)
+    assert always.tolist() == [TINY["n_layer"]] + [1] * 8
+    full = m.forward(prompt)
+    lg, used, conf = m.forward_early_exit(prompt, 2.0)
+    assert used == TINY["n_layer"] and np.allclose(lg, full, atol=1e-6) and conf.size == TINY["n_layer"] - 1
+    lg0, used0, _ = m.forward_early_exit(prompt, 0.0)
+    assert used0 == 1 and not np.allclose(lg0, full, atol=1e-3)
+    assert oracle.softmax_max_prob(lg0[-1]) == pytest.approx(conf[0], rel=1e-5)

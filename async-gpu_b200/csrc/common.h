@@ -29,6 +29,7 @@ struct DevPool {
 // ---------------------------------------------------------------------------------------------
 // context
 // ---------------------------------------------------------------------------------------------
+struct DevBuf;
 struct b200nn_ctx {
     int device = 0;
     std::shared_ptr<DevPool> pool = std::make_shared<DevPool>();
@@ -56,7 +57,10 @@ struct b200nn_ctx {
     int attn_split_items = 0;    // items the streaming decode attention hands out as two halves at the end
     int kv_prefetch_mb = 64;     // KV-cache bytes the streaming decode attention asks into L2 before its wait
     int pdl = 1;                  // launch the decode-step kernels with programmatic dependent launch
-    bool capturing = false;       // true while a decode step is being captured into a graph
+    int f32_tc = 2;               // f32 Linears of more than four rows on the tensor cores: 0 off (f32 FMA kernels),
+                                  // 1 weight rounded to fp16, 2 weight as fp16 hi + lo (two products per K block)
+    std::shared_ptr<DevBuf> xh;   // fp16 copy of an f32 activation handed to such a Linear
+    bool capturing = false;      // true while a decode step is being captured into a graph
 };
 
 int set_error(b200nn_ctx *ctx, int code, const std::string &msg);
@@ -167,9 +171,11 @@ int int4_weight_upload(b200nn_ctx *ctx, const uint32_t *packed, const float *sca
                        size_t N, size_t group, Int4Weight *out);
 
 // f32 weight of a Linear, stored [K,N] (= [in,out]) row-major on the device.
+// w_nk_h: the same weight rounded to fp16 and stored [N,K] (K contiguous), the operand of the
+// tensor-core GEMM that serves more than four rows; absent when a value does not fit fp16's range.
 struct F32Weight {
     int K = 0, N = 0;
-    std::shared_ptr<DevBuf> w_kn, bias;
+    std::shared_ptr<DevBuf> w_kn, bias, w_nk_h;
 };
 // weight given as [out,in] (Linear layout) or [in,out] (checkpoint layout)
 int f32_weight_upload(b200nn_ctx *ctx, const float *w, bool is_out_in, const float *bias, size_t K, size_t N,
@@ -205,6 +211,8 @@ int launch_int4_naive(b200nn_ctx *ctx, const Int4Weight &w, const void *x, bool 
 bool int4_gemm_tc_supported(const Int4Weight &w, int M);
 int launch_int4_gemm_tc(b200nn_ctx *ctx, const Int4Weight &w, const __half *x, int M, const Epilogue &epi);
 int launch_f32_linear(b200nn_ctx *ctx, const F32Weight &w, const void *x, bool x_half, int M, const Epilogue &epi);
+bool f16_gemm_tc_supported(const b200nn_ctx *ctx, const F32Weight &w, int M);
+int launch_f16_gemm_tc(b200nn_ctx *ctx, const F32Weight &w, const __half *x, int M, const Epilogue &epi);
 
 int launch_layernorm(b200nn_ctx *ctx, const float *x, const float *res_in, float *sum_out, const float *gamma,
                      const float *beta, float eps, int rows, int d, void *out, bool out_half);

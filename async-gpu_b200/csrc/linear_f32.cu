@@ -162,6 +162,19 @@ static int f32_linear_t(b200nn_ctx *ctx, const F32Weight &w, const XT *x, int M,
 
 int launch_f32_linear(b200nn_ctx *ctx, const F32Weight &w, const void *x, bool x_half, int M, const Epilogue &epi) {
     if (M <= 0) return B200NN_OK;
+    if (f16_gemm_tc_supported(ctx, w, M) && !((uintptr_t)x & 15)) {
+        // more than four rows: fp16 operands on the tensor cores.  f32 activations are converted once
+        // into a buffer the context keeps (grown outside stream capture only).
+        if (x_half) return launch_f16_gemm_tc(ctx, w, (const __half *)x, M, epi);
+        const size_t need = (size_t)M * w.K * sizeof(__half);
+        if (!ctx->xh || ctx->xh->bytes < need) {
+            if (ctx->capturing) return set_error(ctx, B200NN_ERR_UNSUPPORTED, "activation buffer cannot grow during graph capture");
+            ctx->xh.reset();
+            TRY(dev_alloc(ctx, need, &ctx->xh));
+        }
+        TRY(launch_f32_to_half(ctx, (const float *)x, (__half *)ctx->xh->p, (size_t)M * w.K));
+        return launch_f16_gemm_tc(ctx, w, (const __half *)ctx->xh->p, M, epi);
+    }
     return x_half ? f32_linear_t<__half>(ctx, w, (const __half *)x, M, epi)
                   : f32_linear_t<float>(ctx, w, (const float *)x, M, epi);
 }

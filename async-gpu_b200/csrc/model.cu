@@ -165,8 +165,11 @@ int workspace_alloc(b200nn_gpt2 *m, size_t rows, size_t logit_rows, Workspace *w
 
 // Activations between Linears are fp16 when the tensor-core GEMM will consume them.
 bool model_act_half(const b200nn_gpt2 *m, int rows) {
-    if (!m->int4 || rows <= m->ctx->gemv_max_rows) return false;
     const BlockW &b = m->blocks[0];
+    if (!m->int4) // f32 family: fp16 copies of the weights serve more than four rows
+        return f16_gemm_tc_supported(m->ctx, b.qkv.f, rows) && f16_gemm_tc_supported(m->ctx, b.proj.f, rows) &&
+               f16_gemm_tc_supported(m->ctx, b.fc.f, rows) && f16_gemm_tc_supported(m->ctx, b.fcproj.f, rows);
+    if (rows <= m->ctx->gemv_max_rows) return false;
     return int4_gemm_tc_supported(b.qkv.q, rows) && int4_gemm_tc_supported(b.proj.q, rows) &&
            int4_gemm_tc_supported(b.fc.q, rows) && int4_gemm_tc_supported(b.fcproj.q, rows);
 }
@@ -244,7 +247,8 @@ int run_blocks_range(b200nn_gpt2 *m, Workspace &ws, b200nn_kvcache &kv, int B, i
 int run_head(b200nn_gpt2 *m, Workspace &ws, const float *x, int rows, bool act_half, StepProfile *prof) {
     b200nn_ctx *ctx = m->ctx;
     const int d = m->cfg.n_embd, V = m->cfg.vocab_size;
-    bool head_half = act_half && m->lm_head.int4 && int4_gemm_tc_supported(m->lm_head.q, rows);
+    bool head_half = act_half && (m->lm_head.int4 ? int4_gemm_tc_supported(m->lm_head.q, rows)
+                                                   : f16_gemm_tc_supported(ctx, m->lm_head.f, rows));
     if (ctx->fam_mask & (1u << B200NN_PROF_LAYERNORM)) TRY(launch_layernorm(ctx, x, nullptr, nullptr, (const float *)m->lnf_g->p, (const float *)m->lnf_b->p,
                          m->cfg.layer_norm_epsilon, rows, d, ws.last_ln->p, head_half));
     prof_mark(ctx, prof, B200NN_PROF_LAYERNORM);

@@ -1,5 +1,6 @@
 // Context, device buffers, tensors, host-side quantiser and the upload / re-tiling of weights.
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstring>
 #include <thread>
@@ -274,5 +275,27 @@ int f32_weight_upload(b200nn_ctx *ctx, const float *wsrc, bool is_out_in, const 
         TRY(upload(ctx, wsrc, K * N * sizeof(float), &w->w_kn));
     }
     if (bias) TRY(upload(ctx, bias, N * sizeof(float), &w->bias));
+    // fp16 representation for the tensor-core GEMM (rows > 4): hi[N,K] = the weight rounded to fp16,
+    // then lo[N,K] = the rounded remainder w - hi.  Skipped when a value would overflow fp16 or the
+    // row stride would not be a multiple of 16 bytes.
+    w->w_nk_h.reset();
+    if (K % 8 == 0) {
+        std::vector<__half> h(2 * K * N);
+        __half *hp = h.data(), *lp = h.data() + K * N;
+        std::atomic<int> too_large{0};
+        parallel_for(N, [&, hp, lp](size_t n0, size_t n1) {
+            bool big = false;
+            for (size_t n = n0; n < n1; ++n)
+                for (size_t k = 0; k < K; ++k) {
+                    const float v = is_out_in ? wsrc[n * K + k] : wsrc[k * N + n];
+                    big |= !(fabsf(v) <= 65504.0f);
+                    const __half hi = __float2half_rn(v);
+                    hp[n * K + k] = hi;
+                    lp[n * K + k] = __float2half_rn(v - __half2float(hi));
+                }
+            if (big) too_large.store(1);
+        });
+        if (!too_large.load()) TRY(upload(ctx, h.data(), h.size() * sizeof(__half), &w->w_nk_h));
+    }
     return B200NN_OK;
 }

@@ -28,9 +28,12 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path[:0] = [os.path.join(ROOT, "async-gpu_b200"), ROOT]
 
 WORKLOADS = {
-    # name: (preset, total batch, prompt, max_new)
-    "gpt2-xl-int4-b256": ("xl", 256, 128, 128),
-    "gpt2-small-int4-b32": ("small", 32, 512, 256),
+    # name: (preset, total batch, prompt, max_new, model family)
+    "gpt2-xl-int4-b256": ("xl", 256, 128, 128, "int4"),
+    "gpt2-small-int4-b32": ("small", 32, 512, 256, "int4"),
+    # the unquantised family (f32 weights; Linears of more than four rows on the tensor cores):
+    # not the headline, kept for its prefill figure and profiler captures
+    "gpt2-xl-f32-b16": ("xl", 16, 512, 32, "f32"),
 }
 METRIC = "int4 GPT-2 decode tokens/sec"
 UNIT = "tokens/s"
@@ -123,9 +126,11 @@ def run_reference(args):
     os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
     from b200nn import synth  # seeded data generator only (numpy); no library code runs on this arm
     from b200nn.gpt2 import Gpt2Config
-    preset, total, prompt_len, max_new = WORKLOADS[args.workload]
+    preset, total, prompt_len, max_new, family = WORKLOADS[args.workload]
     cfg = getattr(Gpt2Config, preset)()
-    w = build_int4_oracle_weights(cfg, synth.gpt2_weights(cfg))
+    w = synth.gpt2_weights(cfg)
+    if family == "int4":
+        w = build_int4_oracle_weights(cfg, w)
     prompt = synth.token_ids(synth.BASE_SEED + 7, (total, prompt_len), cfg.vocab_size)[0, : args.cpu_prompt]
     steps = min(args.steps, args.cpu_max_steps)
     sec, threads = cpu_decode_sample(cfg, w, prompt, steps, min(args.warmup, 2))
@@ -133,9 +138,9 @@ def run_reference(args):
     sample = (f"1 of {total} sequences, prompt {args.cpu_prompt} tokens, {steps} KV-cached greedy decode steps, "
               f"f64 accumulate, OpenMP over output columns")
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "impl": "reference", "metric": METRIC.replace("int4", family), "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": min(args.warmup, 2), "ms_per_step": 1e3 * sec / steps, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "int4 weights, f64 accumulate", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": None, "dtype": family + " weights, f64 accumulate", "data": "synthetic",
         "config": {"workload": args.workload, "note": "CPU restatement of the reference path (Rust reference "
                    "cannot be built offline); each step is one decode step of a 1-sequence sample"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
@@ -192,7 +197,7 @@ def run_b200(args):
     import torch
     import torch.distributed as dist
     import b200nn
-    from b200nn import DecodeSession, Gpt2Config, Int4Gpt2Model, synth
+    from b200nn import DecodeSession, Gpt2Config, Gpt2Model, Int4Gpt2Model, synth
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -208,7 +213,7 @@ def run_b200(args):
         if world > 1:
             dist.barrier()
 
-    preset, total, prompt_len, max_new = WORKLOADS[args.workload]
+    preset, total, prompt_len, max_new, family = WORKLOADS[args.workload]
     if args.batch:
         total = args.batch
     cfg = getattr(Gpt2Config, preset)()
@@ -222,7 +227,10 @@ def run_b200(args):
         reg.set_tuning(key, int(val))
     w = synth.gpt2_weights(cfg)
     t0 = time.time()
-    model = Int4Gpt2Model.from_weights(w, cfg, reg, flags=b200nn.QUANT_LM_HEAD, group_size=128)
+    if family == "int4":
+        model = Int4Gpt2Model.from_weights(w, cfg, reg, flags=b200nn.QUANT_LM_HEAD, group_size=128)
+    else:
+        model = Gpt2Model.from_weights(w, cfg, reg)
     build_s = time.time() - t0
     prompts_all = synth.token_ids(synth.BASE_SEED + 7, (total, prompt_len), cfg.vocab_size)
     prompts = np.ascontiguousarray(prompts_all[lo:hi])
@@ -290,7 +298,7 @@ def run_b200(args):
         "attention": {"kernel": "decode_attn_stream_kernel" if batch * H >= 2 * 148 * 8 else "decode_attn_kernel",
                       "bound": "hbm", "unit": "GB/s", "peak": hbm_peak,
                       "achieved": attn_bytes_launch * L / (fam["attention"] * 1e-3) / 1e9 if fam["attention"] else 0.0},
-        "linear": {"kernel": "int4 Linear kernels (4 per layer)", "bound": "hbm", "unit": "GB/s", "peak": hbm_peak,
+        "linear": {"kernel": family + " Linear kernels (4 per layer)", "bound": "hbm", "unit": "GB/s", "peak": hbm_peak,
                    "achieved": lin_bytes / (fam["linear"] * 1e-3) / 1e9 if fam["linear"] else 0.0,
                    "tensor_tflops": lin_flops / (fam["linear"] * 1e-3) / 1e12 if fam["linear"] else 0.0},
     }
@@ -329,26 +337,41 @@ def run_b200(args):
                "note": "generate_batch: prefill + %d decode steps, host token ids in, host tokens out; "
                        "bytes are per decode step per rank" % max_new}
 
+    # the prefill of this rank's prompts on its own (second of two passes), device time on the library's stream
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        sess.prefill(prompts)
+        p0.record(stream)
+        sess.prefill(prompts)
+        p1.record(stream)
+    torch.cuda.synchronize()
+    prefill_ms = p0.elapsed_time(p1)
+    pre_flops = lin_flops * prompt_len + 4 * 0.5 * batch * H * prompt_len * prompt_len * 64 * L
+    prefill = {"ms": prefill_ms, "tokens_per_s": batch * prompt_len / (prefill_ms * 1e-3),
+               "tflops": pre_flops / (prefill_ms * 1e-3) / 1e12, "tokens": batch * prompt_len,
+               "note": "this rank's prompts through all layers (Linear + causal attention flops; LM head on the last rows only)"}
+
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "metric": METRIC.replace("int4", family), "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "int4 weights / fp16 operands / f32 accumulate", "data": "synthetic",
+        "dtype": ("int4 weights / fp16 operands / f32 accumulate" if family == "int4" else
+                  "f32 weights as fp16 hi + lo / fp16 activations / f32 accumulate"), "data": "synthetic",
         "config": {"workload": args.workload, "total_sequences": total, "sequences_per_gpu": batch,
                    "prompt_len": prompt_len, "decode_window": [prompt_len, prompt_len + window - 1],
                    "l2": "inputs larger than L2 (weights + KV read per step: %.1f GB)" %
                          ((lin_bytes + attn_bytes_launch * L) / 1e9),
                    "model_build_s": round(build_s, 1)},
-        "roofline": roof, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+        "roofline": roof, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "prefill": prefill,
     }
     if args.layers:
         line["config"]["layers_override"] = args.layers
         line["config"]["note"] = "reduced depth for a profiler capture: not a benchmark number"
     if args.tune:
         line["config"]["tuning_overrides"] = args.tune
-    if rank == 0 and not args.no_gemv:
+    if rank == 0 and not args.no_gemv and family == "int4":
         line["gemv"] = gemv_bandwidth(reg, cfg, hbm_peak)
     if world == 1 and not args.no_cpu_baseline:
-        wq = build_int4_oracle_weights(cfg, w)
+        wq = build_int4_oracle_weights(cfg, w) if family == "int4" else w
         steps = args.cpu_steps
         sec, threads = cpu_decode_sample(cfg, wq, prompts_all[0, : args.cpu_prompt], steps, 1)
         line["cpu_baseline"] = {"value": steps / sec, "unit": UNIT, "cores": threads, "kind": "port",

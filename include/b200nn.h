@@ -99,7 +99,12 @@ B200NN_API int32_t b200nn_ctx_set_gemv_max_rows(b200nn_ctx *ctx, int32_t rows);
  * "attn_stream" (0 = never use the TMA-fed decode-attention kernel), "attn_stream_min10" (tenths of
  * a (sequence, head) pair per warp of its grid from which it is used; default 20), "kv_prefetch_mb" (KV-cache
  * megabytes that kernel asks into L2 before its dependency wait), "attn_split_items" (items it
- * hands out as two halves at the end of the grid; 0 = none). */
+ * hands out as two halves at the end of the grid; 0 = none).
+ * "f32_tc" selects how an f32 Linear (linear.rs:283-313) multiplies more than four rows: 2 (default;
+ * negative restores it) fp16 activations times the weight held as fp16 hi + lo on the tensor cores,
+ * f32 accumulation (the weight enters with about 22 bits, the activations with fp16's 11); 1 the
+ * weight rounded to fp16 only (half the tensor work, weight error 2^-11 relative); 0 the f32 FMA
+ * kernels for every row count (the reference's arithmetic). */
 B200NN_API int32_t b200nn_ctx_set_tuning(b200nn_ctx *ctx, const char *key, int32_t value);
 /* Measurement aid: after set_tuning("trace", 1) the first block of the next tensor-core GEMM
  * writes SM-clock stamps of its pipeline events into a 256-slot buffer; this copies it out. */

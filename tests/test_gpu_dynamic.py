@@ -92,20 +92,22 @@ def test_forward_features_embedding_table_and_profiled(reg):
     feats = m.forward_features(toks)
     assert feats.shape() == (13, cfg.n_embd)
     # the tied LM head applied by hand to the features gives the model's logits
+    # (the model's head multiplies fp16 copies of both operands for more than four rows)
     by_hand = feats.to_host().astype(np.float64) @ wte.astype(np.float64).T
-    assert np.abs(by_hand - logits).max() < 1e-3
+    assert np.abs(by_hand - logits).max() < 2e-2 and np_ref.rel_rms(logits, by_hand) < 5e-4
     # and the features are the oracle's last hidden state: check through the oracle's logits
     ref = oracle.Model(cfg.as_dict(), w).forward(toks, flags=oracle.KV_FP16)
     assert np.abs(by_hand - ref).max() < 2e-2 and np_ref.rel_rms(by_hand.astype(np.float32), ref) < 1e-3
     lg, timings = m.forward_profiled(toks)
     assert [n for n, _ in timings] == ["embedding", "block_0", "block_1", "block_2", "ln_f", "lm_head"]
     assert all(t > 0 for _, t in timings)
-    assert np.abs(lg.to_host() - logits).max() < 1e-5
-    assert np.array_equal(m.forward_auto_fused(toks).to_host(), logits)
+    # run to run the residual GEMMs add their K splits in a different order: last bits move
+    assert np.abs(lg.to_host() - logits).max() < 2e-3
+    assert np.abs(m.forward_auto_fused(toks).to_host() - logits).max() < 2e-3
     with pytest.raises(b200nn.NnError):
         m.forward_features(np.zeros(cfg.n_positions + 1, np.uint32))
     del wte_t, wpe_t  # views on the model's buffers: the model stays usable
-    assert np.array_equal(m.forward(toks).to_host(), logits)
+    assert np.abs(m.forward(toks).to_host() - logits).max() < 2e-3
 
 
 @pytest.mark.parametrize("int4", [False, True])
@@ -130,9 +132,9 @@ def test_forward_early_exit(reg, int4):
         got = t.to_host()
         assert np.abs(got - ref).max() < 2e-2 and np_ref.rel_rms(got, ref) < 1e-3
     full = m.forward(toks).to_host()
-    # int4: the residual GEMM adds its K splits in arrival order, so two runs differ in the last bits,
-    # which the fp16 activations downstream then round differently
-    assert np.abs(m.forward_early_exit(toks, 2.0)[0].to_host() - full).max() < (2e-3 if int4 else 1e-4)
+    # the residual GEMMs add their K splits in arrival order, so two runs differ in the last bits, which
+    # the fp16 activations downstream then round differently
+    assert np.abs(m.forward_early_exit(toks, 2.0)[0].to_host() - full).max() < 2e-3
 
 
 @pytest.mark.parametrize("int4", [False, True])

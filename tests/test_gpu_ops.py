@@ -91,6 +91,8 @@ def test_int4_matmul_op(reg):
 
 
 # ---- f32 Linear: the reference's own arithmetic-pattern tests (layers/linear.rs:388-464) ---------
+# Tuning key f32_tc selects how more than four rows are multiplied: 2 (default) fp16 activations times
+# the weight as fp16 hi + lo on the tensor cores, 1 the weight rounded to fp16 only, 0 the f32 FMA kernels.
 @pytest.mark.parametrize("idx", [0, 1])
 def test_linear_reference_patterns(reg, idx):
     c = KATS["patterns"][idx]
@@ -98,10 +100,17 @@ def test_linear_reference_patterns(reg, idx):
     w = _formula(c["weight_formula"], n * k)
     bias = _formula(c["bias_formula"], n)
     x = _formula(c["input_formula"], b * k)
-    y = b200nn.Linear(w, bias, k, n, reg).forward(GpuTensor.from_host(x, (b, k), reg)).to_host()
+    lin = b200nn.Linear(w, bias, k, n, reg)
     ref = oracle.matmul(x, np.ascontiguousarray(w.reshape(n, k).T), b, k, n) + bias
-    assert y.shape == (b, n)
-    assert np.abs(y - ref).max() < min(c["tol"], 1e-4)
+    for mode in (2, 1, 0):
+        reg.set_tuning("f32_tc", mode)
+        try:
+            y = lin.forward(GpuTensor.from_host(x, (b, k), reg)).to_host()
+        finally:
+            reg.set_tuning("f32_tc", -1)
+        assert y.shape == (b, n)
+        # fp16 activations on the tensor-core paths: inside the reference's own tolerance
+        assert np.abs(y - ref).max() < min(c["tol"], 1e-4 if (b <= 4 or mode == 0) else 2e-3)
 
 
 @pytest.mark.parametrize("m", [1, 3, 70])
@@ -112,12 +121,63 @@ def test_linear_fused_activation(reg, m):
     x = rng.standard_normal((m, 96)).astype(np.float32)
     lin = b200nn.Linear(w, bias, 96, 200, reg)
     pre = x.astype(np.float64) @ w.astype(np.float64).T + bias
-    y = lin.forward_fused(GpuTensor.from_host(x, (m, 96), reg), b200nn.ACT_GELU_TANH).to_host()
-    assert np.abs(y - np_ref.gelu_tanh(pre)).max() < 1e-4
-    y = lin.forward_fused(GpuTensor.from_host(x, (m, 96), reg), b200nn.ACT_RELU).to_host()
-    assert np.abs(y - np.maximum(pre, 0)).max() < 1e-4
+    for mode in (2, 1, 0):
+        reg.set_tuning("f32_tc", mode)
+        try:
+            tol = 2e-3 if (mode and m > 4) else 1e-4
+            y = lin.forward_fused(GpuTensor.from_host(x, (m, 96), reg), b200nn.ACT_GELU_TANH).to_host()
+            assert np.abs(y - np_ref.gelu_tanh(pre)).max() < tol
+            y = lin.forward_fused(GpuTensor.from_host(x, (m, 96), reg), b200nn.ACT_RELU).to_host()
+            assert np.abs(y - np.maximum(pre, 0)).max() < tol
+        finally:
+            reg.set_tuning("f32_tc", -1)
     with pytest.raises(b200nn.NnError):
         lin.forward(GpuTensor.zeros((m, 95), reg))
+
+
+@pytest.mark.parametrize("mode", [2, 1])
+@pytest.mark.parametrize("m,k,n", [(5, 768, 768), (33, 768, 2304), (128, 1600, 6400), (300, 6400, 1600),
+                                   (1000, 768, 3072), (64, 1600, 50257), (7, 72, 130), (260, 200, 1), (9, 8, 129)])
+def test_linear_tensor_core_shapes(reg, m, k, n, mode):
+    """f32 Linear of more than four rows (linear.rs:283-313) on the tensor cores, f32 accumulation.
+    Checked twice: against the f64 product of the f32 operands at the fp16 tolerance, and against the
+    f64 product of exactly the operands the kernel multiplies (fp16-rounded activations; the weight as
+    fp16 hi + lo, or rounded to fp16) at f32 accumulation accuracy, which pins tiling, swizzle, K tail
+    (K % 64 != 0), ragged N and row tails."""
+    rng = np.random.default_rng(m * 7 + n)
+    w = (rng.standard_normal((n, k)) * 0.05).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    reg.set_tuning("f32_tc", mode)
+    try:
+        launches = reg.launch_count()
+        y = b200nn.Linear(w, bias, k, n, reg).forward(GpuTensor.from_host(x, (m, k), reg)).to_host()
+        assert reg.launch_count() - launches == 2  # activation conversion + the GEMM
+    finally:
+        reg.set_tuning("f32_tc", -1)
+    ref = x.astype(np.float64) @ w.astype(np.float64).T + bias
+    assert np_ref.rel_rms(y, ref) < (3.5e-4 if mode == 2 else 5e-4)
+    hi = w.astype(np.float16)
+    w_used = hi.astype(np.float64)
+    if mode == 2:
+        w_used = w_used + (w - hi.astype(np.float32)).astype(np.float16).astype(np.float64)
+        assert np.abs(w_used - w).max() < 1e-7  # hi + lo carries the f32 weight to about 22 bits
+    ref16 = x.astype(np.float16).astype(np.float64) @ w_used.T + bias
+    assert np_ref.rel_rms(y, ref16) < 5e-6
+    assert np.abs(y - ref16).max() < 1e-4 * max(1.0, float(np.abs(ref16).max()))
+    assert reg.device_error() == 0
+
+
+def test_linear_tensor_core_fallbacks(reg):
+    """K not a multiple of 8 (no 16-byte row stride for the tensor map) and weights beyond fp16's range
+    keep the f32 FMA kernels."""
+    rng = np.random.default_rng(5)
+    for k, scale in [(100, 0.05), (96, 1e6)]:
+        w = (rng.standard_normal((40, k)) * scale).astype(np.float32)
+        x = rng.standard_normal((9, k)).astype(np.float32)
+        y = b200nn.Linear(w, None, k, 40, reg).forward(GpuTensor.from_host(x, (9, k), reg)).to_host()
+        ref = x.astype(np.float64) @ w.astype(np.float64).T
+        assert np_ref.rel_rms(y, ref) < 1e-5
 
 
 # ---- LayerNorm, activations, element-wise -------------------------------------------------------

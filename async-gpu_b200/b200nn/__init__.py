@@ -299,4 +299,5 @@ from . import ops  # noqa: E402
 from .layers import Embedding, Int4Linear, LayerNorm, Linear, MultiHeadAttention, GELU  # noqa: E402
 from .gpt2 import Gpt2Config, Gpt2Model, Int4Gpt2Model, KvCache, DecodeSession  # noqa: E402
 from .sampling import SimpleRng, top_k_sample  # noqa: E402
-from .checkpoint import SafeTensorsFile, TensorInfo, list_tensors, load_all_tensors, load_gpt2_weights  # noqa: E402
+from .checkpoint import (SafeTensorsFile, TensorInfo, list_tensors, load_all_tensors, load_gpt2_weights,  # noqa: E402
+                         load_int4_tensors)

@@ -98,6 +98,47 @@ def load_all_tensors(path):
     return out
 
 
+def load_int4_tensors(path):
+    """Reads a checkpoint in the layout ``scripts/quantize_gpt2_int4.py`` writes (the reference has no
+    reader for it): every quantised matrix is a pair ``<key>.int4_packed`` (U32 ``[in/8, out]``, eight
+    nibbles per word, nibble i at bits 4i, stored value q + 8) and ``<key>.int4_scales`` (F32
+    ``[ceil(in/group), out]``); everything else is F32.  Returns ``(int4, dense)``: ``int4[key]`` =
+    ``(packed, scales, in_features, out_features, group_size)`` exactly as ``Int4Linear`` takes them
+    (int4_linear.rs:40-48), ``dense[key]`` = f32 array.  The group size is read off the shapes (the
+    script's 128 unless the matrix is shorter than one group)."""
+    int4, dense, packed, scales = {}, {}, {}, {}
+    with SafeTensorsFile(path) as f:
+        for i in range(len(f)):
+            ti = f.info(i)
+            if ti.name.endswith(".int4_packed"):
+                if ti.dtype != "U32" or len(ti.shape) != 2:
+                    raise NnError(ERR_UNSUPPORTED, f"tensor {ti.name}: expected a 2-D U32 tensor, got {ti.dtype} {ti.shape}")
+                packed[ti.name[: -len(".int4_packed")]] = f.read(i)
+            elif ti.name.endswith(".int4_scales"):
+                if ti.dtype != "F32" or len(ti.shape) != 2:
+                    raise NnError(ERR_UNSUPPORTED, f"tensor {ti.name}: expected a 2-D F32 tensor, got {ti.dtype} {ti.shape}")
+                scales[ti.name[: -len(".int4_scales")]] = f.read(i)
+            elif ti.dtype == "F32":
+                dense[ti.name] = f.read(i)
+            else:
+                raise NnError(ERR_UNSUPPORTED, f"tensor {ti.name}: expected dtype F32, got {ti.dtype}")
+    for key in sorted(set(packed) | set(scales)):
+        if key not in packed or key not in scales:
+            raise NnError(ERR_UNSUPPORTED, f"{key}: int4_packed and int4_scales must come as a pair")
+        p, s = packed[key], scales[key]
+        k, n = p.shape[0] * 8, p.shape[1]
+        if s.shape[1] != n or s.shape[0] < 1:
+            raise NnError(ERR_UNSUPPORTED, f"{key}: scales {s.shape} do not match packed {p.shape}")
+        g = s.shape[0]
+        group = k if g == 1 else -(-k // g)
+        if g > 1 and (group % 8 or -(-k // group) != g):  # the writer's groups are 128 wide, the last one ragged
+            group = 128
+        if -(-k // group) != g:
+            raise NnError(ERR_UNSUPPORTED, f"{key}: {g} scale rows do not tile in_features = {k}")
+        int4[key] = (np.ascontiguousarray(p), np.ascontiguousarray(s), k, n, group)
+    return int4, dense
+
+
 def load_gpt2_weights(path):
     """``load_gpt2_weights`` (model.rs:308-386) as the dict ``Gpt2Model.from_weights`` takes: keys
     ``wte``, ``wpe``, ``ln_f.weight|bias``, ``h.{i}.<name>``; dense weights stay [in,out]."""

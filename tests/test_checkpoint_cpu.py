@@ -131,3 +131,42 @@ def test_load_gpt2_weights_key_names(tmp_path):
     assert set(got) == set(w)
     assert all(np.array_equal(got[k], np.asarray(w[k], np.float32).reshape(got[k].shape)) for k in w)
     assert got["h.1.mlp.c_fc.weight"].shape == (64, 256)  # Conv1D layout [in,out] kept
+
+
+def test_load_int4_tensors_layout_of_the_reference_script(tmp_path):
+    """The int4 checkpoint layout of scripts/quantize_gpt2_int4.py:21-62, 85-99: `<key>.int4_packed` U32
+    [in/8,out] + `<key>.int4_scales` F32 [ceil(in/128),out]; other tensors F32.  The quantiser here is the
+    oracle's (quantize.rs:102-153), which packs the same way (nibble i of a word at bits 4i, value + 8)."""
+    from oracle import oracle
+    rng = np.random.default_rng(11)
+    tensors, want = {}, {}
+    for key, (k, n) in {"h.0.mlp.c_fc.weight": (256, 40), "h.0.attn.c_proj.weight": (200, 24), "small": (64, 8)}.items():
+        w = (rng.standard_normal((k, n)) * 0.05).astype(np.float32)
+        p, s = oracle.quantize_weight_int4(w, k, n, 128)
+        tensors[key + ".int4_packed"], tensors[key + ".int4_scales"] = p.reshape(k // 8, n), s.reshape(-1, n)
+        want[key] = (p.reshape(k // 8, n), s.reshape(-1, n), k, n)
+    tensors["ln_f.bias"] = rng.standard_normal(16).astype(np.float32)
+    path = tmp_path / "model_int4.safetensors"
+    write_safetensors(path, tensors)
+    int4, dense = checkpoint.load_int4_tensors(path)
+    assert set(dense) == {"ln_f.bias"} and np.array_equal(dense["ln_f.bias"], tensors["ln_f.bias"])
+    assert set(int4) == set(want)
+    for key, (p, s, k, n) in want.items():
+        gp, gs, gk, gn, group = int4[key]
+        assert (gk, gn) == (k, n) and np.array_equal(gp, p) and np.array_equal(gs, s)
+        assert group == (128 if k > 128 else k)  # 200 rows: two groups, the second ragged
+        # the pair is what the oracle's int4 Linear takes
+        x = rng.standard_normal((2, k)).astype(np.float32)
+        ref = x.astype(np.float64) @ oracle.dequant_weight_int4(gp, gs, k, n, group).reshape(k, n).astype(np.float64)
+        assert np.allclose(oracle.int4_linear(x, gp, gs, None, 2, n, k, group, f64=True), ref, atol=1e-9)
+    # a lone half of a pair, or a pair of the wrong dtype, is an error
+    bad = dict(tensors)
+    del bad["small.int4_scales"]
+    write_safetensors(path, bad)
+    with pytest.raises(b200nn.NnError):
+        checkpoint.load_int4_tensors(path)
+    bad = dict(tensors)
+    bad["small.int4_packed"] = bad["small.int4_packed"].astype(np.int64)
+    write_safetensors(path, bad)
+    with pytest.raises(b200nn.NnError):
+        checkpoint.load_int4_tensors(path)

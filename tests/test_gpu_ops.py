@@ -257,3 +257,25 @@ def test_split_qkv_concat_heads_roundtrip(reg):
         assert np.array_equal(t.to_host(), ref)
     back = ops.concat_heads(q, seq, H, dh, reg).to_host()
     assert np.array_equal(back, qkv[:, :d])
+
+
+def test_int4_linear_from_int4_checkpoint_pair(reg, tmp_path):
+    """`<key>.int4_packed` / `<key>.int4_scales` of the reference script's int4 checkpoint
+    (scripts/quantize_gpt2_int4.py:85-99) go straight into Int4Linear (int4_linear.rs:40-48)."""
+    from test_checkpoint_cpu import write_safetensors
+    rng = np.random.default_rng(21)
+    k, n = 768, 200
+    w = (rng.standard_normal((k, n)) * 0.05).astype(np.float32)
+    p, s = oracle.quantize_weight_int4(w, k, n, 128)
+    path = tmp_path / "model_int4.safetensors"
+    write_safetensors(path, {"h.0.mlp.c_fc.weight.int4_packed": p.reshape(k // 8, n),
+                             "h.0.mlp.c_fc.weight.int4_scales": s.reshape(-1, n),
+                             "h.0.mlp.c_fc.bias": np.linspace(-1, 1, n).astype(np.float32)})
+    int4, dense = b200nn.load_int4_tensors(path)
+    gp, gs, gk, gn, group = int4["h.0.mlp.c_fc.weight"]
+    lin = b200nn.Int4Linear(gp, gs, dense["h.0.mlp.c_fc.bias"], gk, gn, group, reg)
+    for m in (1, 40):
+        x = rng.standard_normal((m, k)).astype(np.float32)
+        y = lin.forward(GpuTensor.from_host(x, (m, k), reg)).to_host()
+        ref = oracle.int4_linear(x, gp, oracle.f16_round(gs), dense["h.0.mlp.c_fc.bias"], m, n, k, group, f64=True)
+        assert np_ref.rel_rms(y, ref) < (1e-5 if m == 1 else 5e-4)

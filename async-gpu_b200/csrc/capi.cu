@@ -56,6 +56,7 @@ extern "C" void b200nn_ctx_destroy(b200nn_ctx *ctx) {
     if (ctx->counters) cudaFree(ctx->counters);
     for (void *p : ctx->retired) cudaFree(p);
     ctx->xh.reset();
+    ctx->wh.reset();
     pool_trim(ctx);
     {
         std::lock_guard<std::mutex> g(ctx->pool->mu);
@@ -93,6 +94,8 @@ extern "C" int32_t b200nn_ctx_set_tuning(b200nn_ctx *ctx, const char *key, int32
     else if (!strcmp(key, "tc_min_kb")) ctx->tc_min_kb = value < 1 ? 1 : value;
     else if (!strcmp(key, "pdl")) ctx->pdl = value ? 1 : 0;
     else if (!strcmp(key, "f32_tc")) ctx->f32_tc = value < 0 ? 2 : (value > 2 ? 2 : value);
+    else if (!strcmp(key, "tc_persistent")) ctx->tc_persistent = value ? 1 : 0;
+    else if (!strcmp(key, "int4_via_f16")) ctx->int4_via_f16 = value ? 1 : 0;
     else if (!strcmp(key, "attn_tc")) ctx->attn_tc = value ? 1 : 0;
     else if (!strcmp(key, "attn_stream")) ctx->attn_stream = value ? 1 : 0;
     else if (!strcmp(key, "attn_stream_min10")) ctx->attn_stream_min10 = value < 1 ? 1 : value;

@@ -60,6 +60,9 @@ struct b200nn_ctx {
     int f32_tc = 2;               // f32 Linears of more than four rows on the tensor cores: 0 off (f32 FMA kernels),
                                   // 1 weight rounded to fp16, 2 weight as fp16 hi + lo (two products per K block)
     std::shared_ptr<DevBuf> xh;   // fp16 copy of an f32 activation handed to such a Linear
+    int tc_persistent = 1;        // the plain fp16 GEMM runs one persistent block per SM from two 256-row tiles per SM on
+    int int4_via_f16 = 1;         // int4 Linears with that many tiles dequantise the weight to fp16 once and use that GEMM
+    std::shared_ptr<DevBuf> wh;   // the dequantised weight, [N,K] fp16, one Linear at a time
     bool capturing = false;      // true while a decode step is being captured into a graph
 };
 
@@ -213,6 +216,8 @@ int launch_int4_gemm_tc(b200nn_ctx *ctx, const Int4Weight &w, const __half *x, i
 int launch_f32_linear(b200nn_ctx *ctx, const F32Weight &w, const void *x, bool x_half, int M, const Epilogue &epi);
 bool f16_gemm_tc_supported(const b200nn_ctx *ctx, const F32Weight &w, int M);
 int launch_f16_gemm_tc(b200nn_ctx *ctx, const F32Weight &w, const __half *x, int M, const Epilogue &epi);
+bool int4_via_f16_supported(const b200nn_ctx *ctx, const Int4Weight &w, int M);
+int launch_int4_via_f16(b200nn_ctx *ctx, const Int4Weight &w, const __half *x, int M, const Epilogue &epi);
 
 int launch_layernorm(b200nn_ctx *ctx, const float *x, const float *res_in, float *sum_out, const float *gamma,
                      const float *beta, float eps, int rows, int d, void *out, bool out_half);

@@ -239,6 +239,9 @@ int launch_int4_gemv(b200nn_ctx *ctx, const Int4Weight &w, const void *x, bool x
 int launch_int4_linear(b200nn_ctx *ctx, const Int4Weight &w, const void *x, bool x_half, int M, const Epilogue &epi) {
     if (M <= 0) return B200NN_OK;
     if (!w.fast) return launch_int4_naive(ctx, w, x, x_half, M, epi);
+    // a prefill pass with at least two 256-row tiles per SM: dequantise once, persistent fp16 GEMM
+    if (x_half && !((uintptr_t)x & 15) && int4_via_f16_supported(ctx, w, M))
+        return launch_int4_via_f16(ctx, w, (const __half *)x, M, epi);
     if (M > ctx->gemv_max_rows && x_half && int4_gemm_tc_supported(w, M))
         return launch_int4_gemm_tc(ctx, w, (const __half *)x, M, epi);
     return launch_int4_gemv(ctx, w, x, x_half, M, epi);

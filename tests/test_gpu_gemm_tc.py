@@ -66,3 +66,29 @@ def test_gemv_and_tensor_core_paths_agree(reg):
         reg.set_gemv_max_rows(-1)
     assert np_ref.rel_rms(tc, cc) < 5e-4
     assert np_ref.rel_rms(cc, oracle.int4_linear(x, packed, scales, None, 8, 1600, 1600, 128)) < 1e-5
+
+
+@pytest.mark.parametrize("m,k,n,group", [(2100, 1600, 4800, 128), (5900, 3200, 1600, 128), (9000, 192, 1100, 64)])
+def test_prefill_rows_dequantise_once_then_persistent_gemm(reg, m, k, n, group):
+    """With at least two 256-row tiles per SM the weight is written out once as the fp16 matrix the int4
+    GEMM builds tile by tile, and the persistent fp16 GEMM multiplies it (tuning key int4_via_f16): the same
+    operand values, so the two ways agree to accumulation order, and both match the oracle."""
+    packed, scales, x, _ = synth.int4_linear_case(m + n, m, k, n, group)
+    bias = np.linspace(-1, 1, n).astype(np.float32)
+    lin = b200nn.Int4Linear(packed, scales, bias, k, n, group, reg)
+    t = GpuTensor.from_host(x, (m, k), reg)
+    n0 = reg.launch_count()
+    y = lin.forward(t).to_host()
+    n_new = reg.launch_count() - n0
+    reg.set_tuning("int4_via_f16", 0)
+    try:
+        n0 = reg.launch_count()
+        y_int4 = lin.forward(t).to_host()
+        assert reg.launch_count() - n0 == n_new - 1  # no dequantisation launch on the int4 GEMM's way
+    finally:
+        reg.set_tuning("int4_via_f16", 1)
+    assert np_ref.rel_rms(y, y_int4) < 5e-6
+    ref = oracle.int4_linear(x, packed, scales, bias, m, n, k, group, f64=True)
+    assert np_ref.rel_rms(y, ref) < 5e-4
+    assert np.abs(y - ref).max() < 2e-2 * max(1.0, float(np.abs(ref).max()))
+    assert reg.device_error() == 0

@@ -279,3 +279,34 @@ def test_int4_linear_from_int4_checkpoint_pair(reg, tmp_path):
         y = lin.forward(GpuTensor.from_host(x, (m, k), reg)).to_host()
         ref = oracle.int4_linear(x, gp, oracle.f16_round(gs), dense["h.0.mlp.c_fc.bias"], m, n, k, group, f64=True)
         assert np_ref.rel_rms(y, ref) < (1e-5 if m == 1 else 5e-4)
+
+
+@pytest.mark.parametrize("mode", [2, 1])
+@pytest.mark.parametrize("m,k,n", [(9000, 256, 1100), (9000, 200, 1100), (16384, 768, 768)])
+def test_linear_tensor_core_many_tiles_take_the_persistent_kernel(reg, m, k, n, mode):
+    """From two 256-row tiles per SM on, one persistent block per SM walks the tiles with two accumulators
+    (the epilogue of one tile overlaps the K loop of the next).  Ragged N, a row tail, a K tail; compared
+    with the one-tile-per-block kernel (tuning key tc_persistent = 0: same operands, same order of the K
+    blocks) and with the f64 product of the operands the kernel multiplies."""
+    rng = np.random.default_rng(m + k + n)
+    w = (rng.standard_normal((n, k)) * 0.05).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    lin = b200nn.Linear(w, bias, k, n, reg)
+    t = GpuTensor.from_host(x, (m, k), reg)
+    reg.set_tuning("f32_tc", mode)
+    try:
+        y = lin.forward_fused(t, b200nn.ACT_GELU_TANH).to_host()
+        reg.set_tuning("tc_persistent", 0)
+        y1 = lin.forward_fused(t, b200nn.ACT_GELU_TANH).to_host()
+    finally:
+        reg.set_tuning("tc_persistent", 1)
+        reg.set_tuning("f32_tc", -1)
+    assert np.array_equal(y, y1)
+    hi = w.astype(np.float16)
+    w_used = hi.astype(np.float64)
+    if mode == 2:
+        w_used = w_used + (w - hi.astype(np.float32)).astype(np.float16).astype(np.float64)
+    ref16 = np_ref.gelu_tanh(x.astype(np.float16).astype(np.float64) @ w_used.T + bias)
+    assert np_ref.rel_rms(y, ref16) < 5e-6
+    assert reg.device_error() == 0

@@ -26,6 +26,10 @@
 //
 // Every mbarrier wait is bounded; when one runs out the block records a code in the device error
 // word, all roles leave their loops, TMEM is freed and the kernel returns.
+//
+// Further down: f16_gemm_tc_persistent_kernel, the same GEMM for passes of many tiles (one block per
+// SM, two accumulators), and int4_dequant_f16_kernel, through which an int4 Linear's prefill pass
+// reaches it.
 #include <cooperative_groups.h>
 #include <cuda.h>
 
@@ -709,7 +713,8 @@ int launch_f16_gemm_tc(b200nn_ctx *ctx, const F32Weight &w, const __half *x, int
 // persistent kernel applies (at least two 256-row tiles per SM) and, while a graph is being captured,
 // only if the buffer is already large enough.
 bool int4_via_f16_supported(const b200nn_ctx *ctx, const Int4Weight &w, int M) {
-    return ctx->int4_via_f16 && ctx->encode_tiled && w.fast && (w.K % TILE_K) == 0 && (w.group % TILE_K) == 0 &&
+    // (2048 rows: a prefill pass, not the LM head of a decode step, whose 393 feature tiles alone would qualify)
+    return ctx->int4_via_f16 && M >= 2048 && ctx->encode_tiled && w.fast && (w.K % TILE_K) == 0 && (w.group % TILE_K) == 0 &&
            use_persistent(ctx, w.N, M, pick_mb(ctx, w.N, M)) &&
            !(ctx->capturing && (!ctx->wh || ctx->wh->bytes < (size_t)w.N * w.K * sizeof(__half)));
 }

@@ -104,7 +104,11 @@ B200NN_API int32_t b200nn_ctx_set_gemv_max_rows(b200nn_ctx *ctx, int32_t rows);
  * negative restores it) fp16 activations times the weight held as fp16 hi + lo on the tensor cores,
  * f32 accumulation (the weight enters with about 22 bits, the activations with fp16's 11); 1 the
  * weight rounded to fp16 only (half the tensor work, weight error 2^-11 relative); 0 the f32 FMA
- * kernels for every row count (the reference's arithmetic). */
+ * kernels for every row count (the reference's arithmetic).
+ * "tc_persistent" (default 1): the fp16 GEMM runs as one persistent block per SM from two 256-row
+ * tiles per SM on; 0 = always one tile per block.  "int4_via_f16" (default 1): an int4 Linear over
+ * such a pass of at least 2048 rows writes its weight out once as fp16 and uses that GEMM; 0 = the
+ * int4 GEMM for every row count. */
 B200NN_API int32_t b200nn_ctx_set_tuning(b200nn_ctx *ctx, const char *key, int32_t value);
 /* Measurement aid: after set_tuning("trace", 1) the first block of the next tensor-core GEMM
  * writes SM-clock stamps of its pipeline events into a 256-slot buffer; this copies it out. */

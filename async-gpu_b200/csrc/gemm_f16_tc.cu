@@ -100,6 +100,12 @@ f16_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     __syncthreads();
     tc::tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(gen_base + (tmem_slot - base));
+    // the epilogue's per-thread constants (filled by the epilogue warps, used in both of its places):
+    // lane l owns features 4l..4l+3 of a token row
+    const int n4 = nt * 128 + lane * 4;
+    float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    Epilogue e2 = epi; // the device-side position is read once per thread
+    e2.pos_ptr = nullptr;
 
     if (warp == 0) {
         // ---- producer.  The weight boxes of the first stages do not depend on the previous kernel
@@ -171,6 +177,14 @@ f16_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         const int w8 = warp - 2;          // epilogue warp index
         const int colh = w8 >> 2;         // the NE warps of a quadrant split the token columns
         pdl_wait(); // the epilogue touches buffers the previous kernel may still be using
+        // bias and the device-side position are fetched under the wait for the accumulator
+        if (epi.bias) {
+            if (n4 < N) b4.x = epi.bias[n4];
+            if (n4 + 1 < N) b4.y = epi.bias[n4 + 1];
+            if (n4 + 2 < N) b4.z = epi.bias[n4 + 2];
+            if (n4 + 3 < N) b4.w = epi.bias[n4 + 3];
+        }
+        if (epi.mode == EPI_QKV && epi.pos_ptr) e2.pos_off = epi.pos_off + *epi.pos_ptr;
         // (the vote keeps the warp converged for the warp-collective wait)
         if (!__any_sync(0xffffffffu, abort_flag != 0)) tc::mbar_wait(acc_full, 0, &abort_flag, dev_err, ERR_ACC);
         bar_sync_epi<EPI>();
@@ -195,17 +209,6 @@ f16_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             bar_sync_epi<EPI>();
             // phase 2: one warp per token row, lane l owns features 4l..4l+3
             constexpr int NW = 4 * NE;
-            const int n4 = nt * 128 + lane * 4;
-            float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (epi.bias) {
-                if (n4 < N) b4.x = epi.bias[n4];
-                if (n4 + 1 < N) b4.y = epi.bias[n4 + 1];
-                if (n4 + 2 < N) b4.z = epi.bias[n4 + 2];
-                if (n4 + 3 < N) b4.w = epi.bias[n4 + 3];
-            }
-            Epilogue e2 = epi; // the device-side position is read once per thread
-            if (epi.mode == EPI_QKV && epi.pos_ptr) e2.pos_off = epi.pos_off + *epi.pos_ptr;
-            e2.pos_ptr = nullptr;
             const float4 *stage4 = reinterpret_cast<const float4 *>(stage);
             const int rows = min(MB, M - mt * MB);
             if (splits == 1) {
@@ -243,17 +246,7 @@ f16_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         cluster.sync(); // every block of the cluster has staged its partial tile
         if (warp >= 2 && !abort_flag) {
             constexpr int NW = 4 * NE;
-            const int w8 = warp - 2, n4 = nt * 128 + lane * 4;
-            float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (epi.bias) {
-                if (n4 < N) b4.x = epi.bias[n4];
-                if (n4 + 1 < N) b4.y = epi.bias[n4 + 1];
-                if (n4 + 2 < N) b4.z = epi.bias[n4 + 2];
-                if (n4 + 3 < N) b4.w = epi.bias[n4 + 3];
-            }
-            Epilogue e2 = epi;
-            if (epi.mode == EPI_QKV && epi.pos_ptr) e2.pos_off = epi.pos_off + *epi.pos_ptr;
-            e2.pos_ptr = nullptr;
+            const int w8 = warp - 2;
             const float4 *stage4 = reinterpret_cast<const float4 *>(gen_base);
             const int rows = min(MB, M - mt * MB);
             for (int c = split + splits * w8; c < rows; c += splits * NW) {
@@ -427,19 +420,19 @@ f16_gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++j) {
             const int b = j & 1;
             const int mt = t / n_tiles, nt = t - mt * n_tiles;
-            bool ok = true;
-            if (!__any_sync(0xffffffffu, abort_flag != 0))
-                ok = tc::mbar_wait(acc_full + 8 * b, (j >> 1) & 1, &abort_flag, dev_err, ERR_ACC);
-            if (bar_or_epi<EPI>(!ok || abort_flag != 0)) break; // the same decision in every epilogue thread
-            tc::tc_fence_after_sync();
             const int n4 = nt * 128 + lane * 4;
             float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (epi.bias) {
+            if (epi.bias) { // fetched under the wait for the accumulator
                 if (n4 < N) b4.x = epi.bias[n4];
                 if (n4 + 1 < N) b4.y = epi.bias[n4 + 1];
                 if (n4 + 2 < N) b4.z = epi.bias[n4 + 2];
                 if (n4 + 3 < N) b4.w = epi.bias[n4 + 3];
             }
+            bool ok = true;
+            if (!__any_sync(0xffffffffu, abort_flag != 0))
+                ok = tc::mbar_wait(acc_full + 8 * b, (j >> 1) & 1, &abort_flag, dev_err, ERR_ACC);
+            if (bar_or_epi<EPI>(!ok || abort_flag != 0)) break; // the same decision in every epilogue thread
+            tc::tc_fence_after_sync();
             const int rows = min(MB, M - mt * MB);
 #pragma unroll 1
             for (int c0 = 0; c0 < MB; c0 += CH) {

@@ -132,6 +132,13 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(gen_base + (S.tmem_slot - base));
     const uint32_t tmem_a = tmem_base + MB; // dequantised weight stages follow the accumulator columns
 
+    // the epilogue's per-thread constants (filled by the epilogue warps, used in both of its places):
+    // lane l owns features 4l..4l+3 of a token row
+    const int n4 = nt * TILE_N + lane * 4;
+    float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    Epilogue e2 = epi; // the device-side position is read once per thread, not once per element
+    e2.pos_ptr = nullptr;
+
     if (warp == 0) {
         // ---- packed weight tiles: HBM -> shared, NP stages in flight (one elected lane) ----
         const uint8_t *src = tiles + ((size_t)nt * k_blocks + kb0) * TILE_BYTES;
@@ -242,6 +249,14 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
             if (t == 0 && i < 32) TRACE(128 + i);
         }
         pdl_wait(); // the epilogue touches buffers the previous kernel may still be using
+        // bias and the device-side position are fetched now, under the wait for the last MMAs
+        if (epi.bias) {
+            if (n4 < N) b4.x = epi.bias[n4];
+            if (n4 + 1 < N) b4.y = epi.bias[n4 + 1];
+            if (n4 + 2 < N) b4.z = epi.bias[n4 + 2];
+            if (n4 + 3 < N) b4.w = epi.bias[n4 + 3];
+        }
+        if (epi.mode == EPI_QKV && epi.pos_ptr) e2.pos_off = epi.pos_off + *epi.pos_ptr;
         bar_sync_dequant<DQ>();
         if (!abort_flag) tc::mbar_wait(S.acc_full, 0, &abort_flag, dev_err, ERR_ACC);
         bar_sync_dequant<DQ>();
@@ -270,18 +285,7 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
             // phase 2: one warp per token row, lane l owns features 4l..4l+3
             const int w8 = warp - 3;
             constexpr int NW = 4 * NG; // epilogue warps
-            const int n4 = nt * TILE_N + lane * 4;
             const int tile_lin = mt * gridDim.x + nt;
-            float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (epi.bias) {
-                if (n4 < N) b4.x = epi.bias[n4];
-                if (n4 + 1 < N) b4.y = epi.bias[n4 + 1];
-                if (n4 + 2 < N) b4.z = epi.bias[n4 + 2];
-                if (n4 + 3 < N) b4.w = epi.bias[n4 + 3];
-            }
-            Epilogue e2 = epi; // the device-side position is read once per thread, not once per element
-            if (epi.mode == EPI_QKV && epi.pos_ptr) e2.pos_off = epi.pos_off + *epi.pos_ptr;
-            e2.pos_ptr = nullptr;
             const float4 *stage4 = reinterpret_cast<const float4 *>(stage);
             const int rows = min(MB, M - mt * MB);
             if (splits == 1) {
@@ -354,17 +358,7 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
         cluster.sync(); // every block of the cluster has staged its partial tile
         if (warp >= 3 && !abort_flag) {
             constexpr int NW = 4 * NG;
-            const int w8 = warp - 3, n4 = nt * TILE_N + lane * 4;
-            float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (epi.bias) {
-                if (n4 < N) b4.x = epi.bias[n4];
-                if (n4 + 1 < N) b4.y = epi.bias[n4 + 1];
-                if (n4 + 2 < N) b4.z = epi.bias[n4 + 2];
-                if (n4 + 3 < N) b4.w = epi.bias[n4 + 3];
-            }
-            Epilogue e2 = epi;
-            if (epi.mode == EPI_QKV && epi.pos_ptr) e2.pos_off = epi.pos_off + *epi.pos_ptr;
-            e2.pos_ptr = nullptr;
+            const int w8 = warp - 3;
             const float4 *stage4 = reinterpret_cast<const float4 *>(gen_base);
             const int rows = min(MB, M - mt * MB);
             for (int c = split + splits * w8; c < rows; c += splits * NW) {

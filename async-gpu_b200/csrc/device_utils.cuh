@@ -109,6 +109,38 @@ __device__ __forceinline__ void epi_store4(const Epilogue &e, int m, int n, floa
     }
 }
 
+// Bias of the four features n..n+3 (zero without a bias and past N).
+__device__ __forceinline__ float4 epi_bias4(const Epilogue &e, int n, int N) {
+    float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (e.bias) {
+        if (n < N) b.x = e.bias[n];
+        if (n + 1 < N) b.y = e.bias[n + 1];
+        if (n + 2 < N) b.z = e.bias[n + 2];
+        if (n + 3 < N) b.w = e.bias[n + 3];
+    }
+    return b;
+}
+
+// Residual epilogue as a reduction at L2: resid[m, n..n+3] += v with one vector `red` (no load for
+// the warp to wait on), element-wise atomics where the row is not 16-byte aligned or crosses N.
+// Several K splits may add to the same element; the order of their additions is then not fixed.
+__device__ __forceinline__ void epi_resid_red4(const Epilogue &e, int m, int n, float4 v, int N) {
+    float *dst = e.resid + (size_t)m * e.ldo + n;
+    if ((n + 3 < N) && ((e.ldo & 3) == 0)) {
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                     : "memory");
+    } else {
+        if (n < N) atomicAdd(dst, v.x);
+        if (n + 1 < N) atomicAdd(dst + 1, v.y);
+        if (n + 2 < N) atomicAdd(dst + 2, v.z);
+        if (n + 3 < N) atomicAdd(dst + 3, v.w);
+    }
+}
+
+__device__ __forceinline__ float4 f4_add(float4 a, float4 b) {
+    return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+}
+
 // Same, from a raw accumulated dot product.
 __device__ __forceinline__ void epi_apply(const Epilogue &e, int m, int n, float acc) {
     epi_store(e, m, n, acc + (e.bias ? e.bias[n] : 0.0f));

@@ -50,10 +50,6 @@ __device__ __forceinline__ void bar_sync_epi() {
     asm volatile("bar.sync 1, %0;" ::"n"(NTHREADS) : "memory");
 }
 
-__device__ __forceinline__ float4 f4_add(float4 a, float4 b) {
-    return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
-}
-
 // MB: token-tile width (the MMA's N); NS: operand stages; NE: epilogue groups of four warps;
 // TW: fp16 terms of the weight (1: hi, 2: hi + lo; tmap_w2 is read only with TW = 2).
 template <int MB, int NS, int NE, int TW>
@@ -178,12 +174,7 @@ f16_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         const int colh = w8 >> 2;         // the NE warps of a quadrant split the token columns
         pdl_wait(); // the epilogue touches buffers the previous kernel may still be using
         // bias and the device-side position are fetched under the wait for the accumulator
-        if (epi.bias) {
-            if (n4 < N) b4.x = epi.bias[n4];
-            if (n4 + 1 < N) b4.y = epi.bias[n4 + 1];
-            if (n4 + 2 < N) b4.z = epi.bias[n4 + 2];
-            if (n4 + 3 < N) b4.w = epi.bias[n4 + 3];
-        }
+        b4 = epi_bias4(epi, n4, N);
         if (epi.mode == EPI_QKV && epi.pos_ptr) e2.pos_off = epi.pos_off + *epi.pos_ptr;
         // (the vote keeps the warp converged for the warp-collective wait)
         if (!__any_sync(0xffffffffu, abort_flag != 0)) tc::mbar_wait(acc_full, 0, &abort_flag, dev_err, ERR_ACC);
@@ -219,21 +210,8 @@ f16_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 // reductions at L2; the bias goes in with split 0.  The order of the additions is not
                 // fixed, so the last bits of the sum can differ between runs.
                 const float4 add0 = (split == 0) ? b4 : make_float4(0.f, 0.f, 0.f, 0.f);
-                const bool vec = (n4 + 3 < N) && ((epi.ldo & 3) == 0);
-                for (int c = w8; c < rows; c += NW) {
-                    const float4 v = f4_add(stage4[c * 32 + lane], add0);
-                    float *dst = epi.resid + (size_t)(mt * MB + c) * epi.ldo + n4;
-                    if (vec) {
-                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v.x), "f"(v.y),
-                                     "f"(v.z), "f"(v.w)
-                                     : "memory");
-                    } else {
-                        if (n4 < N) atomicAdd(dst, v.x);
-                        if (n4 + 1 < N) atomicAdd(dst + 1, v.y);
-                        if (n4 + 2 < N) atomicAdd(dst + 2, v.z);
-                        if (n4 + 3 < N) atomicAdd(dst + 3, v.w);
-                    }
-                }
+                for (int c = w8; c < rows; c += NW)
+                    epi_resid_red4(epi, mt * MB + c, n4, f4_add(stage4[c * 32 + lane], add0), N);
             } // else: the splits are one cluster, summed below
         }
     }
@@ -421,13 +399,7 @@ f16_gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
             const int b = j & 1;
             const int mt = t / n_tiles, nt = t - mt * n_tiles;
             const int n4 = nt * 128 + lane * 4;
-            float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (epi.bias) { // fetched under the wait for the accumulator
-                if (n4 < N) b4.x = epi.bias[n4];
-                if (n4 + 1 < N) b4.y = epi.bias[n4 + 1];
-                if (n4 + 2 < N) b4.z = epi.bias[n4 + 2];
-                if (n4 + 3 < N) b4.w = epi.bias[n4 + 3];
-            }
+            const float4 b4 = epi_bias4(epi, n4, N); // fetched under the wait for the accumulator
             bool ok = true;
             if (!__any_sync(0xffffffffu, abort_flag != 0))
                 ok = tc::mbar_wait(acc_full + 8 * b, (j >> 1) & 1, &abort_flag, dev_err, ERR_ACC);
@@ -448,16 +420,11 @@ f16_gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
                 }
                 bar_sync_epi<EPI>();
                 const int lim = min(CH, rows - c0);
-                if (epi.mode == EPI_RESID && n4 + 3 < N && (epi.ldo & 3) == 0) {
-                    // this block is the only one that adds to these elements: a vector reduction at
-                    // L2 does the read-modify-write there, with no load for the warp to wait on
-                    for (int c = w8; c < lim; c += NW) {
-                        const float4 v = f4_add(stage4[c * 32 + lane], b4);
-                        float *dst = epi.resid + (size_t)(mt * MB + c0 + c) * epi.ldo + n4;
-                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v.x), "f"(v.y),
-                                     "f"(v.z), "f"(v.w)
-                                     : "memory");
-                    }
+                if (epi.mode == EPI_RESID) {
+                    // this block is the only one that adds to these elements: a reduction at L2 does
+                    // the read-modify-write there, with no load for the warp to wait on
+                    for (int c = w8; c < lim; c += NW)
+                        epi_resid_red4(epi, mt * MB + c0 + c, n4, f4_add(stage4[c * 32 + lane], b4), N);
                 } else {
                     for (int c = w8; c < lim; c += NW)
                         epi_store4(e2, mt * MB + c0 + c, n4, f4_add(stage4[c * 32 + lane], b4), N);

@@ -52,10 +52,6 @@ __device__ __forceinline__ void bar_sync_dequant() {
     asm volatile("bar.sync 1, %0;" ::"n"(NTHREADS) : "memory");
 }
 
-__device__ __forceinline__ float4 f4_add(float4 a, float4 b) {
-    return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
-}
-
 // MB: token-tile width; NS: operand stages (activation tiles in shared memory, dequantised weight
 // tiles in TMEM); NP: packed-weight stages; NG: dequant groups; TC: TMEM columns to allocate.
 template <int MB, int NS, int NP, int NG, int TC>
@@ -250,12 +246,7 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
         }
         pdl_wait(); // the epilogue touches buffers the previous kernel may still be using
         // bias and the device-side position are fetched now, under the wait for the last MMAs
-        if (epi.bias) {
-            if (n4 < N) b4.x = epi.bias[n4];
-            if (n4 + 1 < N) b4.y = epi.bias[n4 + 1];
-            if (n4 + 2 < N) b4.z = epi.bias[n4 + 2];
-            if (n4 + 3 < N) b4.w = epi.bias[n4 + 3];
-        }
+        b4 = epi_bias4(epi, n4, N);
         if (epi.mode == EPI_QKV && epi.pos_ptr) e2.pos_off = epi.pos_off + *epi.pos_ptr;
         bar_sync_dequant<DQ>();
         if (!abort_flag) tc::mbar_wait(S.acc_full, 0, &abort_flag, dev_err, ERR_ACC);
@@ -297,21 +288,8 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
                 // bias goes in with split 0.  The order in which the splits' partials are added is not
                 // fixed, so the last bits of the sum can differ between runs.
                 const float4 add0 = (split == 0) ? b4 : make_float4(0.f, 0.f, 0.f, 0.f);
-                const bool vec = (n4 + 3 < N) && ((epi.ldo & 3) == 0);
-                for (int c = w8; c < rows; c += NW) {
-                    const float4 v = f4_add(stage4[c * 32 + lane], add0);
-                    float *dst = epi.resid + (size_t)(mt * MB + c) * epi.ldo + n4;
-                    if (vec) {
-                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v.x), "f"(v.y),
-                                     "f"(v.z), "f"(v.w)
-                                     : "memory");
-                    } else {
-                        if (n4 < N) atomicAdd(dst, v.x);
-                        if (n4 + 1 < N) atomicAdd(dst + 1, v.y);
-                        if (n4 + 2 < N) atomicAdd(dst + 2, v.z);
-                        if (n4 + 3 < N) atomicAdd(dst + 3, v.w);
-                    }
-                }
+                for (int c = w8; c < rows; c += NW)
+                    epi_resid_red4(epi, mt * MB + c, n4, f4_add(stage4[c * 32 + lane], add0), N);
             } else if (cluster_mode) {
                 // the K splits of this tile are one thread-block cluster: their staged partial tiles are
                 // summed through distributed shared memory below, where every thread of the block can

@@ -17,6 +17,15 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const float *__restrict_
     __shared__ float red[32];
     const int row = blockIdx.x, tid = threadIdx.x;
     pdl_trigger();
+    // scale and shift are constants: fetched before the wait on the previous kernel, not after the
+    // two reductions where their latency would sit at the end of the block's critical path
+    float g[VPT], bt[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        int j = tid + i * 256;
+        g[i] = (j < d) ? gamma[j] : 0.0f;
+        bt[i] = (j < d) ? beta[j] : 0.0f;
+    }
     pdl_wait();
     const float *xr = x + (size_t)row * d;
     const float *rr = res_in ? res_in + (size_t)row * d : nullptr;
@@ -48,7 +57,7 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const float *__restrict_
     for (int i = 0; i < VPT; ++i) {
         int j = tid + i * 256;
         if (j < d) {
-            float y = (v[i] - mean) * inv_std * gamma[j] + beta[j];
+            float y = (v[i] - mean) * inv_std * g[i] + bt[i];
             if constexpr (sizeof(TOut) == 2)
                 out[(size_t)row * d + j] = __float2half_rn(y);
             else

@@ -10,7 +10,11 @@ prompt of 128 random token ids, greedy decode of 128 tokens.  A "step" is one gr
 every sequence of the batch (all layers, LM head, argmax, token fed back on the device) at context
 128 + (step mod 128).  Weights and token ids are seeded synthetic data.
 
-One JSON line is printed by rank 0; see DESIGN.md for the meaning of every key.
+One JSON line is printed by rank 0: `value` = sequences x steps / max-over-ranks CUDA-event time with
+all state resident in HBM; `e2e` = the same metric through generate_batch (host prompt ids in, host
+tokens out, prefill included); `roofline` = the dominant kernel family of a step timed alone
+(algorithmic bytes / time against the measured HBM peak); `prefill` = this rank's prompts through all
+layers; `gemv` = one-row dequant-GEMV bandwidth; `cpu_baseline` = the oracle on the host cores.
 """
 from __future__ import annotations
 

@@ -461,3 +461,28 @@ def test_prefill_of_16384_rows_takes_the_persistent_gemm(reg, int4):
     same = (out == out1).all(axis=1).mean()
     assert same > 0.9, same  # different accumulation order may flip a near-tie in a few sequences
     assert reg.device_error() == 0
+
+
+@pytest.mark.parametrize("preset,batch,prompt_len,new", [("small", 32, 24, 16), ("xl", 256, 16, 8)])
+def test_full_size_int4_models_against_oracle(reg, preset, batch, prompt_len, new):
+    """The benchmark's two model configurations at full size (GPT-2 Small and XL, every Linear and the LM
+    head int4 g128, fp16 KV cache, 50257-token vocabulary) with their batch sizes, so that every kernel
+    runs at the benchmark's shapes; the first and the last sequence of the batch are checked against the
+    oracle token by token (it runs them one at a time), with shorter prompts than the benchmark's to
+    keep the CPU side at seconds."""
+    cfg = getattr(Gpt2Config, preset)()
+    w = synth.gpt2_weights(cfg)
+    m = Int4Gpt2Model.from_weights(w, cfg, reg, flags=b200nn.QUANT_LM_HEAD, group_size=128)
+    om = oracle.Model(cfg.as_dict(), _int4_oracle_weights(m, cfg, w, True))
+    del w
+    prompts = synth.token_ids(synth.BASE_SEED + 7, (batch, prompt_len), cfg.vocab_size)
+    out, lens = m.generate_batch(prompts, new)
+    assert out.shape == (batch, prompt_len + new)
+    for b in (0, batch - 1):
+        ref, lg = om.generate_cached(prompts[b], new, flags=oracle.KV_FP16, want_logits=True)
+        _check_tokens(out[b][: lens[b]], ref, lg, prompt_len)
+    # logits of the last prompt position of one sequence through the public forward
+    got = m.forward(prompts[0]).to_host()[-1]
+    ref = om.forward(prompts[0], flags=oracle.KV_FP16)[-1]
+    assert np.abs(got - ref).max() < MAX_ABS and np_ref.rel_rms(got, ref) < REL_RMS
+    assert reg.device_error() == 0

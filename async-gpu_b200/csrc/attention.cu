@@ -492,7 +492,7 @@ int launch_decode_attention(b200nn_ctx *ctx, const void *q, bool q_half, int ldq
         CK_LAUNCH(ctx, "decode_attn_stream_kernel");
         return B200NN_OK;
     }
-    int n_splits = (4 * ctx->sm_count + pairs - 1) / pairs;
+    int n_splits = (ctx->attn_blocks_per_sm * ctx->sm_count + pairs - 1) / pairs;
     int max_splits = (max_ctx_hint + 63) / 64;
     if (n_splits > max_splits) n_splits = max_splits;
     if (n_splits > 32) n_splits = 32;

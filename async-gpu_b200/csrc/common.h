@@ -55,6 +55,7 @@ struct b200nn_ctx {
     int attn_stream_min10 = 20;   // ... when there are at least this many tenths of a pair per warp of its grid
                                   // (measured: 2.7 pairs per warp 9 % faster than the split kernel, 1.35 pairs 13 % slower)
     int attn_split_items = 0;    // items the streaming decode attention hands out as two halves at the end
+    int attn_blocks_per_sm = 4;  // blocks per SM the split-context decode attention aims for when it splits the context
     int kv_prefetch_mb = 64;     // KV-cache bytes the streaming decode attention asks into L2 before its wait
     int pdl = 1;                  // launch the decode-step kernels with programmatic dependent launch
     int f32_tc = 2;               // f32 Linears of more than four rows on the tensor cores: 0 off (f32 FMA kernels),

@@ -99,7 +99,9 @@ B200NN_API int32_t b200nn_ctx_set_gemv_max_rows(b200nn_ctx *ctx, int32_t rows);
  * "attn_stream" (0 = never use the TMA-fed decode-attention kernel), "attn_stream_min10" (tenths of
  * a (sequence, head) pair per warp of its grid from which it is used; default 20), "kv_prefetch_mb" (KV-cache
  * megabytes that kernel asks into L2 before its dependency wait), "attn_split_items" (items it
- * hands out as two halves at the end of the grid; 0 = none).
+ * hands out as two halves at the end of the grid; 0 = none), "attn_blocks_per_sm" (blocks per SM the
+ * split-context decode attention aims for when it splits the context of few pairs; default 4, measured
+ * best: 8 and more cost 0.2 ms per GPT-2 XL step at 32 sequences through the merge of the partials).
  * "f32_tc" selects how an f32 Linear (linear.rs:283-313) multiplies more than four rows: 2 (default;
  * negative restores it) fp16 activations times the weight held as fp16 hi + lo on the tensor cores,
  * f32 accumulation (the weight enters with about 22 bits, the activations with fp16's 11); 1 the

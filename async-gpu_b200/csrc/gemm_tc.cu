@@ -22,8 +22,11 @@
 //               Afterwards the same warps move the accumulator TMEM -> shared memory and run the
 //               epilogue row-wise: one warp per token row, 4 features per lane, so that every
 //               global access is a 512-byte contiguous row segment.
-// K can be split across blocks; partial tiles go to scratch and the last block to arrive sums them
-// in split order (deterministic) before the epilogue.
+// K can be split across blocks.  The residual epilogue adds every split's partial tile into the f32
+// residual stream with vector reductions at L2 (order of the additions not fixed).  The other
+// epilogues need the complete sum: up to eight splits run as one thread-block cluster and add their
+// staged partial tiles through distributed shared memory in split order (deterministic); beyond
+// eight (only by override) partial tiles go to scratch and the last block to arrive sums them.
 //
 // Every wait on an mbarrier is bounded: when it runs out the block records a code in the device
 // error word, all roles leave their loops, TMEM is freed and the kernel returns.

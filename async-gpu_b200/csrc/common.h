@@ -47,7 +47,9 @@ struct b200nn_ctx {
     size_t n_counters = 0;
     std::vector<void *> retired;  // outgrown scratch / counter blocks, freed with the context
     void *encode_tiled = nullptr; // cuTensorMapEncodeTiled, resolved through the runtime
-    int tc_mb = 0, tc_splits = 0, tc_min_kb = 4; // tensor-core GEMM tuning overrides (0 = automatic)
+    int tc_mb = 0, tc_splits = 0; // tensor-core GEMM tuning overrides (0 = automatic)
+    int tc_min_kb = 3;            // fewest 64-wide K blocks a K split may get (3 measured best at 16..128 rows:
+                                  // 1.69 against 1.76 ms per GPT-2 XL step at 32 rows with 4; no difference at 256)
     long long *trace = nullptr;  // optional device buffer for in-kernel time stamps (measurement aid)
     uint32_t fam_mask = 0xffffffffu; // kernel families run_blocks / run_head launch (timing aid)
     int attn_tc = 1;              // prefill attention with fp16 q and output runs on the tensor cores

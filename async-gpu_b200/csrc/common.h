@@ -48,6 +48,7 @@ struct b200nn_ctx {
     std::vector<void *> retired;  // outgrown scratch / counter blocks, freed with the context
     void *encode_tiled = nullptr; // cuTensorMapEncodeTiled, resolved through the runtime
     int tc_mb = 0, tc_splits = 0; // tensor-core GEMM tuning overrides (0 = automatic)
+    int tc_min_kb_cluster = 6;    // the same for splits that run as a cluster (their partial tiles cross shared memory)
     int tc_min_kb = 3;            // fewest 64-wide K blocks a K split may get (3 measured best at 16..128 rows:
                                   // 1.69 against 1.76 ms per GPT-2 XL step at 32 rows with 4; no difference at 256)
     long long *trace = nullptr;  // optional device buffer for in-kernel time stamps (measurement aid)

@@ -503,7 +503,7 @@ int launch_cfg(b200nn_ctx *ctx, const WOperand &w, const __half *x, int M, const
     if (epi.mode == EPI_RESID)
         splits = std::min(std::max(1, target / base_ctas), std::max(1, k_blocks / ctx->tc_min_kb));
     else
-        splits = std::min(std::min(8, std::max(1, target / base_ctas)), std::max(1, k_blocks / (2 * ctx->tc_min_kb)));
+        splits = std::min(std::min(8, std::max(1, target / base_ctas)), std::max(1, k_blocks / ctx->tc_min_kb_cluster));
     splits = std::max(1, std::min(splits, 32));
     if (ctx->tc_splits > 0) splits = std::min(ctx->tc_splits, epi.mode == EPI_RESID ? k_blocks : std::min(8, k_blocks));
     const int per = (k_blocks + splits - 1) / splits;

@@ -414,7 +414,7 @@ int launch_cfg(b200nn_ctx *ctx, const Int4Weight &w, const __half *x, int M, con
     if (epi.mode == EPI_RESID)
         splits = std::min(std::max(1, target / base_ctas), std::max(1, w.k_blocks / ctx->tc_min_kb));
     else
-        splits = std::min(std::min(8, std::max(1, target / base_ctas)), std::max(1, w.k_blocks / (2 * ctx->tc_min_kb)));
+        splits = std::min(std::min(8, std::max(1, target / base_ctas)), std::max(1, w.k_blocks / ctx->tc_min_kb_cluster));
     splits = std::max(1, std::min(splits, 32));
     if (ctx->tc_splits > 0) splits = std::min(ctx->tc_splits, w.k_blocks);
     int per = (w.k_blocks + splits - 1) / splits;

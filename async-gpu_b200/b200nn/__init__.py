@@ -50,6 +50,19 @@ class _LayerW(C.Structure):
         "ln_2_weight", "ln_2_bias", "mlp_fc_weight", "mlp_fc_bias", "mlp_proj_weight", "mlp_proj_bias")]
 
 
+class _BlockW(C.Structure):
+    _fields_ = [(n, _f32p) for n in (
+        "ln_1_weight", "ln_1_bias", "attn_qkv_weight", "attn_qkv_bias", "attn_out_weight", "attn_out_bias",
+        "ln_2_weight", "ln_2_bias", "ffn_up_weight", "ffn_up_bias", "ffn_down_weight", "ffn_down_bias")]
+
+
+class _Diag(C.Structure):
+    _fields_ = [("embedding_first", C.c_float * 4), ("embedding_last", C.c_float * 4), ("block0_last", C.c_float * 4),
+                ("final_block_last", C.c_float * 4), ("block0_nonfinite", C.c_int32), ("final_block_nonfinite", C.c_int32),
+                ("ln_f_last", C.c_float * 4), ("top_tokens", C.c_uint32 * 5), ("top_scores", C.c_float * 5),
+                ("n_top", C.c_int32)]
+
+
 class _Weights(C.Structure):
     _fields_ = [("wte", _f32p), ("wpe", _f32p), ("ln_f_weight", _f32p), ("ln_f_bias", _f32p),
                 ("layers", C.POINTER(_LayerW))]
@@ -77,6 +90,7 @@ def load_library() -> C.CDLL:
             "b200nn_ctx_set_gemv_max_rows": (i32, [vp, i32]),
             "b200nn_ctx_set_tuning": (i32, [vp, C.c_char_p, i32]),
             "b200nn_ctx_read_trace": (i32, [vp, C.POINTER(C.c_longlong)]),
+            "b200nn_ctx_read_persist_trace": (i32, [vp, C.POINTER(C.c_uint64), sz]),
             "b200nn_tensor_from_host": (i32, [vp, _f32p, szp, i32, vpp]),
             "b200nn_tensor_zeros": (i32, [vp, szp, i32, vpp]), "b200nn_tensor_to_host": (i32, [vp, _f32p, sz]),
             "b200nn_tensor_ndim": (i32, [vp]), "b200nn_tensor_numel": (sz, [vp]),
@@ -121,6 +135,11 @@ def load_library() -> C.CDLL:
             "b200nn_gpt2_quantized_memory_bytes": (sz, [vp]),
             "b200nn_gpt2_get_int4": (i32, [vp, i32, i32, _u32p, _f32p, szp, szp]),
             "b200nn_gpt2_forward": (i32, [vp, _u32p, sz, vpp]),
+            "b200nn_block_create": (i32, [vp, C.POINTER(_Cfg), C.POINTER(_BlockW), u32, vpp]),
+            "b200nn_int4_block_create": (i32, [vp, C.POINTER(_Cfg), C.POINTER(_BlockW), sz, u32, vpp]),
+            "b200nn_block_forward": (i32, [vp, vp, vpp]),
+            "b200nn_block_forward_cached": (i32, [vp, vp, _f32p, _f32p, sz, vpp, _f32p, _f32p]),
+            "b200nn_block_destroy": (None, [vp]),
             "b200nn_kvcache_create": (i32, [vp, sz, sz, vpp]), "b200nn_kvcache_len": (sz, [vp]),
             "b200nn_kvcache_reset": (i32, [vp]), "b200nn_kvcache_destroy": (None, [vp]),
             "b200nn_gpt2_forward_cached": (i32, [vp, _u32p, sz, vp, vpp]),
@@ -152,6 +171,16 @@ def load_library() -> C.CDLL:
             "b200nn_safetensors_read": (i32, [vp, i32, vp, sz]),
             "b200nn_safetensors_last_error": (C.c_char_p, []),
             "b200nn_gpt2_load_safetensors": (i32, [vp, C.c_char_p, C.POINTER(_Cfg), sz, u32, vpp]),
+            "b200nn_bpe_load": (i32, [C.c_char_p, u32, vpp]),
+            "b200nn_bpe_create": (i32, [C.c_char_p, szp, _u32p, sz, u32, vpp]),
+            "b200nn_bpe_destroy": (None, [vp]), "b200nn_bpe_vocab_size": (sz, [vp]),
+            "b200nn_bpe_encode": (i32, [vp, C.c_char_p, sz, _u32p, sz, szp]),
+            "b200nn_bpe_encode_piece": (i32, [vp, C.c_char_p, sz, _u32p, sz, szp]),
+            "b200nn_bpe_decode": (i32, [vp, _u32p, sz, C.c_char_p, sz, szp]),
+            "b200nn_bpe_last_error": (C.c_char_p, []),
+            "b200nn_gpt2_forward_diagnostic": (i32, [vp, _u32p, sz, vpp, C.POINTER(_Diag)]),
+            "b200nn_prefill_attention_f16": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
+            "b200nn_decode_attention_f16": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
             "b200nn_decode_attention_noalloc": (i32, [i32, vp, vp, vp, vp, i32, i32, i32, i32, vp]),
             "b200nn_noalloc_last_error": (C.c_char_p, []),
             "b200nn_session_destroy": (None, [vp]),
@@ -219,6 +248,12 @@ class KernelRegistry:
 
     def set_tuning(self, key: str, value: int):
         self.check(self.lib.b200nn_ctx_set_tuning(self.h, key.encode(), value))
+
+    def read_persist_trace(self, blocks: int = 148) -> np.ndarray:
+        """[block, 32, 2] nanosecond stamps of the persistent decode kernel's last launch (measurement aid)."""
+        out = np.zeros((blocks, 32, 2), dtype=np.uint64)
+        self.check(self.lib.b200nn_ctx_read_persist_trace(self.h, out.ctypes.data_as(C.POINTER(C.c_uint64)), out.size))
+        return out
 
     def device_error(self) -> int:
         w = C.c_uint32()
@@ -297,7 +332,9 @@ def _out(reg, rc, h):
 
 from . import ops  # noqa: E402
 from .layers import Embedding, Int4Linear, LayerNorm, Linear, MultiHeadAttention, GELU  # noqa: E402
-from .gpt2 import Gpt2Config, Gpt2Model, Int4Gpt2Model, KvCache, DecodeSession  # noqa: E402
+from .gpt2 import (Gpt2Config, Gpt2Model, Int4Gpt2Model, KvCache, DecodeSession, TransformerBlock,  # noqa: E402
+                   Int4TransformerBlock)
 from .sampling import SimpleRng, top_k_sample  # noqa: E402
+from .tokenizer import Gpt2Tokenizer, TokenizerError, GPT2_VOCAB_SIZE, ENDOFTEXT_TOKEN_ID  # noqa: E402
 from .checkpoint import (SafeTensorsFile, TensorInfo, list_tensors, load_all_tensors, load_gpt2_weights,  # noqa: E402
                          load_int4_tensors)

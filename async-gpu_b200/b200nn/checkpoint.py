@@ -105,7 +105,7 @@ def load_int4_tensors(path):
     ``[ceil(in/group), out]``); everything else is F32.  Returns ``(int4, dense)``: ``int4[key]`` =
     ``(packed, scales, in_features, out_features, group_size)`` exactly as ``Int4Linear`` takes them
     (int4_linear.rs:40-48), ``dense[key]`` = f32 array.  The group size is read off the shapes (the
-    script's 128 unless the matrix is shorter than one group)."""
+    script's 128 whenever 128-wide groups tile the matrix, else in_features / scale rows)."""
     int4, dense, packed, scales = {}, {}, {}, {}
     with SafeTensorsFile(path) as f:
         for i in range(len(f)):
@@ -130,10 +130,13 @@ def load_int4_tensors(path):
         if s.shape[1] != n or s.shape[0] < 1:
             raise NnError(ERR_UNSUPPORTED, f"{key}: scales {s.shape} do not match packed {p.shape}")
         g = s.shape[0]
-        group = k if g == 1 else -(-k // g)
-        if g > 1 and (group % 8 or -(-k // group) != g):  # the writer's groups are 128 wide, the last one ragged
-            group = 128
-        if -(-k // group) != g:
+        # the writer's groups are 128 wide with a ragged last one: that reading comes first; only a file
+        # it does not fit (another group size) falls back to in_features / rows
+        if -(-k // 128) == g:
+            group = min(128, k)
+        else:
+            group = k if g == 1 else -(-k // g)
+        if group % 8 or -(-k // group) != g:
             raise NnError(ERR_UNSUPPORTED, f"{key}: {g} scale rows do not tile in_features = {k}")
         int4[key] = (np.ascontiguousarray(p), np.ascontiguousarray(s), k, n, group)
     return int4, dense

@@ -7,8 +7,8 @@ from dataclasses import dataclass
 
 import numpy as np
 
-from . import (ERR_SHAPE, GpuTensor, KernelRegistry, NnError, PROF_NAMES, _Cfg, _LayerW, _Weights, _f32, _f32p, _u32,
-               _u32p)
+from . import (ERR_SHAPE, GpuTensor, KernelRegistry, NnError, PROF_NAMES, _BlockW, _Cfg, _Diag, _LayerW, _Weights, _f32,
+               _f32p, _u32, _u32p)
 
 
 @dataclass
@@ -182,6 +182,33 @@ class Gpt2Model:
         names = ["embedding"] + [f"block_{i}" for i in range(self.config.n_layer)] + ["ln_f", "lm_head"]
         return GpuTensor(self.reg, h), list(zip(names, [float(times[i]) for i in range(n.value)]))
 
+    def forward_diagnostic(self, token_ids, file=None):
+        """``forward_diagnostic`` (gpt2.rs:595-667): forward that prints the reference's ``[diag]`` lines
+        (to ``file``, default stderr) and returns (logits, the reported values as a dict)."""
+        import sys
+        t, tp = _u32(token_ids)
+        h, dg = C.c_void_p(), _Diag()
+        self.reg.check(self.reg.lib.b200nn_gpt2_forward_diagnostic(self.h, tp, t.size, C.byref(h), C.byref(dg)))
+        last, out = t.size - 1, file or sys.stderr
+        f4 = lambda a: "[" + ", ".join(f"{float(v):.6f}" for v in a) + "]"
+        print(f"[diag] Embedding pos0 first4: {f4(dg.embedding_first)}", file=out)
+        print(f"[diag] Embedding pos{last} first4: {f4(dg.embedding_last)}", file=out)
+        for i, vals, bad in ((0, dg.block0_last, dg.block0_nonfinite),
+                             (self.config.n_layer - 1, dg.final_block_last, dg.final_block_nonfinite)):
+            print(f"[diag] Layer {i} pos{last} first4: {f4(vals)}", file=out)
+            if bad:
+                print(f"[diag] WARNING: Layer {i} has {bad} NaN/Inf values!", file=out)
+        print(f"[diag] Final LN pos{last} first4: {f4(dg.ln_f_last)}", file=out)
+        print(f"[diag] Top-5 tokens at pos{last}:", file=out)
+        top = [(int(dg.top_tokens[i]), float(dg.top_scores[i])) for i in range(dg.n_top)]
+        for tok, score in top:
+            print(f"  token {tok}: {score:.4f}", file=out)
+        report = {"embedding_first": list(dg.embedding_first), "embedding_last": list(dg.embedding_last),
+                  "block0_last": list(dg.block0_last), "final_block_last": list(dg.final_block_last),
+                  "block0_nonfinite": dg.block0_nonfinite, "final_block_nonfinite": dg.final_block_nonfinite,
+                  "ln_f_last": list(dg.ln_f_last), "top": top}
+        return GpuTensor(self.reg, h), report
+
     def forward_cached(self, token_ids, new_len, cache: KvCache) -> GpuTensor:
         t, tp = _u32(token_ids)
         h = C.c_void_p()
@@ -328,3 +355,75 @@ class DecodeSession:
                 self.reg.lib.b200nn_session_destroy(self.h)
         except Exception:
             pass
+
+
+class TransformerBlock:
+    """``TransformerBlock::new(ln_1_weight, ln_1_bias, attn_qkv_weight, attn_qkv_bias, attn_out_weight,
+    attn_out_bias, ln_2_weight, ln_2_bias, ffn_up_weight, ffn_up_bias, ffn_down_weight, ffn_down_bias, &config,
+    &registry)`` (gpt2.rs:98-170): one pre-LN block; dense weights in Linear layout [out,in]."""
+    _create = "b200nn_block_create"
+
+    def __init__(self, ln_1_weight, ln_1_bias, attn_qkv_weight, attn_qkv_bias, attn_out_weight, attn_out_bias,
+                 ln_2_weight, ln_2_bias, ffn_up_weight, ffn_up_bias, ffn_down_weight, ffn_down_bias,
+                 config: Gpt2Config, reg: KernelRegistry, flags: int = 0, **extra):
+        d = config.n_embd
+        sizes = [d, d, 3 * d * d, 3 * d, d * d, d, d, d, 4 * d * d, 4 * d, 4 * d * d, d]
+        arrs = [np.ascontiguousarray(a, dtype=np.float32) for a in (
+            ln_1_weight, ln_1_bias, attn_qkv_weight, attn_qkv_bias, attn_out_weight, attn_out_bias, ln_2_weight,
+            ln_2_bias, ffn_up_weight, ffn_up_bias, ffn_down_weight, ffn_down_bias)]
+        for a, n in zip(arrs, sizes):
+            if a.size != n:
+                raise NnError(ERR_SHAPE, f"TransformerBlock: expected {n} elements, got {a.size}")
+        self.reg, self.config, self._keep = reg, config, arrs
+        w = _BlockW(*[a.ctypes.data_as(_f32p) for a in arrs])
+        cfg = config._c()
+        self.h = C.c_void_p()
+        reg.check(self._call_create(reg, cfg, w, flags, extra))
+
+    def _call_create(self, reg, cfg, w, flags, extra):
+        return reg.lib.b200nn_block_create(reg.h, C.byref(cfg), C.byref(w), flags, C.byref(self.h))
+
+    def forward(self, x: GpuTensor) -> GpuTensor:
+        """input [seq_len, n_embd] -> output [seq_len, n_embd] (gpt2.rs:172-204)."""
+        h = C.c_void_p()
+        self.reg.check(self.reg.lib.b200nn_block_forward(self.h, x.h, C.byref(h)))
+        return GpuTensor(self.reg, h)
+
+    forward_auto_fused = forward  # the fused epilogues are always on (gpt2.rs:206-243)
+
+    def forward_cached(self, x: GpuTensor, cached_k, cached_v, kv_len: int):
+        """``forward_cached(input, cached_k, cached_v, kv_len) -> (output, new_k, new_v)`` (gpt2.rs:249-288);
+        cached_k / cached_v: [n_head][kv_len*64]; new_k / new_v: [n_head, new_len*64]."""
+        H, new_len = self.config.n_head, x.shape()[0]
+        ck = cv = None
+        if kv_len:
+            ka, ck = _f32(np.asarray(cached_k, dtype=np.float32))
+            va, cv = _f32(np.asarray(cached_v, dtype=np.float32))
+            if ka.size != H * kv_len * 64 or va.size != H * kv_len * 64:
+                raise NnError(ERR_SHAPE, "forward_cached: cached K/V must hold n_head x kv_len x 64 values")
+        nk = np.empty((H, new_len * 64), dtype=np.float32)
+        nv = np.empty_like(nk)
+        h = C.c_void_p()
+        self.reg.check(self.reg.lib.b200nn_block_forward_cached(self.h, x.h, ck, cv, kv_len, C.byref(h),
+                                                                nk.ctypes.data_as(_f32p), nv.ctypes.data_as(_f32p)))
+        return GpuTensor(self.reg, h), nk, nv
+
+    def __del__(self):
+        try:
+            if self.h and self.reg.h:
+                self.reg.lib.b200nn_block_destroy(self.h)
+        except Exception:
+            pass
+
+
+class Int4TransformerBlock(TransformerBlock):
+    """``Int4TransformerBlock::new(..., &config, group_size, &registry)`` (gpt2.rs:1219-1296): the same twelve
+    slices, every dense weight quantised to int4 with ``group_size`` (attention through
+    ``Int4MultiHeadAttention``, gpt2.rs:1127-1214)."""
+
+    def __init__(self, *args, group_size: int = 128, **kw):
+        super().__init__(*args, group_size=group_size, **kw)
+
+    def _call_create(self, reg, cfg, w, flags, extra):
+        return reg.lib.b200nn_int4_block_create(reg.h, C.byref(cfg), C.byref(w), extra.get("group_size", 128), flags,
+                                                C.byref(self.h))

@@ -114,3 +114,16 @@ def int4_matmul(a: GpuTensor, b_host, k, n, group_size, reg):
     b, bp = _f32(b_host)
     h = C.c_void_p()
     return _out(reg, reg.lib.b200nn_int4_matmul(reg.h, a.h, bp, k, n, group_size, C.byref(h)), h)
+
+
+def prefill_attention_f16(q_ptr, k_cache_ptr, v_cache_ptr, batch, n_heads, capacity, seq_len, past, out_ptr, reg):
+    """Causal attention of ``seq_len`` new rows per sequence on caller-owned fp16 device buffers (device
+    pointers as ints): q / out ``[batch*seq_len, n_heads*64]``, caches ``[batch][n_heads][capacity][64]``."""
+    reg.check(reg.lib.b200nn_prefill_attention_f16(reg.h, q_ptr, k_cache_ptr, v_cache_ptr, batch, n_heads, capacity,
+                                                   seq_len, past, out_ptr))
+
+
+def decode_attention_f16(q_ptr, k_cache_ptr, v_cache_ptr, batch, n_heads, capacity, ctx_len, out_ptr, reg):
+    """One query row per sequence against the first ``ctx_len`` cached positions, fp16 device buffers."""
+    reg.check(reg.lib.b200nn_decode_attention_f16(reg.h, q_ptr, k_cache_ptr, v_cache_ptr, batch, n_heads, capacity,
+                                                  ctx_len, out_ptr))

@@ -669,6 +669,7 @@ struct NoAllocDevice {
     int sm_count = 0;
 };
 NoAllocDevice g_noalloc_dev[NOALLOC_MAX_DEVICES];
+std::mutex g_noalloc_mu;
 thread_local char g_noalloc_error[256] = "";
 
 int noalloc_fail(int code, const char *msg, cudaError_t e = cudaSuccess) {
@@ -686,6 +687,9 @@ extern "C" int32_t b200nn_decode_attention_noalloc(int32_t device, void *stream,
                                                    const void *k_cache_dev, const void *v_cache_dev, int32_t batch,
                                                    int32_t n_heads, int32_t capacity, int32_t ctx_len, float *out_dev) {
     if (!q_dev || !k_cache_dev || !v_cache_dev || !out_dev) return noalloc_fail(B200NN_ERR_ARG, "null buffer");
+    // the kernel reads cached rows with 16-byte loads: a misaligned cache would fault on the device
+    if ((reinterpret_cast<uintptr_t>(k_cache_dev) | reinterpret_cast<uintptr_t>(v_cache_dev)) & 15)
+        return noalloc_fail(B200NN_ERR_ARG, "k_cache_dev and v_cache_dev must be 16-byte aligned");
     if (device < 0 || device >= NOALLOC_MAX_DEVICES) return noalloc_fail(B200NN_ERR_ARG, "device ordinal out of range");
     if (batch <= 0 || n_heads <= 0 || capacity <= 0 || ctx_len <= 0 || ctx_len > capacity)
         return noalloc_fail(B200NN_ERR_SHAPE, "batch, n_heads, capacity must be positive and 1 <= ctx_len <= capacity");
@@ -698,6 +702,7 @@ extern "C" int32_t b200nn_decode_attention_noalloc(int32_t device, void *stream,
     if (prev != device && (e = cudaSetDevice(device)) != cudaSuccess) return noalloc_fail(B200NN_ERR_CUDA, "cudaSetDevice", e);
     int rc = B200NN_OK;
     NoAllocDevice &D = g_noalloc_dev[device];
+    std::lock_guard<std::mutex> setup_guard(g_noalloc_mu); // host threads may share a device's set-up
     if (!D.ready) { // set-up, once per device, with that device current
         void *rp = nullptr, *cp = nullptr;
         if ((e = cudaGetSymbolAddress(&rp, g_noalloc_records)) != cudaSuccess)

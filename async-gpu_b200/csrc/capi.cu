@@ -52,6 +52,8 @@ extern "C" void b200nn_ctx_destroy(b200nn_ctx *ctx) {
         cudaStreamDestroy(ctx->stream);
     }
     if (ctx->dev_err) cudaFree(ctx->dev_err);
+    if (ctx->host_err) cudaFreeHost(ctx->host_err);
+    if (ctx->persist_trace) cudaFree(ctx->persist_trace);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->counters) cudaFree(ctx->counters);
     for (void *p : ctx->retired) cudaFree(p);
@@ -75,8 +77,8 @@ extern "C" int32_t b200nn_ctx_trim(b200nn_ctx *ctx) {
 
 extern "C" int32_t b200nn_ctx_synchronize(b200nn_ctx *ctx) {
     if (!ctx) return B200NN_ERR_ARG;
-    CK(ctx, cudaStreamSynchronize(ctx->stream));
-    return B200NN_OK;
+    CK(ctx, cudaSetDevice(ctx->device));
+    return stream_sync_check(ctx);
 }
 extern "C" void *b200nn_ctx_stream(b200nn_ctx *ctx) { return ctx ? (void *)ctx->stream : nullptr; }
 extern "C" const char *b200nn_last_error_message(b200nn_ctx *ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
@@ -109,6 +111,18 @@ extern "C" int32_t b200nn_ctx_set_tuning(b200nn_ctx *ctx, const char *key, int32
         if (!value && ctx->trace) { cudaFree(ctx->trace); ctx->trace = nullptr; }
     }
     else if (!strcmp(key, "gemv_max_rows")) ctx->gemv_max_rows = value < 0 ? 2 : value;
+    else if (!strcmp(key, "persist")) ctx->persist = value ? 1 : 0;
+    else if (!strcmp(key, "persist_min_rows")) ctx->persist_min_rows = value < 1 ? 3 : value;
+    else if (!strcmp(key, "persist_max_rows")) ctx->persist_max_rows = value < 1 ? 256 : value;
+    else if (!strcmp(key, "persist_prefetch_mb")) ctx->persist_prefetch_mb = value < 0 ? 0 : value;
+    else if (!strcmp(key, "persist_wait_kcycles")) ctx->persist_wait_cycles = value <= 0 ? 0 : 1000LL * value;
+    else if (!strcmp(key, "persist_fault_phase")) ctx->persist_fault_phase = value;
+    else if (!strcmp(key, "persist_trace")) { // value != 0: allocate (once) and clear the phase-stamp buffer
+        const size_t bytes = (size_t)256 * 32 * 2 * sizeof(unsigned long long);
+        if (value && !ctx->persist_trace && cudaMalloc(&ctx->persist_trace, bytes) != cudaSuccess) return B200NN_ERR_CUDA;
+        if (ctx->persist_trace) cudaMemset(ctx->persist_trace, 0, bytes);
+        if (!value && ctx->persist_trace) { cudaStreamSynchronize(ctx->stream); cudaFree(ctx->persist_trace); ctx->persist_trace = nullptr; }
+    }
     else return set_error(ctx, B200NN_ERR_UNSUPPORTED, std::string("unknown tuning key ") + key);
     return B200NN_OK;
 }
@@ -116,6 +130,13 @@ extern "C" int32_t b200nn_ctx_read_trace(b200nn_ctx *ctx, long long *out256) {
     if (!ctx || !out256 || !ctx->trace) return B200NN_ERR_ARG;
     CK(ctx, cudaStreamSynchronize(ctx->stream));
     CK(ctx, cudaMemcpy(out256, ctx->trace, 256 * sizeof(long long), cudaMemcpyDeviceToHost));
+    return B200NN_OK;
+}
+extern "C" int32_t b200nn_ctx_read_persist_trace(b200nn_ctx *ctx, unsigned long long *out, size_t capacity) {
+    if (!ctx || !out || !ctx->persist_trace) return B200NN_ERR_ARG;
+    const size_t n = std::min(capacity, (size_t)256 * 32 * 2);
+    CK(ctx, cudaStreamSynchronize(ctx->stream));
+    CK(ctx, cudaMemcpy(out, ctx->persist_trace, n * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
     return B200NN_OK;
 }
 extern "C" int32_t b200nn_ctx_device_error(b200nn_ctx *ctx, uint32_t *word_out) {
@@ -156,8 +177,7 @@ extern "C" int32_t b200nn_tensor_to_host(const b200nn_tensor *t, float *host, si
     if (capacity_elems < t->numel) return set_error(ctx, B200NN_ERR_SHAPE, "to_host: destination too small");
     CK(ctx, cudaSetDevice(ctx->device));
     CK(ctx, cudaMemcpyAsync(host, t->buf->p, t->numel * 4, cudaMemcpyDeviceToHost, ctx->stream));
-    CK(ctx, cudaStreamSynchronize(ctx->stream));
-    return B200NN_OK;
+    return stream_sync_check(ctx);
 }
 extern "C" int32_t b200nn_tensor_ndim(const b200nn_tensor *t) { return t ? (int32_t)t->shape.size() : 0; }
 extern "C" size_t b200nn_tensor_numel(const b200nn_tensor *t) { return t ? t->numel : 0; }

@@ -164,3 +164,34 @@ extern "C" int32_t b200nn_attention_kv(b200nn_ctx *ctx, const b200nn_tensor *q, 
     *out = y3;
     return B200NN_OK;
 }
+
+// ---- batched attention on caller-owned fp16 device buffers ------------------------------------
+// The kernels of the model path as stand-alone operations: q and out are token-major rows
+// [batch*rows, n_heads*64] fp16, the caches fp16 [batch][n_heads][capacity][64] with the new positions
+// already appended.  Stream-ordered on the context's stream; nothing is copied or allocated
+// except the decode kernel's split scratch on first use.
+extern "C" int32_t b200nn_prefill_attention_f16(b200nn_ctx *ctx, const void *q_dev, const void *k_cache_dev,
+                                                const void *v_cache_dev, int32_t batch, int32_t n_heads, int32_t capacity,
+                                                int32_t seq_len, int32_t past, void *out_dev) {
+    if (!ctx || !q_dev || !k_cache_dev || !v_cache_dev || !out_dev) return B200NN_ERR_ARG;
+    if (batch <= 0 || n_heads <= 0 || seq_len <= 0 || past < 0 || past + seq_len > capacity)
+        return set_error(ctx, B200NN_ERR_SHAPE, "prefill_attention_f16: need batch, heads, seq_len > 0 and past + seq_len <= capacity");
+    if (((uintptr_t)q_dev | (uintptr_t)k_cache_dev | (uintptr_t)v_cache_dev | (uintptr_t)out_dev) & 15)
+        return set_error(ctx, B200NN_ERR_ARG, "prefill_attention_f16: buffers must be 16-byte aligned");
+    CK(ctx, cudaSetDevice(ctx->device));
+    return launch_prefill_attention(ctx, q_dev, true, n_heads * 64, (const __half *)k_cache_dev, (const __half *)v_cache_dev,
+                                    batch, n_heads, capacity, seq_len, past, out_dev, true);
+}
+
+extern "C" int32_t b200nn_decode_attention_f16(b200nn_ctx *ctx, const void *q_dev, const void *k_cache_dev,
+                                               const void *v_cache_dev, int32_t batch, int32_t n_heads, int32_t capacity,
+                                               int32_t ctx_len, void *out_dev) {
+    if (!ctx || !q_dev || !k_cache_dev || !v_cache_dev || !out_dev) return B200NN_ERR_ARG;
+    if (batch <= 0 || n_heads <= 0 || ctx_len <= 0 || ctx_len > capacity)
+        return set_error(ctx, B200NN_ERR_SHAPE, "decode_attention_f16: need batch, heads > 0 and 1 <= ctx_len <= capacity");
+    if (((uintptr_t)q_dev | (uintptr_t)k_cache_dev | (uintptr_t)v_cache_dev | (uintptr_t)out_dev) & 15)
+        return set_error(ctx, B200NN_ERR_ARG, "decode_attention_f16: buffers must be 16-byte aligned");
+    CK(ctx, cudaSetDevice(ctx->device));
+    return launch_decode_attention(ctx, q_dev, true, n_heads * 64, (const __half *)k_cache_dev, (const __half *)v_cache_dev,
+                                   batch, n_heads, capacity, nullptr, ctx_len - 1, out_dev, true, capacity);
+}

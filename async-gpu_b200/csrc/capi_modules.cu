@@ -109,8 +109,7 @@ extern "C" int32_t b200nn_int4_linear_forward_host(b200nn_int4_linear *l, const 
     CK(ctx, cudaMemcpyAsync(xd->p, x_host, m * (size_t)l->l.K * 4, cudaMemcpyHostToDevice, ctx->stream));
     TRY(b200nn_int4_linear_forward_dev(l, (const float *)xd->p, m, (float *)yd->p));
     CK(ctx, cudaMemcpyAsync(y_host, yd->p, m * (size_t)l->l.N * 4, cudaMemcpyDeviceToHost, ctx->stream));
-    CK(ctx, cudaStreamSynchronize(ctx->stream));
-    return B200NN_OK;
+    return stream_sync_check(ctx);
 }
 
 extern "C" size_t b200nn_int4_linear_memory_bytes(const b200nn_int4_linear *l) {
@@ -281,7 +280,7 @@ static int attention_run(b200nn_attention *a, const b200nn_tensor *x, const floa
             if (ce != cudaSuccess) rc = set_cuda_error(ctx, ce, "attention new K/V copy");
         }
     }
-    if (rc == B200NN_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = B200NN_ERR_CUDA;
+    if (rc == B200NN_OK) rc = stream_sync_check(ctx); // new K/V rows went to the host: report a device-side abort
     if (rc != B200NN_OK) { delete o; return rc; }
     *y = o;
     return B200NN_OK;

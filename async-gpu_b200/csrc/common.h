@@ -40,6 +40,7 @@ struct b200nn_ctx {
     int gemv_max_rows = 2;       // rows at or below this take the CUDA-core GEMV
     uint64_t launches = 0;       // kernels launched by this library
     uint32_t *dev_err = nullptr; // device error word (bounded waits report here)
+    uint32_t *host_err = nullptr; // pinned landing place of that word for stream_sync_check
     // split-K / split-KV scratch, grown on demand outside stream capture
     float *scratch = nullptr;
     size_t scratch_bytes = 0;
@@ -52,7 +53,6 @@ struct b200nn_ctx {
     int tc_min_kb = 3;            // fewest 64-wide K blocks a K split may get (3 measured best at 16..128 rows:
                                   // 1.69 against 1.76 ms per GPT-2 XL step at 32 rows with 4; no difference at 256)
     long long *trace = nullptr;  // optional device buffer for in-kernel time stamps (measurement aid)
-    uint32_t fam_mask = 0xffffffffu; // kernel families run_blocks / run_head launch (timing aid)
     int attn_tc = 1;              // prefill attention with fp16 q and output runs on the tensor cores
     int attn_stream = 1;          // decode attention over many (sequence, head) pairs uses the TMA-fed kernel
     int attn_stream_min10 = 20;   // ... when there are at least this many tenths of a pair per warp of its grid
@@ -68,11 +68,21 @@ struct b200nn_ctx {
     int int4_via_f16 = 1;         // int4 Linears with that many tiles dequantise the weight to fp16 once and use that GEMM
     std::shared_ptr<DevBuf> wh;   // the dequantised weight, [N,K] fp16, one Linear at a time
     bool capturing = false;      // true while a decode step is being captured into a graph
+    // one persistent kernel for all transformer blocks of an int4 decode step (decode_persistent.cu)
+    int persist = 0;              // 1: decode steps of persist_min_rows..persist_max_rows rows take it (opt-in: measured
+                                  // slower than one kernel per operation on GPT-2 XL at every batch size, see decode_persistent.cu)
+    int persist_min_rows = 3, persist_max_rows = 256; // decode batches (rows) that take it
+    int persist_prefetch_mb = 48; // KV-cache megabytes per layer it asks into L2 ahead of the attention phase
+    long long persist_wait_cycles = 0; // bound of its grid-wide waits in SM clocks (0: about a second)
+    void *persist_trace = nullptr; // optional stamp buffer [148][32][2] u64 (measurement aid, "persist_trace")
+    int persist_fault_phase = -1; // test hook: block 0 leaves out its arrival after this phase, so the bounded
+                                  // waits of every other block run out (-1: never)
 };
 
 int set_error(b200nn_ctx *ctx, int code, const std::string &msg);
 int set_cuda_error(b200nn_ctx *ctx, cudaError_t e, const char *what);
 int ensure_scratch(b200nn_ctx *ctx, size_t bytes, size_t counters);
+int stream_sync_check(b200nn_ctx *ctx); // stream synchronise + device error word -> B200NN_ERR_DEVICE
 
 #define CK(ctx, call)                                                     \
     do {                                                                  \
@@ -97,10 +107,12 @@ inline void prefer_max_smem(Kernel kern) {
 }
 #define PREFER_SMEM_ONCE(kern)                    \
     do {                                          \
-        static bool _done = false;                \
-        if (!_done) {                             \
+        static bool _done[16] = {};               \
+        int _dev = 0;                             \
+        cudaGetDevice(&_dev);                     \
+        if (!_done[_dev & 15]) {                  \
             prefer_max_smem(kern);                \
-            _done = true;                         \
+            _done[_dev & 15] = true;              \
         }                                         \
     } while (0)
 

@@ -220,7 +220,7 @@ int sample_row(b200nn_gpt2 *m, Workspace &ws, size_t k, float temp, uint64_t *rn
     std::vector<uint32_t> idx(kk);
     CK(ctx, cudaMemcpyAsync(vals.data(), vals_d, kk * 4, cudaMemcpyDeviceToHost, ctx->stream));
     CK(ctx, cudaMemcpyAsync(idx.data(), idx_d, kk * 4, cudaMemcpyDeviceToHost, ctx->stream));
-    CK(ctx, cudaStreamSynchronize(ctx->stream));
+    TRY(stream_sync_check(ctx));
     *token = sample_from_candidates(vals.data(), idx.data(), kk, rng);
     return B200NN_OK;
 }
@@ -231,7 +231,7 @@ int max_prob_of_row(b200nn_gpt2 *m, const float *row, float *conf_host) {
     max_prob_kernel<<<1, 1024, 0, ctx->stream>>>(row, m->cfg.vocab_size, ctx->scratch);
     CK_LAUNCH(ctx, "max_prob_kernel");
     CK(ctx, cudaMemcpyAsync(conf_host, ctx->scratch, 4, cudaMemcpyDeviceToHost, ctx->stream));
-    CK(ctx, cudaStreamSynchronize(ctx->stream));
+    TRY(stream_sync_check(ctx));
     return B200NN_OK;
 }
 
@@ -240,7 +240,7 @@ int argmax_row(b200nn_gpt2 *m, Workspace &ws, uint32_t *token) {
     // the reference's argmax keeps the last of equal maxima (gpt2.rs:991-997)
     TRY(launch_argmax(ctx, (const float *)ws.logits->p, 1, m->cfg.vocab_size, m->cfg.vocab_size, true, (uint32_t *)ws.tok->p));
     CK(ctx, cudaMemcpyAsync(token, ws.tok->p, 4, cudaMemcpyDeviceToHost, ctx->stream));
-    CK(ctx, cudaStreamSynchronize(ctx->stream));
+    TRY(stream_sync_check(ctx));
     return B200NN_OK;
 }
 
@@ -497,6 +497,89 @@ extern "C" int32_t b200nn_gpt2_forward_profiled(b200nn_gpt2 *m, const uint32_t *
         delete t;
         return rc;
     }
+    *logits = t;
+    return B200NN_OK;
+}
+
+// Gpt2Model::forward_diagnostic (gpt2.rs:595-667): forward of one sequence that also reports the values
+// the reference prints to stderr: the first four hidden values after the embedding (position 0 and the
+// last position), after block 0 and after the last block (last position, with the count of non-finite
+// values of the whole hidden state), after the final LayerNorm, and the five best tokens of the last
+// position.  The reference hard-codes "block 11"; here it is the model's last block.
+extern "C" int32_t b200nn_gpt2_forward_diagnostic(b200nn_gpt2 *m, const uint32_t *ids_host, size_t seq_len,
+                                                  b200nn_tensor **logits, b200nn_gpt2_diagnostic *diag) {
+    if (!m || !ids_host || !logits || !diag) return B200NN_ERR_ARG;
+    b200nn_ctx *ctx = m->ctx;
+    const int L = m->cfg.n_layer, S = (int)seq_len, V = m->cfg.vocab_size, d = m->cfg.n_embd;
+    if (seq_len == 0 || seq_len > (size_t)m->cfg.n_positions)
+        return set_error(ctx, B200NN_ERR_DIM, "forward_diagnostic: seq_len must be in [1, n_positions]");
+    CK(ctx, cudaSetDevice(ctx->device));
+    memset(diag, 0, sizeof(*diag));
+    CacheGuard g;
+    TRY(b200nn_kvcache_create(m, 1, seq_len, &g.c));
+    Workspace ws;
+    TRY(workspace_alloc(m, seq_len, seq_len, &ws));
+    const bool ah = model_act_half(m, S);
+    std::vector<float> h((size_t)S * d);
+    auto fetch = [&](const void *src) -> int {
+        CK(ctx, cudaMemcpyAsync(h.data(), src, h.size() * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        return stream_sync_check(ctx);
+    };
+    auto count_bad = [&]() {
+        int32_t n = 0;
+        for (float v : h) n += !std::isfinite(v);
+        return n;
+    };
+    const size_t last = (size_t)(S - 1) * d;
+    TRY(embed_one(m, ws, ids_host, S, 0));
+    TRY(fetch(ws.x->p));
+    for (int i = 0; i < 4 && i < d; ++i) {
+        diag->embedding_first[i] = h[i];
+        diag->embedding_last[i] = h[last + i];
+    }
+    for (int l = 0; l < L; ++l) {
+        TRY(run_blocks_range(m, ws, *g.c, 1, S, nullptr, 0, ah, nullptr, l, l + 1));
+        if (l == 0 || l == L - 1) {
+            TRY(fetch(ws.x->p));
+            float *dst = l == 0 ? diag->block0_last : diag->final_block_last;
+            for (int i = 0; i < 4 && i < d; ++i) dst[i] = h[last + i];
+            (l == 0 ? diag->block0_nonfinite : diag->final_block_nonfinite) = count_bad();
+            if (L == 1) {
+                memcpy(diag->final_block_last, diag->block0_last, sizeof(diag->block0_last));
+                diag->final_block_nonfinite = diag->block0_nonfinite;
+            }
+        }
+    }
+    // final LayerNorm in f32 for the report, then the regular head
+    std::shared_ptr<DevBuf> lnf;
+    TRY(dev_alloc(ctx, h.size() * 4, &lnf));
+    TRY(launch_layernorm(ctx, (const float *)ws.x->p, nullptr, nullptr, (const float *)m->lnf_g->p, (const float *)m->lnf_b->p,
+                         m->cfg.layer_norm_epsilon, S, d, lnf->p, false));
+    TRY(fetch(lnf->p));
+    for (int i = 0; i < 4 && i < d; ++i) diag->ln_f_last[i] = h[last + i];
+    TRY(run_head(m, ws, (const float *)ws.x->p, S, ah, nullptr));
+    b200nn_tensor *t = nullptr;
+    TRY(tensor_alloc(ctx, {seq_len, (size_t)V}, false, &t));
+    std::vector<float> row((size_t)V);
+    cudaError_t e = cudaMemcpyAsync(t->buf->p, ws.logits->p, t->numel * 4, cudaMemcpyDeviceToDevice, ctx->stream);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(row.data(), (const float *)ws.logits->p + (size_t)(S - 1) * V, (size_t)V * 4, cudaMemcpyDeviceToHost,
+                            ctx->stream);
+    int rc = e == cudaSuccess ? stream_sync_check(ctx) : set_cuda_error(ctx, e, "forward_diagnostic copy");
+    if (rc != B200NN_OK) {
+        delete t;
+        return rc;
+    }
+    // stable descending order, as the reference's sort_by on (index, value) pairs
+    std::vector<int> idx((size_t)V);
+    for (int i = 0; i < V; ++i) idx[i] = i;
+    const int k = std::min(5, V);
+    std::stable_sort(idx.begin(), idx.end(), [&](int a, int b) { return row[a] > row[b]; });
+    for (int i = 0; i < k; ++i) {
+        diag->top_tokens[i] = (uint32_t)idx[i];
+        diag->top_scores[i] = row[idx[i]];
+    }
+    diag->n_top = k;
     *logits = t;
     return B200NN_OK;
 }

@@ -183,11 +183,11 @@ static int gemv_chunk(b200nn_ctx *ctx, const Int4Weight &w, const XT *x, int m_v
     splits = (w.k_blocks + per - 1) / per;
     const size_t smem = ((size_t)MT * per * 64 + (size_t)(GEMV_SLICES + 1) * MT * 128) * sizeof(float);
     auto kern = int4_gemv_kernel<MT, XT>;
-    static bool attr_done = false;
-    if (!attr_done) {
+    static bool attr_done[16] = {}; // function attributes are per device
+    if (!attr_done[ctx->device & 15]) {
         CK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         prefer_max_smem(kern);
-        attr_done = true;
+        attr_done[ctx->device & 15] = true;
     }
     if (smem > 200 * 1024) return set_error(ctx, B200NN_ERR_UNSUPPORTED, "int4 GEMV: K too large for one cluster");
     cudaLaunchConfig_t cfg = {};

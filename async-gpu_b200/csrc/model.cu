@@ -183,6 +183,67 @@ static inline void prof_mark(b200nn_ctx *ctx, StepProfile *p, int fam) {
     p->fam.push_back(fam);
 }
 
+// The seven launches of one transformer block, each on its own so that the forward pass (all of them,
+// in order) and the per-family timing routine (one family at a time) issue exactly the same launches.
+int BlockLaunch::ln1() const {
+    const BlockW &b = m->blocks[l];
+    return launch_layernorm(m->ctx, (const float *)ws.x->p, nullptr, nullptr, (const float *)b.ln1_g->p, (const float *)b.ln1_b->p,
+                            m->cfg.layer_norm_epsilon, B * S, m->cfg.n_embd, ws.ln->p, act_half);
+}
+int BlockLaunch::qkv() const {
+    const int d = m->cfg.n_embd;
+    Epilogue e;
+    e.mode = EPI_QKV;
+    e.out = ws.q->p;
+    e.ldo = d;
+    e.out_half = act_half;
+    e.kc = kv.kl(l);
+    e.vc = kv.vl(l);
+    e.d_model = d;
+    e.n_head = m->cfg.n_head;
+    e.rows_per_seq = S;
+    e.cap = (int)kv.cap;
+    e.pos_ptr = pos_ptr;
+    e.pos_off = pos_off;
+    return linear_forward(m->ctx, m->blocks[l].qkv, ws.ln->p, act_half, B * S, e);
+}
+int BlockLaunch::attention() const {
+    const int d = m->cfg.n_embd, H = m->cfg.n_head;
+    if (S == 1)
+        return launch_decode_attention(m->ctx, ws.q->p, act_half, d, kv.kl(l), kv.vl(l), B, H, (int)kv.cap, pos_ptr, pos_off,
+                                       ws.att->p, act_half, (int)kv.cap);
+    return launch_prefill_attention(m->ctx, ws.q->p, act_half, d, kv.kl(l), kv.vl(l), B, H, (int)kv.cap, S, pos_off, ws.att->p,
+                                    act_half);
+}
+int BlockLaunch::proj() const {
+    Epilogue r;
+    r.mode = EPI_RESID;
+    r.resid = (float *)ws.x->p;
+    r.ldo = m->cfg.n_embd;
+    return linear_forward(m->ctx, m->blocks[l].proj, ws.att->p, act_half, B * S, r);
+}
+int BlockLaunch::ln2() const {
+    const BlockW &b = m->blocks[l];
+    return launch_layernorm(m->ctx, (const float *)ws.x->p, nullptr, nullptr, (const float *)b.ln2_g->p, (const float *)b.ln2_b->p,
+                            m->cfg.layer_norm_epsilon, B * S, m->cfg.n_embd, ws.ln->p, act_half);
+}
+int BlockLaunch::fc() const {
+    Epilogue f;
+    f.mode = EPI_STORE;
+    f.act = m->act();
+    f.out = ws.fc->p;
+    f.ldo = 4 * m->cfg.n_embd;
+    f.out_half = act_half;
+    return linear_forward(m->ctx, m->blocks[l].fc, ws.ln->p, act_half, B * S, f);
+}
+int BlockLaunch::fcproj() const {
+    Epilogue r;
+    r.mode = EPI_RESID;
+    r.resid = (float *)ws.x->p;
+    r.ldo = m->cfg.n_embd;
+    return linear_forward(m->ctx, m->blocks[l].fcproj, ws.fc->p, act_half, B * S, r);
+}
+
 int run_blocks(b200nn_gpt2 *m, Workspace &ws, b200nn_kvcache &kv, int B, int S, const int *pos_ptr, int pos_off,
                bool act_half, StepProfile *prof) {
     return run_blocks_range(m, ws, kv, B, S, pos_ptr, pos_off, act_half, prof, 0, m->cfg.n_layer);
@@ -191,72 +252,48 @@ int run_blocks(b200nn_gpt2 *m, Workspace &ws, b200nn_kvcache &kv, int B, int S, 
 int run_blocks_range(b200nn_gpt2 *m, Workspace &ws, b200nn_kvcache &kv, int B, int S, const int *pos_ptr, int pos_off,
                      bool act_half, StepProfile *prof, int layer_begin, int layer_end) {
     b200nn_ctx *ctx = m->ctx;
-    const int d = m->cfg.n_embd, H = m->cfg.n_head, T = B * S;
-    float *x = (float *)ws.x->p;
     for (int l = layer_begin; l < layer_end; ++l) {
-        const BlockW &b = m->blocks[l];
-        if (ctx->fam_mask & (1u << B200NN_PROF_LAYERNORM)) TRY(launch_layernorm(ctx, x, nullptr, nullptr, (const float *)b.ln1_g->p, (const float *)b.ln1_b->p,
-                             m->cfg.layer_norm_epsilon, T, d, ws.ln->p, act_half));
+        const BlockLaunch bl{m, ws, kv, l, B, S, pos_ptr, pos_off, act_half};
+        TRY(bl.ln1());
         prof_mark(ctx, prof, B200NN_PROF_LAYERNORM);
-        Epilogue e;
-        e.mode = EPI_QKV;
-        e.out = ws.q->p;
-        e.ldo = d;
-        e.out_half = act_half;
-        e.kc = kv.kl(l);
-        e.vc = kv.vl(l);
-        e.d_model = d;
-        e.n_head = H;
-        e.rows_per_seq = S;
-        e.cap = (int)kv.cap;
-        e.pos_ptr = pos_ptr;
-        e.pos_off = pos_off;
-        if (ctx->fam_mask & (1u << B200NN_PROF_LINEAR)) TRY(linear_forward(ctx, b.qkv, ws.ln->p, act_half, T, e));
+        TRY(bl.qkv());
         prof_mark(ctx, prof, B200NN_PROF_LINEAR);
-        if (!(ctx->fam_mask & (1u << B200NN_PROF_ATTENTION))) {
-        } else if (S == 1)
-            TRY(launch_decode_attention(ctx, ws.q->p, act_half, d, kv.kl(l), kv.vl(l), B, H, (int)kv.cap, pos_ptr,
-                                        pos_off, ws.att->p, act_half, (int)kv.cap));
-        else
-            TRY(launch_prefill_attention(ctx, ws.q->p, act_half, d, kv.kl(l), kv.vl(l), B, H, (int)kv.cap, S, pos_off,
-                                         ws.att->p, act_half));
+        TRY(bl.attention());
         prof_mark(ctx, prof, B200NN_PROF_ATTENTION);
-        Epilogue r;
-        r.mode = EPI_RESID;
-        r.resid = x;
-        r.ldo = d;
-        if (ctx->fam_mask & (1u << B200NN_PROF_LINEAR)) TRY(linear_forward(ctx, b.proj, ws.att->p, act_half, T, r));
+        TRY(bl.proj());
         prof_mark(ctx, prof, B200NN_PROF_LINEAR);
-        if (ctx->fam_mask & (1u << B200NN_PROF_LAYERNORM)) TRY(launch_layernorm(ctx, x, nullptr, nullptr, (const float *)b.ln2_g->p, (const float *)b.ln2_b->p,
-                             m->cfg.layer_norm_epsilon, T, d, ws.ln->p, act_half));
+        TRY(bl.ln2());
         prof_mark(ctx, prof, B200NN_PROF_LAYERNORM);
-        Epilogue f;
-        f.mode = EPI_STORE;
-        f.act = m->act();
-        f.out = ws.fc->p;
-        f.ldo = 4 * d;
-        f.out_half = act_half;
-        if (ctx->fam_mask & (1u << B200NN_PROF_LINEAR)) TRY(linear_forward(ctx, b.fc, ws.ln->p, act_half, T, f));
+        TRY(bl.fc());
         prof_mark(ctx, prof, B200NN_PROF_LINEAR);
-        if (ctx->fam_mask & (1u << B200NN_PROF_LINEAR)) TRY(linear_forward(ctx, b.fcproj, ws.fc->p, act_half, T, r));
+        TRY(bl.fcproj());
         prof_mark(ctx, prof, B200NN_PROF_LINEAR);
     }
     return B200NN_OK;
 }
 
-int run_head(b200nn_gpt2 *m, Workspace &ws, const float *x, int rows, bool act_half, StepProfile *prof) {
-    b200nn_ctx *ctx = m->ctx;
-    const int d = m->cfg.n_embd, V = m->cfg.vocab_size;
-    bool head_half = act_half && (m->lm_head.int4 ? int4_gemm_tc_supported(m->lm_head.q, rows)
-                                                   : f16_gemm_tc_supported(ctx, m->lm_head.f, rows));
-    if (ctx->fam_mask & (1u << B200NN_PROF_LAYERNORM)) TRY(launch_layernorm(ctx, x, nullptr, nullptr, (const float *)m->lnf_g->p, (const float *)m->lnf_b->p,
-                         m->cfg.layer_norm_epsilon, rows, d, ws.last_ln->p, head_half));
-    prof_mark(ctx, prof, B200NN_PROF_LAYERNORM);
+bool head_act_half(const b200nn_gpt2 *m, int rows, bool act_half) {
+    return act_half && (m->lm_head.int4 ? int4_gemm_tc_supported(m->lm_head.q, rows)
+                                        : f16_gemm_tc_supported(m->ctx, m->lm_head.f, rows));
+}
+int launch_head_norm(b200nn_gpt2 *m, Workspace &ws, const float *x, int rows, bool head_half) {
+    return launch_layernorm(m->ctx, x, nullptr, nullptr, (const float *)m->lnf_g->p, (const float *)m->lnf_b->p,
+                            m->cfg.layer_norm_epsilon, rows, m->cfg.n_embd, ws.last_ln->p, head_half);
+}
+int launch_head_linear(b200nn_gpt2 *m, Workspace &ws, int rows, bool head_half) {
     Epilogue e;
     e.mode = EPI_STORE;
     e.out = ws.logits->p;
-    e.ldo = V;
-    if (ctx->fam_mask & (1u << B200NN_PROF_LM_HEAD)) TRY(linear_forward(ctx, m->lm_head, ws.last_ln->p, head_half, rows, e));
+    e.ldo = m->cfg.vocab_size;
+    return linear_forward(m->ctx, m->lm_head, ws.last_ln->p, head_half, rows, e);
+}
+
+int run_head(b200nn_gpt2 *m, Workspace &ws, const float *x, int rows, bool act_half, StepProfile *prof) {
+    b200nn_ctx *ctx = m->ctx;
+    const bool head_half = head_act_half(m, rows, act_half);
+    TRY(launch_head_norm(m, ws, x, rows, head_half));
+    prof_mark(ctx, prof, B200NN_PROF_LAYERNORM);
+    TRY(launch_head_linear(m, ws, rows, head_half));
     prof_mark(ctx, prof, B200NN_PROF_LM_HEAD);
     return B200NN_OK;
 }

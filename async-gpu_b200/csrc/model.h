@@ -90,6 +90,20 @@ int run_blocks(b200nn_gpt2 *m, Workspace &ws, b200nn_kvcache &kv, int B, int S, 
 // The same for blocks [layer_begin, layer_end) only (data-dependent depth: early exit).
 int run_blocks_range(b200nn_gpt2 *m, Workspace &ws, b200nn_kvcache &kv, int B, int S, const int *pos_ptr, int pos_off,
                      bool act_half, StepProfile *prof, int layer_begin, int layer_end);
+// The launches of transformer block `l` over B*S rows (arguments as run_blocks), one at a time.
+struct BlockLaunch {
+    b200nn_gpt2 *m;
+    Workspace &ws;
+    b200nn_kvcache &kv;
+    int l, B, S;
+    const int *pos_ptr;
+    int pos_off;
+    bool act_half;
+    int ln1() const, qkv() const, attention() const, proj() const, ln2() const, fc() const, fcproj() const;
+};
+bool head_act_half(const b200nn_gpt2 *m, int rows, bool act_half);
+int launch_head_norm(b200nn_gpt2 *m, Workspace &ws, const float *x, int rows, bool head_half);
+int launch_head_linear(b200nn_gpt2 *m, Workspace &ws, int rows, bool head_half);
 // Final LayerNorm + LM head over `rows` rows of `x` -> ws.logits [rows, vocab].
 int run_head(b200nn_gpt2 *m, Workspace &ws, const float *x, int rows, bool act_half, StepProfile *prof);
 bool model_act_half(const b200nn_gpt2 *m, int rows);
@@ -106,6 +120,15 @@ struct b200nn_session {
     bool prefilled = false, eager_done = false;
     cudaGraphExec_t graph = nullptr;
     uint64_t launches_per_step = 0; // kernels in one captured decode step
+    // persistent decode (decode_persistent.cu): per-layer pointer table, f32 accumulators of the q/k/v and
+    // MLP hidden GEMMs (zero at rest), grid counter + per-phase nanoseconds
+    bool persist = false;
+    std::shared_ptr<DevBuf> pd_layers, pd_qkv_acc, pd_fc_acc, pd_sync;
     int *pos_ptr() const { return static_cast<int *>(counters->p); }
     int *step_ptr() const { return static_cast<int *>(counters->p) + 1; }
 };
+
+// All transformer blocks of an int4 decode step as one persistent cooperative kernel.
+bool decode_persistent_supported(const b200nn_gpt2 *m, int rows);
+int decode_persistent_prepare(b200nn_session *s);
+int launch_decode_layers(b200nn_session *s, bool profile);

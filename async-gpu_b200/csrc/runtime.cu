@@ -23,6 +23,23 @@ int set_cuda_error(b200nn_ctx *ctx, cudaError_t e, const char *what) {
     return B200NN_ERR_CUDA;
 }
 
+// Waits for the context's stream and brings the device error word back in the same step.  A kernel
+// whose bounded wait ran out leaves its output unwritten and a code in that word: the call that hands
+// results to the host then fails with B200NN_ERR_DEVICE instead of returning stale data.  The word is
+// cleared so that the context stays usable.
+int stream_sync_check(b200nn_ctx *ctx) {
+    if (!ctx->host_err) CK(ctx, cudaMallocHost((void **)&ctx->host_err, sizeof(uint32_t)));
+    *ctx->host_err = 0;
+    CK(ctx, cudaMemcpyAsync(ctx->host_err, ctx->dev_err, sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+    CK(ctx, cudaStreamSynchronize(ctx->stream));
+    const uint32_t w = *ctx->host_err;
+    if (!w) return B200NN_OK;
+    CK(ctx, cudaMemsetAsync(ctx->dev_err, 0, sizeof(uint32_t), ctx->stream));
+    char msg[96];
+    snprintf(msg, sizeof(msg), "a kernel's bounded wait ran out (device error word 0x%x); results were not written", w);
+    return set_error(ctx, B200NN_ERR_DEVICE, msg);
+}
+
 static void free_on_device(void *p, int device) {
     int cur = -1;
     cudaGetDevice(&cur);

@@ -196,14 +196,30 @@ extern "C" int32_t b200nn_safetensors_open(const char *path, b200nn_safetensors 
                 return st_fail(B200NN_ERR_IO, "malformed header (entry of " + en.name + ")");
             // the checks the format's own reader makes: known dtype, range inside the file, size = numel * width
             const size_t width = dtype_size(en.dtype);
-            size_t numel = 1;
-            for (size_t s : en.shape) numel *= s;
             if (!width) return st_fail(B200NN_ERR_IO, "unknown dtype " + en.dtype + " for " + en.name);
+            // element count and byte size with overflow checks: a shape like [2^32, 2^32] must not wrap to 0
+            size_t nbytes = width;
+            for (size_t s : en.shape)
+                if (__builtin_mul_overflow(nbytes, s, &nbytes))
+                    return st_fail(B200NN_ERR_IO, "shape of " + en.name + " overflows the addressable size");
             if (en.end < en.begin || en.end > data_len) return st_fail(B200NN_ERR_IO, "data_offsets of " + en.name + " outside the file");
-            if (en.end - en.begin != numel * width) return st_fail(B200NN_ERR_IO, "byte size of " + en.name + " does not match its shape");
+            if (en.end - en.begin != nbytes) return st_fail(B200NN_ERR_IO, "byte size of " + en.name + " does not match its shape");
             st->entries.push_back(std::move(en));
         } while (j.eat(','));
         if (!j.eat('}')) return st_fail(B200NN_ERR_IO, "malformed header (end of object)");
+    }
+    // as the format's own reader requires: in offset order the tensors follow one another without gap
+    // or overlap, starting at 0 and ending at the end of the data section
+    {
+        std::vector<std::pair<size_t, size_t>> spans;
+        for (const StEntry &en : st->entries) spans.emplace_back(en.begin, en.end);
+        std::sort(spans.begin(), spans.end());
+        size_t at = 0;
+        for (const auto &sp : spans) {
+            if (sp.first != at) return st_fail(B200NN_ERR_IO, "data_offsets overlap or leave a gap in the data section");
+            at = sp.second;
+        }
+        if (at != data_len) return st_fail(B200NN_ERR_IO, "data_offsets do not cover the data section");
     }
     std::sort(st->entries.begin(), st->entries.end(), [](const StEntry &a, const StEntry &b) { return a.name < b.name; });
     for (size_t i = 1; i < st->entries.size(); ++i)

@@ -133,6 +133,10 @@ extern "C" int32_t b200nn_session_create(b200nn_gpt2 *m, size_t batch, size_t ca
     CK(ctx, cudaMemsetAsync(s->counters->p, 0, 2 * sizeof(int), ctx->stream));
     TRY(dev_alloc(ctx, batch * s->hist_cap * 4, &s->history));
     CK(ctx, cudaMemsetAsync(s->history->p, 0, batch * s->hist_cap * 4, ctx->stream));
+    if (decode_persistent_supported(m, (int)batch)) {
+        TRY(decode_persistent_prepare(s.get()));
+        s->persist = true;
+    }
     *out = s.release();
     return B200NN_OK;
 }
@@ -220,7 +224,21 @@ static int decode_step(b200nn_session *s, StepProfile *prof) {
         prof->ev.push_back(e);
         prof->fam.push_back(B200NN_PROF_EMBED);
     }
-    TRY(run_blocks(m, ws, s->kv, B, 1, s->pos_ptr(), 0, ah, prof));
+    if (s->persist && ctx->persist) {
+        // every transformer block in one cooperative launch; with `prof` its phases are timed inside the
+        // kernel and the launch as a whole is booked under the attention family's event slot
+        if (prof) CK(ctx, cudaMemsetAsync((char *)s->pd_sync->p + 64, 0, 128, ctx->stream));
+        TRY(launch_decode_layers(s, prof != nullptr));
+        if (prof) {
+            cudaEvent_t e;
+            cudaEventCreate(&e);
+            cudaEventRecord(e, ctx->stream);
+            prof->ev.push_back(e);
+            prof->fam.push_back(-1); // split by the in-kernel phase times afterwards
+        }
+    } else {
+        TRY(run_blocks(m, ws, s->kv, B, 1, s->pos_ptr(), 0, ah, prof));
+    }
     TRY(run_head(m, ws, (const float *)ws.x->p, B, ah, prof));
     TRY(launch_argmax(ctx, (const float *)ws.logits->p, B, m->cfg.vocab_size, m->cfg.vocab_size,
                       (s->flags & B200NN_ARGMAX_LAST) != 0, (uint32_t *)ws.tok->p));
@@ -243,6 +261,16 @@ extern "C" int32_t b200nn_session_step(b200nn_session *s, size_t n_steps) {
     if (s->position + n_steps > s->cap) return set_error(ctx, B200NN_ERR_DIM, "session_step: capacity exceeded");
     CK(ctx, cudaSetDevice(ctx->device));
     size_t done = 0;
+    if (s->persist && ctx->persist) {
+        // a step is six launches (embedding, the persistent kernel, final norm, LM head, argmax, record):
+        // nothing to gain from a graph, and the cooperative launch stays an ordinary launch
+        for (; done < n_steps; ++done) TRY(decode_step(s, nullptr));
+        s->eager_done = true;
+        s->position += n_steps;
+        s->steps_done += n_steps;
+        s->kv.len = s->position;
+        return B200NN_OK;
+    }
     if (!s->eager_done && n_steps > 0) { // sizes the split scratch before anything is captured
         TRY(decode_step(s, nullptr));
         s->eager_done = true;
@@ -299,7 +327,7 @@ extern "C" int32_t b200nn_session_tokens(b200nn_session *s, uint32_t *out, size_
     size_t n = std::min(s->steps_done, capacity_per_seq);
     CK(ctx, cudaMemcpy2DAsync(out, capacity_per_seq * 4, s->history->p, s->hist_cap * 4, n * 4, s->batch,
                               cudaMemcpyDeviceToHost, ctx->stream));
-    CK(ctx, cudaStreamSynchronize(ctx->stream));
+    TRY(stream_sync_check(ctx));
     if (generated) *generated = n;
     return B200NN_OK;
 }
@@ -310,8 +338,7 @@ extern "C" int32_t b200nn_session_logits(b200nn_session *s, float *out) {
     CK(ctx, cudaSetDevice(ctx->device));
     CK(ctx, cudaMemcpyAsync(out, s->ws_step.logits->p, s->batch * (size_t)s->m->cfg.vocab_size * 4,
                             cudaMemcpyDeviceToHost, ctx->stream));
-    CK(ctx, cudaStreamSynchronize(ctx->stream));
-    return B200NN_OK;
+    return stream_sync_check(ctx);
 }
 
 extern "C" int32_t b200nn_session_profile_step(b200nn_session *s, float *times_ms, uint64_t *linear_bytes) {
@@ -332,7 +359,19 @@ extern "C" int32_t b200nn_session_profile_step(b200nn_session *s, float *times_m
     for (size_t i = 0; i < prof.ev.size(); ++i) {
         float ms = 0.0f;
         cudaEventElapsedTime(&ms, prev, prof.ev[i]);
-        times_ms[prof.fam[i]] += ms;
+        if (prof.fam[i] >= 0) times_ms[prof.fam[i]] += ms;
+        else {
+            // the persistent kernel: phase kinds LN1, QKV, ATT, PROJ, LN2, FC, ACT, FCPROJ as block 0 saw them
+            unsigned long long ns[8] = {};
+            cudaMemcpy(ns, (char *)s->pd_sync->p + 64, sizeof(ns), cudaMemcpyDeviceToHost);
+            double tot = 0;
+            for (int k = 0; k < 8; ++k) tot += (double)ns[k];
+            if (tot > 0) {
+                times_ms[B200NN_PROF_LAYERNORM] += ms * (float)((ns[0] + ns[4]) / tot);
+                times_ms[B200NN_PROF_ATTENTION] += ms * (float)(ns[2] / tot);
+                times_ms[B200NN_PROF_LINEAR] += ms * (float)((ns[1] + ns[3] + ns[5] + ns[6] + ns[7]) / tot);
+            } else times_ms[B200NN_PROF_LINEAR] += ms;
+        }
         prev = prof.ev[i];
     }
     cudaEventDestroy(e0);
@@ -376,17 +415,36 @@ extern "C" int32_t b200nn_session_time_family(b200nn_session *s, int32_t family,
     CK(ctx, cudaEventCreate(&e1));
     const uint64_t before = ctx->launches;
     uint64_t per_pass = 0;
-    ctx->fam_mask = 1u << family;
     int rc = B200NN_OK;
+    // the launches of one step that belong to the family, issued directly (the forward pass itself
+    // carries no measurement switches)
+    auto one_pass = [&]() -> int {
+        for (int l = 0; l < m->cfg.n_layer; ++l) {
+            const BlockLaunch bl{m, s->ws_step, s->kv, l, B, 1, s->pos_ptr(), 0, ah};
+            if (family == B200NN_PROF_LAYERNORM) {
+                TRY(bl.ln1());
+                TRY(bl.ln2());
+            } else if (family == B200NN_PROF_LINEAR) {
+                TRY(bl.qkv());
+                TRY(bl.proj());
+                TRY(bl.fc());
+                TRY(bl.fcproj());
+            } else if (family == B200NN_PROF_ATTENTION) {
+                TRY(bl.attention());
+            }
+        }
+        const bool hh = head_act_half(m, B, ah);
+        if (family == B200NN_PROF_LAYERNORM) TRY(launch_head_norm(m, s->ws_step, (const float *)s->ws_step.x->p, B, hh));
+        if (family == B200NN_PROF_LM_HEAD) TRY(launch_head_linear(m, s->ws_step, B, hh));
+        return B200NN_OK;
+    };
     // one untimed pass sizes scratch and warms the instruction cache
     for (int r = -1; r < reps && rc == B200NN_OK; ++r) {
         if (r == 0) cudaEventRecord(e0, ctx->stream);
-        rc = run_blocks(m, s->ws_step, s->kv, B, 1, s->pos_ptr(), 0, ah, nullptr);
-        if (rc == B200NN_OK) rc = run_head(m, s->ws_step, (const float *)s->ws_step.x->p, B, ah, nullptr);
+        rc = one_pass();
         if (r == -1) per_pass = ctx->launches - before;
     }
     cudaEventRecord(e1, ctx->stream);
-    ctx->fam_mask = 0xffffffffu;
     cudaError_t ce = cudaStreamSynchronize(ctx->stream);
     float ms = 0.0f;
     cudaEventElapsedTime(&ms, e0, e1);

@@ -11,10 +11,15 @@ every sequence of the batch (all layers, LM head, argmax, token fed back on the 
 128 + (step mod 128).  Weights and token ids are seeded synthetic data.
 
 One JSON line is printed by rank 0: `value` = sequences x steps / max-over-ranks CUDA-event time with
-all state resident in HBM; `e2e` = the same metric through generate_batch (host prompt ids in, host
-tokens out, prefill included); `roofline` = the dominant kernel family of a step timed alone
-(algorithmic bytes / time against the measured HBM peak); `prefill` = this rank's prompts through all
-layers; `gemv` = one-row dequant-GEMV bandwidth; `cpu_baseline` = the oracle on the host cores.
+all state resident in HBM (the K timed steps sit in the middle of the decode window, so their mean
+context is the window's mean whatever K is; the timed region is repeated and the median reported);
+`e2e` = the same metric through generate_batch (host prompt ids in, host tokens out, prefill included,
+every rank's tokens gathered on rank 0 inside the timed region); `roofline` = the dominant kernel
+family of a step timed alone (algorithmic bytes / time against the measured HBM peak); `prefill` =
+this rank's prompts through all layers; `gemv` = one-row dequant-GEMV bandwidth; at N=1 also
+`int4_linear` (the isolated int4 Linear at 1 / 8 / 64 rows on GPT-2 Small's four shapes, L2-cold and
+L2-warm), `attention` (isolated causal attention, batch 8 x 12 heads x 256 / 512 / 1024, and decode
+attention of 64 sequences over 1024 cached positions) and `cpu_baseline` = the oracle on the host cores.
 """
 from __future__ import annotations
 
@@ -48,6 +53,17 @@ def shard_bounds(total: int, world: int, rank: int):
     base, extra = divmod(total, world)
     lo = rank * base + min(rank, extra)
     return lo, lo + base + (1 if rank < extra else 0)
+
+
+def traffic_ratio(kernel: str):
+    """DRAM bytes / algorithmic bytes of a kernel's profiler capture, from profiles/dram_traffic.json
+    (written by hand from the capture summarised beside it)."""
+    p = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        e = json.load(open(p))[kernel]
+        return float(e["dram_bytes"]) / float(e["algorithmic_bytes"]), e.get("source")
+    except Exception:
+        return None, None
 
 
 def peaks():
@@ -197,6 +213,133 @@ def gemv_bandwidth(reg, cfg, hbm_peak, iters=96):
     return out
 
 
+def _graph_time(reg, stream, launch, iters):
+    """Microseconds per call of `launch(i)`, i = 0..iters-1, captured into one CUDA graph and replayed
+    (the host's launch rate is not what is being measured); one untimed replay first."""
+    import torch
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
+        for i in range(iters):
+            launch(i)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        g.replay()
+        e0.record(stream)
+        g.replay()
+        e1.record(stream)
+    torch.cuda.synchronize()
+    del g
+    return e0.elapsed_time(e1) / iters * 1e3
+
+
+def int4_linear_isolated(reg, hbm_peak, tf_peak, iters=64):
+    """The isolated int4 Linear of GPT-2 Small (K, N) in {(768,3072), (3072,768), (768,2304), (768,50257)}
+    at M in {1, 8, 64} rows through Int4Linear.forward on device buffers (f32 in, f32 out: the reference's
+    interface, int4_linear.rs:60-130).  Nibbles uniform in [-8,7], group 128, fp16-representable scales,
+    activations N(0,1).  `cold`: every launch reads another copy of the weight (copies add up to > 256 MB,
+    twice the L2); `warm`: the same weight every launch.  Bytes are algorithmic: nibbles + fp16 scales +
+    f32 input rows + f32 output rows; flops 2*M*K*N."""
+    import torch
+    import b200nn
+    from b200nn import synth
+    stream = torch.cuda.ExternalStream(reg.stream)
+    out = {}
+    for (k, n) in ((768, 3072), (3072, 768), (768, 2304), (768, 50257)):
+        packed, scales, _, _ = synth.int4_linear_case(21, 1, k, n, 128)
+        copies = max(2, int(256e6 // (k * n / 2)) + 1)
+        lins = [b200nn.Int4Linear(packed, scales, None, k, n, 128, reg) for _ in range(copies)]
+        for m in (1, 8, 64):
+            x = torch.randn(m, k, device="cuda")
+            y = torch.empty(m, n, device="cuda")
+            for l in lins[:2]:
+                l.forward_dev(x.data_ptr(), m, y.data_ptr())
+            reg.synchronize()
+            nbytes = k * n // 2 + ((k + 127) // 128) * n * 2 + m * k * 4 + m * n * 4
+            rec = {"bytes": nbytes}
+            for mode in ("cold", "warm"):
+                us = _graph_time(reg, stream, lambda i: lins[i % copies if mode == "cold" else 0].forward_dev(
+                    x.data_ptr(), m, y.data_ptr()), iters)
+                rec[mode] = {"us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1),
+                             "frac_of_hbm_peak": round(nbytes / us / 1e3 / hbm_peak, 4),
+                             "tflops": round(2 * m * k * n / us / 1e6, 2)}
+            out[f"M{m}_K{k}_N{n}"] = rec
+        del lins
+    return out
+
+
+def attention_isolated(reg, hbm_peak, tf_peak):
+    """Isolated attention on fp16 device buffers in the library's cache layout.  Prefill: causal, batch 8,
+    12 heads, head_dim 64, seq 256 / 512 / 1024, Q/K/V N(0,1); flops 4 * 0.5 * B * H * n^2 * 64 (the
+    convention of tests_transformer.rs:2219-2224 times the batch); both a single launch between events
+    and the graph-replayed rate are given (these are microseconds of tensor work).  Decode: one query
+    per sequence, 64 sequences x 12 heads against 1024 cached positions; bytes B*H*1024*64*2*2 + q + out,
+    rotating over copies of the cache that add up to more than the L2."""
+    import torch
+    from b200nn import ops
+    stream = torch.cuda.ExternalStream(reg.stream)
+    out = {"prefill": {}, "decode": {}}
+    B, H = 8, 12
+    for n in (256, 512, 1024):
+        q = torch.randn(B * n, H * 64, device="cuda", dtype=torch.float16)
+        kc = torch.randn(B, H, n, 64, device="cuda", dtype=torch.float16)
+        vc = torch.randn(B, H, n, 64, device="cuda", dtype=torch.float16)
+        o = torch.empty_like(q)
+        call = lambda i: ops.prefill_attention_f16(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, H, n, n, 0, o.data_ptr(), reg)
+        call(0)
+        reg.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            call(0)
+            e1.record(stream)
+        torch.cuda.synchronize()
+        single_us = e0.elapsed_time(e1) * 1e3
+        us = _graph_time(reg, stream, call, 32)
+        flops = 4 * 0.5 * B * H * n * n * 64
+        out["prefill"][f"seq{n}"] = {"us_graph": round(us, 2), "us_single_launch": round(single_us, 2),
+                                     "tflops": round(flops / us / 1e6, 2),
+                                     "frac_of_bf16_peak": round(flops / us / 1e6 / tf_peak, 4)}
+    B, ctx = 64, 1024
+    copies = 3  # 3 x 201 MB of K and V: more than the 126 MB L2 between two uses of a copy
+    q = torch.randn(B, H * 64, device="cuda", dtype=torch.float16)
+    kcs = [torch.randn(B, H, ctx, 64, device="cuda", dtype=torch.float16) for _ in range(copies)]
+    vcs = [torch.randn(B, H, ctx, 64, device="cuda", dtype=torch.float16) for _ in range(copies)]
+    o = torch.empty_like(q)
+    call = lambda i: ops.decode_attention_f16(q.data_ptr(), kcs[i % copies].data_ptr(), vcs[i % copies].data_ptr(), B, H,
+                                              ctx, ctx, o.data_ptr(), reg)
+    call(0)
+    reg.synchronize()
+    us = _graph_time(reg, stream, call, 30)
+    nbytes = B * H * ctx * 64 * 2 * 2 + 2 * B * H * 64 * 2
+    out["decode"]["b64_kv1024"] = {"us": round(us, 2), "bytes": nbytes, "GBps": round(nbytes / us / 1e3, 1),
+                                   "frac_of_hbm_peak": round(nbytes / us / 1e3 / hbm_peak, 4)}
+    return out
+
+
+def cpu_reference_form(steps=1):
+    """BASELINE config 1 the way the reference's CPU test runs it (tests_inference.rs:4393-4540): GPT-2
+    Small, f32 weights, f64 accumulation, greedy decode WITHOUT a KV cache (every step recomputes the
+    whole sequence), one thread.  Bounded sample: the 64-token prompt and `steps` generated tokens."""
+    from oracle import oracle
+    from b200nn import synth
+    from b200nn.gpt2 import Gpt2Config
+    cfg = Gpt2Config.small()
+    w = synth.gpt2_weights(cfg)
+    prompt = synth.token_ids(synth.BASE_SEED + 7, (1, 64), cfg.vocab_size)[0]
+    om = oracle.Model(cfg.as_dict(), w)
+    threads = oracle.num_threads()
+    oracle.lib().orc_set_num_threads(1)
+    try:
+        t0 = time.perf_counter()
+        om.generate(prompt, steps)
+        sec = time.perf_counter() - t0
+    finally:
+        oracle.lib().orc_set_num_threads(threads)
+    return {"value": steps / sec, "unit": UNIT, "cores": 1, "kind": "port",
+            "sample": f"GPT-2 Small f32, prompt 64, {steps} greedy token(s) without KV cache, f64, single thread "
+                      f"({sec:.1f} s)"}
+
+
 def run_b200(args):
     import torch
     import torch.distributed as dist
@@ -257,27 +400,41 @@ def run_b200(args):
             done += k
 
     run_steps(max(args.warmup, 3))
+    # fill the rest of the decode window once, so that every context of it has its cached rows and the
+    # timed region can start anywhere inside it
+    if sess.position() < prompt_len + window:
+        sess.step(prompt_len + window - sess.position())
     reg.synchronize()
-    sess.rewind(prompt_len)
     launches0 = reg.launch_count()
+    # The K timed steps sit in the middle of the decode window [prompt_len, prompt_len + window): their
+    # mean context is the window's mean whatever K is (K > window wraps around the whole window).  The
+    # timed region runs `reps` times from the same start (the cache keeps its rows); the median counts.
+    first_ctx = prompt_len + max(0, (window - args.steps) // 2)
+    reps = max(1, args.reps)
     sampler = ClockSampler(local)
-    barrier()
-    torch.cuda.synchronize()
     sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(stream):
-        e0.record(stream)
-        run_steps(args.steps)
-        e1.record(stream)
-    torch.cuda.synchronize()
-    barrier()
+    rep_ms = []
+    for _ in range(reps):
+        sess.rewind(first_ctx)
+        barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            run_steps(args.steps)
+            e1.record(stream)
+        torch.cuda.synchronize()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        rep_ms.append(float(t.item()))
     clocks = sampler.finish()
-    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms = float(ms.item())
-    launches = reg.launch_count() - launches0
+    ms = sorted(rep_ms)[len(rep_ms) // 2]
+    launches = (reg.launch_count() - launches0) // reps
     value = total * args.steps / (ms / 1e3)
+    last_ctx = first_ctx + args.steps - 1
+    contexts = [first_ctx, last_ctx] if args.steps <= window else [prompt_len, prompt_len + window - 1]
 
     # per-kernel-family device time of single decode steps at mid-window context (CUDA events
     # around every launch on the library's stream), for the roofline of the dominant kernel
@@ -312,8 +469,9 @@ def run_b200(args):
     # DRAM bytes per launch: the ratio dram bytes / algorithmic bytes of the kernel's ncu capture on a
     # smaller case of the same workload (2 layers, context 130: 218.1 MB moved for 213.0 MB), applied
     # to this launch's algorithmic bytes -- the kernel streams, so its traffic grows with the rows read
-    roof["traffic"] = 1.024 * attn_bytes_launch if dominant == "attention" and batch * H >= 2 * 148 * 8 else None
-    roof["traffic_source"] = "ncu capture at context 130 scaled by rows" if roof["traffic"] else None
+    ratio, ratio_src = traffic_ratio(roofs[dominant]["kernel"])
+    roof["traffic"] = ratio * attn_bytes_launch if dominant == "attention" and ratio else None
+    roof["traffic_source"] = (ratio_src + ", scaled by the rows this launch reads") if roof["traffic"] else None
     roof["peak_source"] = peak_kind
     roof["launch_ms"] = fam[dominant] / max(1, fam_launches[dominant])
     roof["launches_per_step"] = fam_launches
@@ -321,13 +479,28 @@ def run_b200(args):
     roof["other"] = {k2: {"achieved": v["achieved"], "frac": v["achieved"] / v["peak"]} for k2, v in roofs.items()
                      if k2 != dominant}
 
-    # end to end through the public batched generate call: host prompts in, host tokens out
+    # end to end through the public batched generate call: host prompts in, host tokens out; with more
+    # than one rank every rank's [sequences, prompt + new] token matrix is gathered on rank 0 inside the
+    # timed region (the one cross-GPU step of the batch-sharded path)
     e2e_runs = []
+    gathered_rows = None
     for _ in range(args.e2e_runs):
         barrier()
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         out, lens = model.generate_batch(prompts, max_new)
+        if world > 1:
+            mine = torch.from_numpy(out.astype(np.int32)).cuda()
+            sizes = [shard_bounds(total, world, r)[1] - shard_bounds(total, world, r)[0] for r in range(world)]
+            pad = torch.zeros((max(sizes), mine.shape[1]), dtype=torch.int32, device="cuda")
+            pad[: mine.shape[0]] = mine
+            parts = [torch.empty_like(pad) for _ in range(world)] if rank == 0 else None
+            dist.gather(pad, parts, dst=0)
+            if rank == 0:
+                allt = torch.cat([parts[r][: sizes[r]] for r in range(world)]).cpu().numpy()
+                gathered_rows = int(allt.shape[0])
+        else:
+            gathered_rows = int(out.shape[0])
         t1 = time.perf_counter()
         dt = torch.tensor([t1 - t0], device="cuda", dtype=torch.float64)
         if world > 1:
@@ -337,9 +510,10 @@ def run_b200(args):
     if e2e_runs:
         best = min(e2e_runs)
         e2e = {"value": total * max_new / best, "unit": UNIT, "h2d_bytes_per_step": batch * prompt_len * 4 / max_new,
-               "d2h_bytes_per_step": batch * max_new * 4 / max_new, "seconds_per_generate": best,
-               "note": "generate_batch: prefill + %d decode steps, host token ids in, host tokens out; "
-                       "bytes are per decode step per rank" % max_new}
+               "d2h_bytes_per_step": batch * (prompt_len + max_new) * 4 / max_new, "seconds_per_generate": best,
+               "sequences_on_rank0": gathered_rows,
+               "note": "generate_batch: prefill + %d decode steps, host token ids in, host tokens out, all ranks' "
+                       "tokens gathered on rank 0; bytes are per decode step per rank" % max_new}
 
     # the prefill of this rank's prompts on its own (second of two passes), device time on the library's stream
     p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -362,6 +536,7 @@ def run_b200(args):
                   "f32 weights as fp16 hi + lo / fp16 activations / f32 accumulate"), "data": "synthetic",
         "config": {"workload": args.workload, "total_sequences": total, "sequences_per_gpu": batch,
                    "prompt_len": prompt_len, "decode_window": [prompt_len, prompt_len + window - 1],
+                   "timed_contexts": contexts, "timed_region_repeats": reps, "timed_region_ms": [round(x, 3) for x in rep_ms],
                    "l2": "inputs larger than L2 (weights + KV read per step: %.1f GB)" %
                          ((lin_bytes + attn_bytes_launch * L) / 1e9),
                    "model_build_s": round(build_s, 1)},
@@ -374,6 +549,11 @@ def run_b200(args):
         line["config"]["tuning_overrides"] = args.tune
     if rank == 0 and not args.no_gemv and family == "int4":
         line["gemv"] = gemv_bandwidth(reg, cfg, hbm_peak)
+    if world == 1 and not args.no_isolated and family == "int4" and not args.layers:
+        del sess
+        reg.trim()
+        line["int4_linear"] = int4_linear_isolated(reg, hbm_peak, tf_peak)
+        line["attention"] = attention_isolated(reg, hbm_peak, tf_peak)
     if world == 1 and not args.no_cpu_baseline:
         wq = build_int4_oracle_weights(cfg, w) if family == "int4" else w
         steps = args.cpu_steps
@@ -381,6 +561,8 @@ def run_b200(args):
         line["cpu_baseline"] = {"value": steps / sec, "unit": UNIT, "cores": threads, "kind": "port",
                                 "sample": f"1 of {total} sequences, prompt {args.cpu_prompt}, {steps} KV-cached decode "
                                           f"steps with the oracle (f64 accumulate)"}
+        if not args.no_cpu_reference_form:
+            line["cpu_baseline"]["reference_form_gpt2_small"] = cpu_reference_form()
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -399,7 +581,11 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: build only this many layers")
     ap.add_argument("--no-gemv", action="store_true", help="skip the dequant-GEMV bandwidth measurement")
     ap.add_argument("--e2e-runs", type=int, default=2)
+    ap.add_argument("--reps", type=int, default=5, help="repeats of the timed region (the median is reported)")
+    ap.add_argument("--no-isolated", action="store_true", help="skip the isolated int4 Linear / attention measurements")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-cpu-reference-form", action="store_true",
+                    help="skip the single-thread, cache-less GPT-2 Small CPU run (the reference's own CPU test form)")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
                     help="measurement aid: b200nn_ctx_set_tuning override, e.g. --tune attn_stream=0 (repeatable)")
     ap.add_argument("--cpu-steps", type=int, default=8)

@@ -71,6 +71,7 @@ typedef struct b200nn_attention b200nn_attention;
 typedef struct b200nn_gpt2 b200nn_gpt2;
 typedef struct b200nn_kvcache b200nn_kvcache;
 typedef struct b200nn_session b200nn_session;
+typedef struct b200nn_block b200nn_block;
 
 /* ---- context: KernelRegistry::init_default (GH/nn/registry.rs:131-135) --------------------- */
 B200NN_API const char *b200nn_version(void);
@@ -116,6 +117,15 @@ B200NN_API int32_t b200nn_ctx_set_tuning(b200nn_ctx *ctx, const char *key, int32
 /* Measurement aid: after set_tuning("trace", 1) the first block of the next tensor-core GEMM
  * writes SM-clock stamps of its pipeline events into a 256-slot buffer; this copies it out. */
 B200NN_API int32_t b200nn_ctx_read_trace(b200nn_ctx *ctx, long long *out256);
+/* Measurement aid of the persistent decode kernel (one cooperative launch for all transformer blocks
+ * of an int4 decode step; tuning keys "persist" 0/1, "persist_min_rows", "persist_max_rows",
+ * "persist_prefetch_mb", "persist_wait_kcycles" = bound of its grid-wide waits in thousands of SM
+ * clocks, "persist_fault_phase" = test hook: block 0 leaves out its arrival after that phase so that
+ * every bounded wait runs out and the step reports B200NN_ERR_DEVICE).  After
+ * set_tuning("persist_trace", 1) each block stamps the global timer when the inputs of a phase are
+ * ready and when it arrives at the phase's end, for the first 32 phases of a launch; this copies
+ * out [block][32][2] nanosecond stamps (capacity in 64-bit words).  No counterpart in the reference. */
+B200NN_API int32_t b200nn_ctx_read_persist_trace(b200nn_ctx *ctx, unsigned long long *out, size_t capacity);
 
 /* ---- GpuTensor (GH/nn/tensor.rs:45-110, 201-221, 270) -------------------------------------- */
 B200NN_API int32_t b200nn_tensor_from_host(b200nn_ctx *ctx, const float *host, const size_t *shape, int32_t ndim,
@@ -263,6 +273,38 @@ B200NN_API size_t b200nn_gpt2_quantized_memory_bytes(const b200nn_gpt2 *m);
 B200NN_API int32_t b200nn_gpt2_get_int4(const b200nn_gpt2 *m, int32_t layer, int32_t which, uint32_t *packed,
                                         float *scales, size_t *k_out, size_t *n_out);
 
+/* ---- TransformerBlock / Int4TransformerBlock (gpt2.rs:98-289, 1219-1339) ---------------------------
+ * One pre-LN block: x += Attn(LN1(x)); x += W2.GELU(W1.LN2(x)+b1)+b2.  The twelve slices are what
+ * TransformerBlock::new takes (gpt2.rs:120-135), dense weights in Linear layout [out,in]:
+ * attn_qkv_weight [3d,d], attn_out_weight [d,d], ffn_up_weight [4d,d], ffn_down_weight [d,4d]. */
+typedef struct {
+    const float *ln_1_weight, *ln_1_bias;
+    const float *attn_qkv_weight, *attn_qkv_bias;
+    const float *attn_out_weight, *attn_out_bias;
+    const float *ln_2_weight, *ln_2_bias;
+    const float *ffn_up_weight, *ffn_up_bias;
+    const float *ffn_down_weight, *ffn_down_bias;
+} b200nn_block_weights;
+/* TransformerBlock::new (gpt2.rs:120-170); cfg gives n_embd, n_head and layer_norm_epsilon; flags as
+ * for the models (B200NN_GELU_SIGMOID). */
+B200NN_API int32_t b200nn_block_create(b200nn_ctx *ctx, const b200nn_gpt2_config *cfg, const b200nn_block_weights *w,
+                                       uint32_t flags, b200nn_block **out);
+/* Int4TransformerBlock::new (gpt2.rs:1232-1296) with Int4MultiHeadAttention::new (1141-1188): every
+ * dense weight is transposed to [in,out] and quantised with quantize_weight_int4 (scales rounded to fp16). */
+B200NN_API int32_t b200nn_int4_block_create(b200nn_ctx *ctx, const b200nn_gpt2_config *cfg, const b200nn_block_weights *w,
+                                            size_t group_size, uint32_t flags, b200nn_block **out);
+/* TransformerBlock::forward / forward_auto_fused, Int4TransformerBlock::forward (gpt2.rs:172-243,
+ * 1299-1339): x [seq_len,d] of one sequence, causal attention over its rows -> [seq_len,d].  The fused
+ * epilogues are always on, so forward_auto_fused is this call. */
+B200NN_API int32_t b200nn_block_forward(b200nn_block *b, const b200nn_tensor *x, b200nn_tensor **y);
+/* TransformerBlock::forward_cached (gpt2.rs:249-288): x [new_len,d] at positions kv_len..; cached_k /
+ * cached_v host f32 [n_head][kv_len*64] (NULL when kv_len is 0); returns y and, when the pointers are
+ * given, the new K,V rows [n_head][new_len*64] (the values the fp16 cache holds). */
+B200NN_API int32_t b200nn_block_forward_cached(b200nn_block *b, const b200nn_tensor *x, const float *cached_k,
+                                               const float *cached_v, size_t kv_len, b200nn_tensor **y, float *new_k_out,
+                                               float *new_v_out);
+B200NN_API void b200nn_block_destroy(b200nn_block *b);
+
 /* Gpt2Model::forward / Int4Gpt2Model::forward (gpt2.rs:481-499, 1522-1533): one sequence of host
  * token ids -> logits [seq_len,vocab] for every position. */
 B200NN_API int32_t b200nn_gpt2_forward(b200nn_gpt2 *m, const uint32_t *ids_host, size_t seq_len, b200nn_tensor **logits);
@@ -298,6 +340,22 @@ B200NN_API int32_t b200nn_gpt2_forward_features(b200nn_gpt2 *m, const uint32_t *
 /* Gpt2Model::embedding_table (gpt2.rs:584-586): wte [vocab,n_embd] and wpe [n_positions,n_embd] as
  * tensors that share the model's device buffers; destroy them with b200nn_tensor_destroy. */
 B200NN_API int32_t b200nn_gpt2_embedding_table(b200nn_gpt2 *m, b200nn_tensor **wte, b200nn_tensor **wpe);
+/* Gpt2Model::forward_diagnostic (gpt2.rs:595-667): forward of one sequence plus the values the
+ * reference prints to stderr while it runs, returned instead of printed: the first four hidden values
+ * after the embedding (position 0 and the last position), after block 0 and after the last block (last
+ * position; with the number of NaN/Inf values in the whole hidden state), after the final LayerNorm
+ * (last position), and the five highest logits of the last position with their token ids. */
+typedef struct {
+    float embedding_first[4], embedding_last[4];
+    float block0_last[4], final_block_last[4];
+    int32_t block0_nonfinite, final_block_nonfinite;
+    float ln_f_last[4];
+    uint32_t top_tokens[5];
+    float top_scores[5];
+    int32_t n_top;
+} b200nn_gpt2_diagnostic;
+B200NN_API int32_t b200nn_gpt2_forward_diagnostic(b200nn_gpt2 *m, const uint32_t *ids_host, size_t seq_len,
+                                                  b200nn_tensor **logits, b200nn_gpt2_diagnostic *diag);
 /* Gpt2Model::forward_profiled (gpt2.rs:529-568): forward plus the device time in milliseconds of
  * every component in the reference's order: embedding, block_0 .. block_{L-1}, ln_f, lm_head
  * (n_layer + 3 values; `capacity` is the length of times_ms). */
@@ -397,6 +455,46 @@ B200NN_API const char *b200nn_safetensors_last_error(void);
 B200NN_API int32_t b200nn_gpt2_load_safetensors(b200nn_ctx *ctx, const char *path, const b200nn_gpt2_config *cfg,
                                                 size_t int4_group, uint32_t flags, b200nn_gpt2 **out);
 
+/* ---- Gpt2Tokenizer (crates/core/gpu-host/src/tokenizer.rs:34-62) ---------------------------------
+ * Host code.  The reference wraps tiktoken-rs' r50k_base; here the byte-level BPE is implemented over a
+ * vocabulary given at run time: a file in tiktoken's format (one "base64(token bytes) rank" per
+ * line, as r50k_base.tiktoken is published) or a table in memory.  `endoftext_id` is the id of the
+ * special token <|endoftext|> (50256 for GPT-2; tokenizer.rs:10-11).  Every single byte must be a
+ * token.  b200nn_bpe_encode = Gpt2Tokenizer::encode (encode_with_special_tokens), b200nn_bpe_decode =
+ * ::decode (returns raw bytes; the caller checks UTF-8), b200nn_bpe_vocab_size = ::vocab_size.
+ * b200nn_bpe_encode_piece merges one already-split piece (for hosts that split with their own Unicode
+ * tables; the library's splitter is exact for ASCII and approximates \p{L} / \p{N} by block beyond).
+ * Buffers too small return B200NN_ERR_SHAPE with the needed length in *n_out. */
+typedef struct b200nn_bpe b200nn_bpe;
+B200NN_API int32_t b200nn_bpe_load(const char *path, uint32_t endoftext_id, b200nn_bpe **out);
+/* token i = token_bytes[token_offsets[i] .. token_offsets[i+1]) with rank ranks[i] */
+B200NN_API int32_t b200nn_bpe_create(const uint8_t *token_bytes, const size_t *token_offsets, const uint32_t *ranks,
+                                     size_t n_tokens, uint32_t endoftext_id, b200nn_bpe **out);
+B200NN_API void b200nn_bpe_destroy(b200nn_bpe *t);
+B200NN_API size_t b200nn_bpe_vocab_size(const b200nn_bpe *t);
+B200NN_API int32_t b200nn_bpe_encode(const b200nn_bpe *t, const uint8_t *text, size_t n, uint32_t *out, size_t capacity,
+                                     size_t *n_out);
+B200NN_API int32_t b200nn_bpe_encode_piece(const b200nn_bpe *t, const uint8_t *piece, size_t n, uint32_t *out,
+                                           size_t capacity, size_t *n_out);
+B200NN_API int32_t b200nn_bpe_decode(const b200nn_bpe *t, const uint32_t *ids, size_t n, uint8_t *out, size_t capacity,
+                                     size_t *n_out);
+B200NN_API const char *b200nn_bpe_last_error(void);
+
+/* ---- batched attention on caller-owned fp16 device buffers ----------------------------------------
+ * The model path's attention kernels as stand-alone, stream-ordered operations (what
+ * ops::multi_head_flash_attention / flash_attention_kv, ops/attention.rs:151-202, 557-606, are to the
+ * reference's layers), with the batch axis and the fp16 cache layout of this library:
+ *   q_dev, out_dev              fp16 [batch*rows, n_heads*64], token-major (rows = seq_len, or 1 for decode)
+ *   k_cache_dev, v_cache_dev    fp16 [batch][n_heads][capacity][64], new positions already appended
+ * prefill: row i of a sequence sits at position past+i and attends to positions 0..past+i (tcgen05
+ * kernel); decode: one query per sequence against positions 0..ctx_len-1.  All buffers 16-byte aligned. */
+B200NN_API int32_t b200nn_prefill_attention_f16(b200nn_ctx *ctx, const void *q_dev, const void *k_cache_dev,
+                                                const void *v_cache_dev, int32_t batch, int32_t n_heads, int32_t capacity,
+                                                int32_t seq_len, int32_t past, void *out_dev);
+B200NN_API int32_t b200nn_decode_attention_f16(b200nn_ctx *ctx, const void *q_dev, const void *k_cache_dev,
+                                               const void *v_cache_dev, int32_t batch, int32_t n_heads, int32_t capacity,
+                                               int32_t ctx_len, void *out_dev);
+
 /* ---- decode attention without any allocation ----------------------------------------------------
  * This entry point has no counterpart in the reference.  It is for callers that cannot let the
  * library call cudaMalloc: a host that has handed out its whole device-memory budget, or code that
@@ -404,7 +502,9 @@ B200NN_API int32_t b200nn_gpt2_load_safetensors(b200nn_ctx *ctx, const char *pat
  * It needs no context: the caller passes the device ordinal, its own
  * stream (NULL = default stream), and device buffers it owns:
  *   q_dev   [batch, n_heads*64] f32    one query row per sequence
- *   k_cache_dev, v_cache_dev  fp16 [batch][n_heads][capacity][64], positions [0, ctx_len) filled
+ *   k_cache_dev, v_cache_dev  fp16 [batch][n_heads][capacity][64], positions [0, ctx_len) filled;
+ *                             both 16-byte aligned (rows are read with 16-byte loads; a misaligned
+ *                             pointer returns B200NN_ERR_ARG instead of faulting on the device)
  *   out_dev [batch, n_heads*64] f32
  * and gets softmax(q.K^T/8).V per (sequence, head) over the first ctx_len positions, computed by
  * the same kernel as the regular decode path.  The kernel's split-context scratch is a fixed

@@ -532,6 +532,23 @@ static void block_forward(const orc_model *m, const orc_layer *L, double *hidden
     free(ln); free(qkv); free(ac); free(tmp); free(fh);
 }
 
+/* One transformer block on its own (TransformerBlock::forward / forward_cached, gpt2.rs:172-288), for
+ * checking a block handle in isolation: layer `layer` of `m` over `nq` rows x [nq,d] at positions
+ * past..; kc / vc f32 [n_head][cap][dh] hold the cached rows [0,past) on entry and the new rows as
+ * well on return; out [nq,d]. */
+ORC_API void orc_block_forward(const orc_model *m, int layer, const float *x, size_t nq, size_t past, float *kc,
+                               float *vc, size_t cap, uint32_t flags, float *out) {
+    size_t d = (size_t)m->cfg.n_embd, H = (size_t)m->cfg.n_head, dh = d / H, nkv = H * cap * dh;
+    double *h = (double *)malloc(nq * d * sizeof(double));
+    double *kd = (double *)malloc(nkv * sizeof(double)), *vd = (double *)malloc(nkv * sizeof(double));
+    for (size_t i = 0; i < nq * d; ++i) h[i] = (double)x[i];
+    for (size_t i = 0; i < nkv; ++i) { kd[i] = (double)kc[i]; vd[i] = (double)vc[i]; }
+    block_forward(m, &m->layers[layer], h, nq, past, kd, vd, cap, flags);
+    for (size_t i = 0; i < nq * d; ++i) out[i] = (float)h[i];
+    for (size_t i = 0; i < nkv; ++i) { kc[i] = (float)kd[i]; vc[i] = (float)vd[i]; }
+    free(h); free(kd); free(vd);
+}
+
 typedef struct {
     double *k, *v; /* [n_layer][n_head][cap][dh] */
     size_t cap, len;

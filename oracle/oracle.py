@@ -85,6 +85,7 @@ def lib() -> C.CDLL:
                                       C.POINTER(C.c_double), u32p]
         L.orc_time_decode.restype = C.c_int
         L.orc_mha_f64.argtypes = [f32p, sz, f32p, f32p, sz, sz, sz, sz, sz, f32p]
+        L.orc_block_forward.argtypes = [C.c_void_p, C.c_int, f32p, sz, sz, f32p, f32p, sz, C.c_uint32, f32p]
         u64p, i32p = C.POINTER(C.c_uint64), C.POINTER(C.c_int32)
         L.orc_rng_new.argtypes = [C.c_uint64]
         L.orc_rng_new.restype = C.c_uint64
@@ -291,6 +292,25 @@ class Model:
         if rc != 0:
             raise RuntimeError(f"orc_forward rc={rc}")
         return out
+
+    def block_forward(self, layer, x, past=0, kc=None, vc=None, flags=0):
+        """One block alone: x [nq,d] at positions past..; kc / vc [H,past,dh] are the cached rows.
+        Returns (out [nq,d], k [H,past+nq,dh], v [H,past+nq,dh])."""
+        x, xp = _f32(x)
+        nq, d = x.shape
+        H = self.cfg.n_head
+        dh = d // H
+        cap = past + nq
+        k = np.zeros((H, cap, dh), dtype=np.float32)
+        v = np.zeros((H, cap, dh), dtype=np.float32)
+        if past:
+            k[:, :past] = np.asarray(kc, dtype=np.float32).reshape(H, past, dh)
+            v[:, :past] = np.asarray(vc, dtype=np.float32).reshape(H, past, dh)
+        out = np.empty((nq, d), dtype=np.float32)
+        f32p = C.POINTER(C.c_float)
+        lib().orc_block_forward(self._h, layer, xp, nq, past, k.ctypes.data_as(f32p), v.ctypes.data_as(f32p), cap, flags,
+                                out.ctypes.data_as(f32p))
+        return out, k, v
 
     def _gen(self, fn, prompt, max_new, flags, want_logits):
         p, pp = _u32(prompt)

@@ -29,6 +29,40 @@ def test_library_exports_every_declared_symbol():
     assert set(names) == set(lib._declared)
 
 
+def test_rust_sys_crate_declares_exactly_the_header(): 
+    """crates/b200nn-sys/src/lib.rs (the binding the reference's Rust host links against; it cannot be
+    compiled where there is no cargo) must declare every exported function once, with the header's
+    parameter count, and the #[repr(C)] structs must have the header's fields in the header's order."""
+    text = open(os.path.join(ROOT, "include", "b200nn.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    h_fns = {}
+    for m in re.finditer(r"B200NN_API\s+[^;#]*?\b(b200nn_\w+)\s*\(([^;]*?)\)\s*;", header, flags=re.S):
+        args = " ".join(m.group(2).split())
+        h_fns[m.group(1)] = 0 if args == "void" else args.count(",") + 1
+    rs = open(os.path.join(ROOT, "crates", "b200nn-sys", "src", "lib.rs")).read()
+    r_fns = {}
+    for m in re.finditer(r"pub fn (b200nn_\w+)\s*\((.*?)\)\s*(?:->\s*[^;]+)?;", rs, flags=re.S):
+        args = m.group(2).strip().rstrip(",")
+        assert m.group(1) not in r_fns, f"{m.group(1)} declared twice"
+        r_fns[m.group(1)] = 0 if not args else args.count(":")
+    assert set(r_fns) == set(h_fns) == set(_declared_symbols())
+    assert r_fns == h_fns
+    # struct fields: C `const float *a, *b;` lists against Rust `pub a: *const f32,`
+    for name in ("b200nn_gpt2_config", "b200nn_gpt2_layer_weights", "b200nn_gpt2_weights", "b200nn_block_weights",
+                 "b200nn_gpt2_diagnostic"):
+        c_body = re.search(r"typedef struct \{([^}]*)\}\s*" + name + r"\s*;", header).group(1)
+        c_fields = []
+        for stmt in c_body.split(";"):
+            stmt = stmt.strip()
+            if stmt:
+                c_fields += [re.sub(r"\[\d+\]|[^\w]", "", part.split()[-1]) for part in stmt.split(",")]
+        r_body = re.search(r"pub struct " + name + r"\s*\{([^}]*)\}", rs).group(1)
+        r_fields = re.findall(r"pub (\w+):", r_body)
+        assert r_fields == c_fields, name
+    for const in re.findall(r"\b(B200NN_[A-Z0-9_]+)\s*=", header):
+        assert re.search(r"pub const " + const + r":", rs), f"{const} missing from the crate"
+
+
 def test_version_string():
     assert b"sm_100a" in b200nn.load_library().b200nn_version()
 

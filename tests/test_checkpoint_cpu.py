@@ -89,7 +89,8 @@ def test_reads_files_written_by_the_safetensors_package(tmp_path):
     assert all(np.array_equal(back[k], t[k]) for k in t)
 
 
-@pytest.mark.parametrize("case", ["missing", "short", "hdr_len", "not_json", "range", "size", "dtype", "dup", "no_offsets"])
+@pytest.mark.parametrize("case", ["missing", "short", "hdr_len", "not_json", "range", "size", "dtype", "dup", "no_offsets",
+                                  "overflow", "overlap", "gap", "uncovered"])
 def test_malformed_files_are_rejected(tmp_path, case):
     p = tmp_path / "bad.safetensors"
     data = np.arange(4, dtype=np.float32).tobytes()
@@ -115,6 +116,17 @@ def test_malformed_files_are_rejected(tmp_path, case):
         put(b'{"a":{"dtype":"F32","shape":[2],"data_offsets":[0,8]},"a":{"dtype":"F32","shape":[2],"data_offsets":[8,16]}}')
     elif case == "no_offsets":
         put(json.dumps({"a": {"dtype": "F32", "shape": [4]}}).encode())
+    elif case == "overflow":  # 2^32 x 2^32 x 4 bytes wraps to 0 in 64 bits: must not pass as an empty tensor
+        put(json.dumps({"a": {"dtype": "F32", "shape": [2**32, 2**32], "data_offsets": [0, 0]},
+                        "b": {"dtype": "F32", "shape": [4], "data_offsets": [0, 16]}}).encode())
+    elif case == "overlap":
+        put(json.dumps({"a": {"dtype": "F32", "shape": [3], "data_offsets": [0, 12]},
+                        "b": {"dtype": "F32", "shape": [2], "data_offsets": [8, 16]}}).encode())
+    elif case == "gap":
+        put(json.dumps({"a": {"dtype": "F32", "shape": [1], "data_offsets": [0, 4]},
+                        "b": {"dtype": "F32", "shape": [2], "data_offsets": [8, 16]}}).encode())
+    elif case == "uncovered":  # the last 8 bytes of the data section belong to no tensor
+        put(json.dumps({"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8]}}).encode())
     with pytest.raises(b200nn.NnError) as e:
         checkpoint.SafeTensorsFile(p)
     assert e.value.code == b200nn.ERR_IO and str(e.value)
@@ -140,7 +152,9 @@ def test_load_int4_tensors_layout_of_the_reference_script(tmp_path):
     from oracle import oracle
     rng = np.random.default_rng(11)
     tensors, want = {}, {}
-    for key, (k, n) in {"h.0.mlp.c_fc.weight": (256, 40), "h.0.attn.c_proj.weight": (200, 24), "small": (64, 8)}.items():
+    # 1080 rows: nine 128-wide groups (the last ragged), although 1080 / 9 = 120 would tile as well
+    for key, (k, n) in {"h.0.mlp.c_fc.weight": (256, 40), "h.0.attn.c_proj.weight": (200, 24), "small": (64, 8),
+                        "ragged9": (1080, 8)}.items():
         w = (rng.standard_normal((k, n)) * 0.05).astype(np.float32)
         p, s = oracle.quantize_weight_int4(w, k, n, 128)
         tensors[key + ".int4_packed"], tensors[key + ".int4_scales"] = p.reshape(k // 8, n), s.reshape(-1, n)

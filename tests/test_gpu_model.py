@@ -486,3 +486,100 @@ def test_full_size_int4_models_against_oracle(reg, preset, batch, prompt_len, ne
     ref = om.forward(prompts[0], flags=oracle.KV_FP16)[-1]
     assert np.abs(got - ref).max() < MAX_ABS and np_ref.rel_rms(got, ref) < REL_RMS
     assert reg.device_error() == 0
+    if preset != "xl":
+        return
+    # the benchmark's own decode window: 256 sequences with 128-token prompts, stepped to a context of 161;
+    # the logits of that step (rows 0 and 255) against the oracle, where the greedy histories agree
+    P, steps = 128, 33
+    prompts = synth.token_ids(synth.BASE_SEED + 7, (batch, P), cfg.vocab_size)
+    s = DecodeSession(m, batch=batch, capacity=P + steps + 2)
+    s.prefill(prompts)
+    s.step(1)
+    s.step(steps - 1)
+    assert s.position() == P + steps
+    toks, lgs = s.tokens(), s.logits()
+    compared = 0
+    for b in (0, batch - 1):
+        ref, lg = om.generate_cached(prompts[b], steps + 1, flags=oracle.KV_FP16, want_logits=True)
+        _check_tokens(np.concatenate([prompts[b], toks[b]]), ref, lg, P)
+        if np.array_equal(toks[b], ref[P:]):
+            assert np.abs(lgs[b] - lg[-1]).max() < MAX_ABS and np_ref.rel_rms(lgs[b], lg[-1]) < REL_RMS
+            compared += 1
+    assert compared >= 1  # a near-tie may end one history early, not both
+    assert reg.device_error() == 0
+
+
+def test_forward_diagnostic_reports_the_reference_values(reg, capsys):
+    """forward_diagnostic (gpt2.rs:595-667): the same logits as forward, and the reported values are the
+    oracle's hidden states at the places the reference prints them."""
+    cfg = _mini(n_layer=3)
+    w = synth.gpt2_weights(cfg, base_seed=83, std=0.08, random_ln=True)
+    m = Gpt2Model.from_weights(w, cfg, reg)
+    toks = synth.token_ids(4, (11,), cfg.vocab_size)
+    logits, rep = m.forward_diagnostic(toks)
+    got = logits.to_host()
+    ref = oracle.Model(cfg.as_dict(), w).forward(toks, flags=oracle.KV_FP16)
+    _check_logits(got, ref)
+    err = capsys.readouterr().err
+    assert "[diag] Embedding pos0 first4:" in err and "[diag] Layer 2 pos10 first4:" in err and "Top-5 tokens at pos10" in err
+    emb0 = w["wte"][toks[0]][:4] + w["wpe"][0][:4]
+    assert np.allclose(rep["embedding_first"], emb0, atol=1e-6)
+    emb_last = w["wte"][toks[-1]][:4] + w["wpe"][10][:4]
+    assert np.allclose(rep["embedding_last"], emb_last, atol=1e-6)
+    assert rep["block0_nonfinite"] == 0 and rep["final_block_nonfinite"] == 0
+    order = np.argsort(-ref[-1], kind="stable")[:5]
+    assert [t for t, _ in rep["top"]] == order.tolist() or np.abs(np.sort(ref[-1])[::-1][:5] - [v for _, v in rep["top"]]).max() < 2e-2
+    assert np.allclose([v for _, v in rep["top"]], np.sort(got[-1])[::-1][:5], atol=1e-6)
+    # hidden state after block 0, last position, against the oracle's block on the embedded rows
+    x = (w["wte"][toks] + w["wpe"][: len(toks)]).astype(np.float32)
+    h0, _, _ = oracle.Model(cfg.as_dict(), w).block_forward(0, x, flags=oracle.KV_FP16)
+    assert np.abs(np.asarray(rep["block0_last"]) - h0[-1][:4]).max() < 5e-3
+
+
+def test_two_contexts_in_one_process_one_host_thread_each(reg):
+    """One context per GPU, one host thread per context (the threading model of the batch-sharded path):
+    two contexts are created in this process (on two GPUs when there are two, else both on GPU 0), each
+    thread builds its own int4 model and generates its half of the batch, then runs a four-row Int4Linear
+    through the CUDA-core GEMV at a shape (K 4096, 149 feature tiles: no K split) whose block needs more than
+    48 KB of dynamic shared memory, which is a per-device function attribute."""
+    import threading
+
+    import torch
+    ndev = torch.cuda.device_count()
+    devices = [0, 1 if ndev > 1 else 0]
+    cfg = _mini(n_layer=2, d=128, vocab=257, npos=64)
+    w = synth.gpt2_weights(cfg, base_seed=88, std=0.08, random_ln=True)
+    prompts = synth.token_ids(6, (12, 9), cfg.vocab_size)
+    K, N = 4096, 19072
+    rng = np.random.default_rng(5)
+    packed = rng.integers(0, 2 ** 32, (K // 8, N), dtype=np.uint32)  # eight random nibbles per word
+    scales = rng.uniform(0.005, 0.02, (K // 128, N)).astype(np.float16).astype(np.float32)
+    x = rng.standard_normal((4, K)).astype(np.float32)
+    results, errors = {}, []
+
+    def work(i):
+        try:
+            r = b200nn.KernelRegistry(devices[i])
+            m = Int4Gpt2Model.from_weights(w, cfg, r)
+            out, lens = m.generate_batch(prompts[i * 6:(i + 1) * 6], 6)
+            r.set_gemv_max_rows(4)
+            y = b200nn.Int4Linear(packed, scales, None, K, N, 128, r).forward(b200nn.GpuTensor.from_host(x, (4, K), r)).to_host()
+            results[i] = (out, y, r.device_error())
+            r.close()
+        except Exception as e:  # surfaced below: a thread must not swallow a failure
+            errors.append((i, repr(e)))
+
+    th = [threading.Thread(target=work, args=(i,)) for i in range(2)]
+    for t in th:
+        t.start()
+    for t in th:
+        t.join()
+    assert not errors, errors
+    m0 = Int4Gpt2Model.from_weights(w, cfg, reg)
+    ref, _ = m0.generate_batch(prompts, 6)
+    yref = oracle.int4_linear(x, packed, scales, None, 4, N, K, 128)
+    for i in range(2):
+        out, y, err = results[i]
+        assert err == 0
+        assert (out == ref[i * 6:(i + 1) * 6]).mean() > 0.97
+        assert np_ref.rel_rms(y, yref) < 1e-5

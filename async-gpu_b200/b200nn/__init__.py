@@ -19,7 +19,7 @@ LIB_PATH = os.path.join(os.path.dirname(_HERE), "libb200nn.so")
 
 OK, ERR_SHAPE, ERR_DIM, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE, ERR_ARG, ERR_IO, ERR_MISSING = range(9)
 ACT_NONE, ACT_GELU_TANH, ACT_GELU_SIGMOID, ACT_RELU = range(4)
-GELU_SIGMOID, QUANT_LM_HEAD, ARGMAX_LAST, STOP_ON_EOS = 1, 2, 4, 8
+GELU_SIGMOID, QUANT_LM_HEAD, ARGMAX_LAST, STOP_ON_EOS, TOKENS_ONLY = 1, 2, 4, 8, 16
 PROF_NAMES = ("embed", "layernorm", "linear", "attention", "lm_head", "argmax")
 
 _KINDS = {ERR_SHAPE: "ShapeMismatch", ERR_DIM: "DimOutOfRange", ERR_UNSUPPORTED: "KernelNotFound",
@@ -157,6 +157,8 @@ def load_library() -> C.CDLL:
             "b200nn_gpt2_forward_profiled": (i32, [vp, _u32p, sz, vpp, _f32p, i32, C.POINTER(i32)]),
             "b200nn_simple_rng_new": (C.c_uint64, [C.c_uint64]),
             "b200nn_simple_rng_next_f32": (C.c_float, [C.POINTER(C.c_uint64)]),
+            "b200nn_simple_rng_fill_uniform": (i32, [C.POINTER(C.c_uint64), sz, _f32p]),
+            "b200nn_simple_rng_fill_normal": (i32, [C.POINTER(C.c_uint64), sz, C.c_float, _f32p]),
             "b200nn_top_k_sample": (i32, [_f32p, sz, sz, C.c_float, C.POINTER(C.c_uint64), _u32p]),
             "b200nn_gpt2_generate_cached_sampling": (i32, [vp, _u32p, sz, sz, sz, C.c_float, C.POINTER(C.c_uint64), _u32p,
                                                            szp]),

@@ -38,6 +38,8 @@ struct b200nn_ctx {
     int last_cuda = 0;
     int sm_count = 148;
     int gemv_max_rows = 2;       // rows at or below this take the CUDA-core GEMV
+    int ln_fold = 0;             // 1: decode steps of int4 models fold each block LayerNorm into the GEMMs around it (measured slower than the LayerNorm kernels: the residual GEMMs then need complete sums, i.e. cluster splits)
+    int fused_argmax = 1;        // greedy decode steps take the argmax in the LM head's epilogue (0: separate kernel)
     uint64_t launches = 0;       // kernels launched by this library
     uint32_t *dev_err = nullptr; // device error word (bounded waits report here)
     uint32_t *host_err = nullptr; // pinned landing place of that word for stream_sync_check
@@ -188,6 +190,12 @@ struct Int4Weight {
 };
 int int4_weight_upload(b200nn_ctx *ctx, const uint32_t *packed, const float *scales, const float *bias, size_t K,
                        size_t N, size_t group, Int4Weight *out);
+// The two per-feature vectors a Linear needs to take a LayerNorm (scale g, shift beta, both [K] on the
+// device) in through its epilogue (see Epilogue): gsum[n] = sum_k g_k w_kn and
+// bc[n] = sum_k beta_k w_kn + bias[n], with w the dequantised weight as the kernels see it
+// (fp16(nibble * fp16 scale)); accumulated in f64.
+int int4_weight_ln_fold(b200nn_ctx *ctx, const Int4Weight &w, const float *g_dev, const float *beta_dev,
+                        std::shared_ptr<DevBuf> *gsum, std::shared_ptr<DevBuf> *bc);
 
 // f32 weight of a Linear, stored [K,N] (= [in,out]) row-major on the device.
 // w_nk_h: the same weight rounded to fp16 and stored [N,K] (K contiguous), the operand of the
@@ -203,7 +211,7 @@ int f32_weight_upload(b200nn_ctx *ctx, const float *w, bool is_out_in, const flo
 // ---------------------------------------------------------------------------------------------
 // epilogue shared by every Linear kernel
 // ---------------------------------------------------------------------------------------------
-enum { EPI_STORE = 0, EPI_RESID = 1, EPI_QKV = 2 };
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_QKV = 2, EPI_RESID_LN = 3 };
 
 struct Epilogue {
     int mode = EPI_STORE;
@@ -218,6 +226,29 @@ struct Epilogue {
     int d_model = 0, n_head = 0, rows_per_seq = 1, cap = 0;
     const int *pos_ptr = nullptr; // optional device scalar added to pos_off
     int pos_off = 0;
+    // Greedy pick fused into the epilogue (LM head): per output row and per group of 32 consecutive
+    // features the largest finished value and its feature index go to amax_val / amax_idx
+    // [row][amax_entries]; a second, tiny kernel reduces the entries of a row (launch_argmax_entries).
+    // Ties keep the lowest index, or the highest with amax_keep_last.  no_store: do not write `out`.
+    float *amax_val = nullptr;
+    int *amax_idx = nullptr;
+    int amax_entries = 0, amax_keep_last = 0, no_store = 0;
+    // LayerNorm folded into the GEMMs on either side of it (decode steps of the int4 models), so that no
+    // LayerNorm kernel runs between them.  With LN(x) = (x - mean) * rstd * g + b,
+    //     LN(x) . W = rstd * ((x * g) . W - mean * sum_k g_k W_kn) + sum_k b_k W_kn :
+    // producer (mode EPI_RESID_LN, a residual GEMM whose block holds complete sums): x_new = resid + value
+    //   is written back (f32), xg_out = fp16(x_new * next_g) is what the next GEMM multiplies, and the
+    //   row's (sum x_new, sum x_new^2) over the 128 features of feature tile t goes to
+    //   stats_out[(row * stats_nt + t) * 2 + 0..1] (every tile writes its own slot: no zeroing, no atomics);
+    // consumer (ln_stats set): finished value = rstd * (acc - mean * ln_gsum[n]) + bias[n], where mean and
+    //   rstd come from the ln_nt (<= 32) partial sums of the row and `bias` already holds
+    //   sum_k b_k W_kn + the Linear's own bias.
+    const float *ln_stats = nullptr, *ln_gsum = nullptr;
+    int ln_nt = 0, stats_nt = 0;
+    float ln_eps = 0.0f, ln_inv_d = 0.0f;
+    __half *xg_out = nullptr;
+    const float *next_g = nullptr;
+    float *stats_out = nullptr;
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -237,6 +268,11 @@ int launch_int4_via_f16(b200nn_ctx *ctx, const Int4Weight &w, const __half *x, i
 
 int launch_layernorm(b200nn_ctx *ctx, const float *x, const float *res_in, float *sum_out, const float *gamma,
                      const float *beta, float eps, int rows, int d, void *out, bool out_half);
+// launch_embedding that also prepares the first LayerNorm for folding: xg = fp16(out * g) and each row's
+// (sum, sum of squares) in partial 0 of stats [n_rows][stats_nt][2] (the other partials zero).
+int launch_embedding_ln(b200nn_ctx *ctx, const uint32_t *ids, const float *wte, const float *wpe, int n_rows, int d,
+                        const int *pos_ptr, int vocab, int n_positions, float *out, const float *g, __half *xg,
+                        float *stats, int stats_nt);
 int launch_embedding(b200nn_ctx *ctx, const uint32_t *ids, const float *wte, const float *wpe, int n_rows, int d,
                      int rows_per_seq, const int *pos_ptr, int pos_off, int vocab, int n_positions, float *out);
 int launch_activation(b200nn_ctx *ctx, const float *x, float *y, size_t n, int act);
@@ -251,6 +287,9 @@ int launch_gather_last_rows(b200nn_ctx *ctx, const float *src, int n_seq, int ro
 // logits [rows, ld] -> token per row; appends to history[row*hist_cap + *hist_len_ptr]; finished mask
 int launch_argmax(b200nn_ctx *ctx, const float *logits, int rows, int vocab, int ld, bool keep_last,
                   uint32_t *tok_out);
+// second stage of the fused greedy pick: entries [rows][n_entries] (value, index) -> token per row
+int launch_argmax_entries(b200nn_ctx *ctx, const float *val, const int *idx, int rows, int n_entries, int vocab,
+                          bool keep_last, uint32_t *tok_out);
 int launch_record_tokens(b200nn_ctx *ctx, const uint32_t *tok, int rows, uint32_t *history, int hist_cap,
                          int *step_ptr, int *pos_ptr);
 

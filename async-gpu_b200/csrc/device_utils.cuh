@@ -35,6 +35,7 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 
 // Consumes one finished output value v (bias already added) for row m (token), column n (feature).
 __device__ __forceinline__ void epi_store(const Epilogue &e, int m, int n, float v) {
+    if (e.no_store) return;
     if (e.mode == EPI_RESID) {
         size_t i = (size_t)m * e.ldo + n;
         e.resid[i] += v;
@@ -65,6 +66,7 @@ __device__ __forceinline__ void epi_store(const Epilogue &e, int m, int n, float
 // stores when the destination allows it, element-wise otherwise.  pos_ptr must already be folded
 // into e.pos_off by the caller (it is not dereferenced here for the vector path).
 __device__ __forceinline__ void epi_store4(const Epilogue &e, int m, int n, float4 v, int N) {
+    if (e.no_store) return;
     const bool vec = (n + 3 < N) && ((e.ldo & 3) == 0) && (e.pos_ptr == nullptr);
     if (!vec) {
         if (n < N) epi_store(e, m, n, v.x);
@@ -109,6 +111,56 @@ __device__ __forceinline__ void epi_store4(const Epilogue &e, int m, int n, floa
     }
 }
 
+// ---- greedy pick fused into the epilogue ---------------------------------------------------------
+// The better of two (value, index) candidates: larger value; on equal values the lower index, or the
+// higher with keep_last (Rust's max_by, gpt2.rs:991-997).  NaN never wins, as in argmax_kernel.
+__device__ __forceinline__ void amax_merge(float &bv, int &bi, float v, int i, int keep_last) {
+    if (v > bv || (v == bv && (keep_last ? i > bi : i < bi))) {
+        bv = v;
+        bi = i;
+    }
+}
+// Warp-collective (all 32 lanes, converged).  The lane holds the finished values of features n..n+3 of
+// row m (n a multiple of 4, consecutive lanes consecutive groups of four): each group of eight lanes
+// covers 32 features = one entry of the partial-argmax table.
+__device__ __forceinline__ void epi_argmax4(const Epilogue &e, int m, int n, float4 v, int N) {
+    float bv = -INFINITY;
+    int bi = e.amax_keep_last ? -1 : 0x7fffffff;
+    if (n < N) amax_merge(bv, bi, v.x, n, e.amax_keep_last);
+    if (n + 1 < N) amax_merge(bv, bi, v.y, n + 1, e.amax_keep_last);
+    if (n + 2 < N) amax_merge(bv, bi, v.z, n + 2, e.amax_keep_last);
+    if (n + 3 < N) amax_merge(bv, bi, v.w, n + 3, e.amax_keep_last);
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        amax_merge(bv, bi, ov, oi, e.amax_keep_last);
+    }
+    if ((threadIdx.x & 7) == 0 && (n >> 5) < e.amax_entries) {
+        const size_t at = (size_t)m * e.amax_entries + (n >> 5);
+        e.amax_val[at] = bv;
+        e.amax_idx[at] = bi;
+    }
+}
+// Warp-collective.  The lane holds the finished value of feature n of row m, the warp 32 consecutive
+// features starting at a multiple of 32 (valid = the lane's feature exists).
+__device__ __forceinline__ void epi_argmax1(const Epilogue &e, int m, int n, float v, bool valid) {
+    float bv = valid ? v : -INFINITY;
+    int bi = valid && v == v ? n : (e.amax_keep_last ? -1 : 0x7fffffff);
+    if (!(bv == bv)) bv = -INFINITY; // NaN never wins
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        amax_merge(bv, bi, ov, oi, e.amax_keep_last);
+    }
+    if ((threadIdx.x & 31) == 0 && (n >> 5) < e.amax_entries) {
+        const size_t at = (size_t)m * e.amax_entries + (n >> 5);
+        e.amax_val[at] = bv;
+        e.amax_idx[at] = bi;
+    }
+}
+
 // Bias of the four features n..n+3 (zero without a bias and past N).
 __device__ __forceinline__ float4 epi_bias4(const Epilogue &e, int n, int N) {
     float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -139,6 +191,81 @@ __device__ __forceinline__ void epi_resid_red4(const Epilogue &e, int m, int n, 
 
 __device__ __forceinline__ float4 f4_add(float4 a, float4 b) {
     return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+}
+
+// ---- LayerNorm folded into the neighbouring GEMMs (see Epilogue) ---------------------------------
+// A row's (mean, 1/sqrt(var + eps)) from the partial sums its producer left, added in tile order.
+__device__ __forceinline__ float2 epi_row_mean_rstd(const Epilogue &e, int m) {
+    const float2 *p = reinterpret_cast<const float2 *>(e.ln_stats) + (size_t)m * e.ln_nt;
+    float s1 = 0.0f, s2 = 0.0f;
+    for (int j = 0; j < e.ln_nt; ++j) {
+        const float2 v = __ldcg(p + j);
+        s1 += v.x;
+        s2 += v.y;
+    }
+    const float mean = s1 * e.ln_inv_d;
+    return make_float2(mean, rsqrtf(fmaxf(s2 * e.ln_inv_d - mean * mean, 0.0f) + e.ln_eps));
+}
+// The four sums of products acc (features n..n+3 of a row) -> finished values: plain bias add, or with
+// ln_stats the normalisation applied after the product (mr = the row's mean and rstd, g4 =
+// ln_gsum[n..n+3], b4 = bias[n..n+3]).
+__device__ __forceinline__ float4 epi_finish4(const Epilogue &e, float4 acc, float4 g4, float4 b4, float2 mr) {
+    if (!e.ln_stats) return f4_add(acc, b4);
+    const float mean = mr.x, rstd = mr.y;
+    return make_float4(fmaf(rstd, fmaf(-mean, g4.x, acc.x), b4.x), fmaf(rstd, fmaf(-mean, g4.y, acc.y), b4.y),
+                       fmaf(rstd, fmaf(-mean, g4.z, acc.z), b4.z), fmaf(rstd, fmaf(-mean, g4.w, acc.w), b4.w));
+}
+// The per-lane constant of the LayerNorm fold: the consumer's ln_gsum[n..n+3], or the producer's
+// next_g[n..n+3] (no Linear is both).
+__device__ __forceinline__ float4 epi_fold4(const Epilogue &e, int n, int N) {
+    const float *src = e.mode == EPI_RESID_LN ? e.next_g : e.ln_gsum;
+    float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (src) {
+        if (n < N) g.x = src[n];
+        if (n + 1 < N) g.y = src[n + 1];
+        if (n + 2 < N) g.z = src[n + 2];
+        if (n + 3 < N) g.w = src[n + 3];
+    }
+    return g;
+}
+// The residual values a producer row will be added to (fetched early, under the reduction of the sums).
+__device__ __forceinline__ float4 epi_resid_old4(const Epilogue &e, int m, int n, int N) {
+    if (e.mode != EPI_RESID_LN || n >= N) return make_float4(0.f, 0.f, 0.f, 0.f);
+    return *reinterpret_cast<const float4 *>(e.resid + (size_t)m * e.ldo + n);
+}
+// Residual epilogue that also prepares the next LayerNorm.  Warp-collective: the 32 lanes are converged on
+// one token row m, lane l holding features n..n+3 (n = 128 * tile + 4 l); v = the finished values (bias
+// included), r = epi_resid_old4, ng = next_g[n..n+3].  N and ldo are multiples of 4 (the model width).
+__device__ __forceinline__ void epi_resid_ln4(const Epilogue &e, int m, int n, float4 v, float4 r, float4 ng, int N) {
+    float s1 = 0.0f, s2 = 0.0f;
+    if (n < N) {
+        const size_t i = (size_t)m * e.ldo + n;
+        r.x += v.x; r.y += v.y; r.z += v.z; r.w += v.w;
+        *reinterpret_cast<float4 *>(e.resid + i) = r;
+        __half2 lo = __floats2half2_rn(r.x * ng.x, r.y * ng.y), hi = __floats2half2_rn(r.z * ng.z, r.w * ng.w);
+        *reinterpret_cast<uint2 *>(e.xg_out + i) = make_uint2(*reinterpret_cast<uint32_t *>(&lo), *reinterpret_cast<uint32_t *>(&hi));
+        s1 = (r.x + r.y) + (r.z + r.w);
+        s2 = (r.x * r.x + r.y * r.y) + (r.z * r.z + r.w * r.w);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    }
+    if ((threadIdx.x & 31) == 0)
+        *reinterpret_cast<float2 *>(e.stats_out + ((size_t)m * e.stats_nt + (n >> 7)) * 2) = make_float2(s1, s2);
+}
+// One finished row of a 128-feature tile leaves the GEMM (warp-collective as above): acc = the complete
+// sums of products, f4 = epi_fold4, mr = the row's (mean, rstd) when ln_stats is set, r = epi_resid_old4.
+__device__ __forceinline__ void epi_emit4(const Epilogue &e2, const Epilogue &epi, int m, int n, float4 acc, float4 f4,
+                                          float4 b4, float2 mr, float4 r, int N) {
+    const float4 v = epi_finish4(epi, acc, f4, b4, mr);
+    if (epi.mode == EPI_RESID_LN) {
+        epi_resid_ln4(epi, m, n, v, r, f4, N);
+    } else {
+        epi_store4(e2, m, n, v, N);
+        if (epi.amax_val) epi_argmax4(epi, m, n, v, N);
+    }
 }
 
 // Same, from a raw accumulated dot product.

@@ -18,6 +18,28 @@
 // SimpleRng (gpt2.rs:1000-1023) and top_k_sample (gpt2.rs:1029-1058) on host arrays
 // ---------------------------------------------------------------------------------------------
 extern "C" uint64_t b200nn_simple_rng_new(uint64_t seed) { return seed ? seed : 0xDEADBEEFCAFE1234ull; }
+extern "C" float b200nn_simple_rng_next_f32(uint64_t *state);
+
+// Synthetic tensors a Rust caller can regenerate bit for bit with the reference's own SimpleRng:
+// uniforms are next_f32; normals are Box-Muller in f64 on consecutive pairs (u1, u2) of uniforms,
+// z0 = sqrt(-2 ln(1 - u1)) cos(2 pi u2), z1 = sqrt(-2 ln(1 - u1)) sin(2 pi u2), scaled by std and cast
+// to f32 (1 - u1 lies in (0, 1], so the logarithm is finite); an odd count drops the last z1.
+extern "C" int32_t b200nn_simple_rng_fill_uniform(uint64_t *state, size_t n, float *out) {
+    if (!state || (!out && n)) return B200NN_ERR_ARG;
+    for (size_t i = 0; i < n; ++i) out[i] = b200nn_simple_rng_next_f32(state);
+    return B200NN_OK;
+}
+extern "C" int32_t b200nn_simple_rng_fill_normal(uint64_t *state, size_t n, float std_dev, float *out) {
+    if (!state || (!out && n)) return B200NN_ERR_ARG;
+    const double two_pi = 6.283185307179586476925286766559;
+    for (size_t i = 0; i < n; i += 2) {
+        const double u1 = (double)b200nn_simple_rng_next_f32(state), u2 = (double)b200nn_simple_rng_next_f32(state);
+        const double r = sqrt(-2.0 * log(1.0 - u1));
+        out[i] = (float)(r * cos(two_pi * u2) * (double)std_dev);
+        if (i + 1 < n) out[i + 1] = (float)(r * sin(two_pi * u2) * (double)std_dev);
+    }
+    return B200NN_OK;
+}
 
 extern "C" float b200nn_simple_rng_next_f32(uint64_t *state) {
     uint64_t x = *state;

@@ -203,8 +203,11 @@ f16_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             const float4 *stage4 = reinterpret_cast<const float4 *>(stage);
             const int rows = min(MB, M - mt * MB);
             if (splits == 1) {
-                for (int c = w8; c < rows; c += NW)
-                    epi_store4(e2, mt * MB + c, n4, f4_add(stage4[c * 32 + lane], b4), N);
+                for (int c = w8; c < rows; c += NW) {
+                    const float4 v = f4_add(stage4[c * 32 + lane], b4);
+                    epi_store4(e2, mt * MB + c, n4, v, N);
+                    if (epi.amax_val) epi_argmax4(epi, mt * MB + c, n4, v, N);
+                }
             } else if (epi.mode == EPI_RESID) {
                 // every split adds its partial tile into the f32 residual stream with vector
                 // reductions at L2; the bias goes in with split 0.  The order of the additions is not
@@ -232,6 +235,7 @@ f16_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 for (int sp = 0; sp < splits; ++sp)
                     sum = f4_add(sum, cluster.map_shared_rank(stage4, sp)[c * 32 + lane]);
                 epi_store4(e2, mt * MB + c, n4, sum, N);
+                if (epi.amax_val) epi_argmax4(epi, mt * MB + c, n4, sum, N);
             }
         }
         cluster.sync(); // no block leaves while its shared memory may still be read
@@ -426,8 +430,11 @@ f16_gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
                     for (int c = w8; c < lim; c += NW)
                         epi_resid_red4(epi, mt * MB + c0 + c, n4, f4_add(stage4[c * 32 + lane], b4), N);
                 } else {
-                    for (int c = w8; c < lim; c += NW)
-                        epi_store4(e2, mt * MB + c0 + c, n4, f4_add(stage4[c * 32 + lane], b4), N);
+                    for (int c = w8; c < lim; c += NW) {
+                        const float4 v = f4_add(stage4[c * 32 + lane], b4);
+                        epi_store4(e2, mt * MB + c0 + c, n4, v, N);
+                        if (epi.amax_val) epi_argmax4(epi, mt * MB + c0 + c, n4, v, N);
+                    }
                 }
                 bar_sync_epi<EPI>(); // the stage is free for the next pass
             }

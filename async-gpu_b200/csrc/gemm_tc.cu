@@ -71,6 +71,7 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
 #else
 #define TRACE(slot) do { } while (0)
 #endif
+#define ROWSTAT(c) (epi.ln_stats ? rowstat[c] : make_float2(0.f, 0.f))
     constexpr int X_BYTES = MB * 128;
     constexpr int DQ = 128 * NG; // dequant / epilogue threads
     static_assert(MB + NS * A_COLS <= TC, "TMEM budget exceeded");
@@ -84,6 +85,7 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
     extern __shared__ uint8_t smem_raw[];
     __shared__ int abort_flag;
     __shared__ int is_last;
+    __shared__ float2 rowstat[MB]; // (mean, rstd) of the tile's token rows when a LayerNorm is folded in
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nt = blockIdx.x, split = blockIdx.y, splits = gridDim.y, mt = blockIdx.z;
@@ -134,7 +136,7 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
     // the epilogue's per-thread constants (filled by the epilogue warps, used in both of its places):
     // lane l owns features 4l..4l+3 of a token row
     const int n4 = nt * TILE_N + lane * 4;
-    float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f), g4 = b4;
     Epilogue e2 = epi; // the device-side position is read once per thread, not once per element
     e2.pos_ptr = nullptr;
 
@@ -250,6 +252,9 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
         pdl_wait(); // the epilogue touches buffers the previous kernel may still be using
         // bias and the device-side position are fetched now, under the wait for the last MMAs
         b4 = epi_bias4(epi, n4, N);
+        g4 = epi_fold4(epi, n4, N);
+        // folded LayerNorm: one thread per token row adds up the row's partial sums (the barrier below publishes them)
+        if (epi.ln_stats && t < MB && mt * MB + t < M) rowstat[t] = epi_row_mean_rstd(epi, mt * MB + t);
         if (epi.mode == EPI_QKV && epi.pos_ptr) e2.pos_off = epi.pos_off + *epi.pos_ptr;
         bar_sync_dequant<DQ>();
         if (!abort_flag) tc::mbar_wait(S.acc_full, 0, &abort_flag, dev_err, ERR_ACC);
@@ -284,7 +289,8 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
             const int rows = min(MB, M - mt * MB);
             if (splits == 1) {
                 for (int c = w8; c < rows; c += NW)
-                    epi_store4(e2, mt * MB + c, n4, f4_add(stage4[c * 32 + lane], b4), N);
+                    epi_emit4(e2, epi, mt * MB + c, n4, stage4[c * 32 + lane], g4, b4, ROWSTAT(c),
+                              epi_resid_old4(epi, mt * MB + c, n4, N), N);
             } else if (epi.mode == EPI_RESID) {
                 // residual epilogue with split K: every split adds its partial tile straight into the
                 // f32 residual stream with vector reductions at L2 (no scratch, no second pass); the
@@ -313,7 +319,8 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
                     // the last block to arrive sums the partial tiles in split order
                     const float4 *p4 = reinterpret_cast<const float4 *>(scratch + ((size_t)tile_lin * splits * MB) * TILE_N);
                     for (int c = w8; c < rows; c += NW) {
-                        float4 sum = b4;
+                        const float4 r_old = epi_resid_old4(epi, mt * MB + c, n4, N);
+                        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
                         int sp = 0;
                         for (; sp + 4 <= splits; sp += 4) { // four independent 512-byte row reads in flight
                             float4 t0 = __ldcg(p4 + ((size_t)(sp + 0) * MB + c) * 32 + lane);
@@ -323,7 +330,7 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
                             sum = f4_add(f4_add(f4_add(f4_add(sum, t0), t1), t2), t3);
                         }
                         for (; sp < splits; ++sp) sum = f4_add(sum, __ldcg(p4 + ((size_t)sp * MB + c) * 32 + lane));
-                        epi_store4(e2, mt * MB + c, n4, sum, N);
+                        epi_emit4(e2, epi, mt * MB + c, n4, sum, g4, b4, ROWSTAT(c), r_old, N);
                     }
                 }
             }
@@ -343,10 +350,11 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
             const float4 *stage4 = reinterpret_cast<const float4 *>(gen_base);
             const int rows = min(MB, M - mt * MB);
             for (int c = split + splits * w8; c < rows; c += splits * NW) {
-                float4 sum = b4;
+                const float4 r_old = epi_resid_old4(epi, mt * MB + c, n4, N); // in flight under the partial rows' reads
+                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
                 for (int sp = 0; sp < splits; ++sp)
                     sum = f4_add(sum, cluster.map_shared_rank(stage4, sp)[c * 32 + lane]);
-                epi_store4(e2, mt * MB + c, n4, sum, N);
+                epi_emit4(e2, epi, mt * MB + c, n4, sum, g4, b4, ROWSTAT(c), r_old, N);
             }
         }
         cluster.sync(); // no block leaves while its shared memory may still be read
@@ -360,6 +368,7 @@ int4_gemm_tc_kernel(const uint8_t *__restrict__ tiles, const __half *__restrict_
     __syncthreads();
     if (warp == 2) tc::tmem_dealloc(tmem_base, TC);
 #undef TRACE
+#undef ROWSTAT
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,

@@ -121,14 +121,15 @@ int4_gemv_kernel(const uint4 *__restrict__ tiles, const __half *__restrict__ sca
         }
     }
     cluster.sync(); // every block's partial tile is in its shared memory
-    if (cluster.block_rank() == 0 && slice == 0 && n < N) {
+    if (cluster.block_rank() == 0 && slice == 0) { // warps 0..3: 32 consecutive features each
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             if (m >= m_valid) break;
             float t = 0.0f;
             for (int sp = 0; sp < splits; ++sp) // fixed order: the result does not depend on timing
                 t += cluster.map_shared_rank(part, sp)[m * 128 + r];
-            epi_apply(epi, m0 + m, n, t);
+            if (n < N) epi_apply(epi, m0 + m, n, t);
+            if (epi.amax_val) epi_argmax1(epi, m0 + m, n, t + (epi.bias && n < N ? epi.bias[n] : 0.0f), n < N);
         }
     }
     cluster.sync(); // no block leaves while its shared memory may still be read
@@ -232,12 +233,22 @@ static int gemv_all(b200nn_ctx *ctx, const Int4Weight &w, const XT *x, int M, co
 
 int launch_int4_gemv(b200nn_ctx *ctx, const Int4Weight &w, const void *x, bool x_half, int M, const Epilogue &epi) {
     if (M <= 0) return B200NN_OK;
+    if (epi.ln_stats || epi.mode == EPI_RESID_LN) { // folded LayerNorms exist in the tensor-core GEMM's epilogue only
+        if (!(w.fast && M > ctx->gemv_max_rows && x_half && int4_gemm_tc_supported(w, M)) || int4_via_f16_supported(ctx, w, M))
+            return set_error(ctx, B200NN_ERR_UNSUPPORTED, "folded LayerNorm: this Linear does not run on the tensor-core GEMM");
+        return launch_int4_gemm_tc(ctx, w, (const __half *)x, M, epi);
+    }
     if (!w.fast) return launch_int4_naive(ctx, w, x, x_half, M, epi);
     return x_half ? gemv_all<__half>(ctx, w, (const __half *)x, M, epi) : gemv_all<float>(ctx, w, (const float *)x, M, epi);
 }
 
 int launch_int4_linear(b200nn_ctx *ctx, const Int4Weight &w, const void *x, bool x_half, int M, const Epilogue &epi) {
     if (M <= 0) return B200NN_OK;
+    if (epi.ln_stats || epi.mode == EPI_RESID_LN) { // folded LayerNorms exist in the tensor-core GEMM's epilogue only
+        if (!(w.fast && M > ctx->gemv_max_rows && x_half && int4_gemm_tc_supported(w, M)) || int4_via_f16_supported(ctx, w, M))
+            return set_error(ctx, B200NN_ERR_UNSUPPORTED, "folded LayerNorm: this Linear does not run on the tensor-core GEMM");
+        return launch_int4_gemm_tc(ctx, w, (const __half *)x, M, epi);
+    }
     if (!w.fast) return launch_int4_naive(ctx, w, x, x_half, M, epi);
     // a prefill pass with at least two 256-row tiles per SM: dequantise once, persistent fp16 GEMM
     if (x_half && !((uintptr_t)x & 15) && int4_via_f16_supported(ctx, w, M))

@@ -119,6 +119,47 @@ int launch_embedding(b200nn_ctx *ctx, const uint32_t *ids, const float *wte, con
     return B200NN_OK;
 }
 
+// The decode-step embedding when the first LayerNorm is folded into the q/k/v GEMM (see Epilogue): one
+// row per block at position *pos_ptr.
+__global__ void __launch_bounds__(256) embedding_ln_kernel(const uint32_t *__restrict__ ids, const float *__restrict__ wte,
+                                                           const float *__restrict__ wpe, int d, const int *pos_ptr, int vocab,
+                                                           int n_positions, float *__restrict__ out,
+                                                           const float *__restrict__ g, __half *__restrict__ xg,
+                                                           float *__restrict__ stats, int stats_nt) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    uint32_t tok = ids[r];
+    if (tok >= (uint32_t)vocab) tok = vocab - 1;
+    int pos = *pos_ptr;
+    if (pos >= n_positions) pos = n_positions - 1;
+    const float *a = wte + (size_t)tok * d, *b = wpe + (size_t)pos * d;
+    float s1 = 0.0f, s2 = 0.0f;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        const float v = a[j] + b[j];
+        out[(size_t)r * d + j] = v;
+        xg[(size_t)r * d + j] = __float2half_rn(v * g[j]);
+        s1 += v;
+        s2 += v * v;
+    }
+    s1 = block_sum(s1, red);
+    s2 = block_sum(s2, red);
+    for (int t = threadIdx.x; t < stats_nt; t += blockDim.x)
+        reinterpret_cast<float2 *>(stats)[(size_t)r * stats_nt + t] = t == 0 ? make_float2(s1, s2) : make_float2(0.f, 0.f);
+}
+
+int launch_embedding_ln(b200nn_ctx *ctx, const uint32_t *ids, const float *wte, const float *wpe, int n_rows, int d,
+                        const int *pos_ptr, int vocab, int n_positions, float *out, const float *g, __half *xg,
+                        float *stats, int stats_nt) {
+    if (n_rows <= 0) return B200NN_OK;
+    PREFER_SMEM_ONCE(embedding_ln_kernel);
+    launch_pdl(ctx, embedding_ln_kernel, dim3(n_rows), dim3(256), 0, ids, wte, wpe, d, pos_ptr, vocab, n_positions, out, g, xg,
+               stats, stats_nt);
+    CK_LAUNCH(ctx, "embedding_ln_kernel");
+    return B200NN_OK;
+}
+
 // ---------------------------------------------------------------------------------------------
 // element-wise ops (ops/activation.rs, ops/reshape.rs:112-186)
 // ---------------------------------------------------------------------------------------------
@@ -316,6 +357,51 @@ int launch_argmax(b200nn_ctx *ctx, const float *logits, int rows, int vocab, int
     PREFER_SMEM_ONCE(argmax_kernel);
     launch_pdl(ctx, argmax_kernel, dim3(rows), dim3(1024), 0, logits, vocab, ld, keep_last ? 1 : 0, tok_out);
     CK_LAUNCH(ctx, "argmax_kernel");
+    return B200NN_OK;
+}
+
+// Second stage of the greedy pick fused into the LM head's epilogue: the (value, index) entries of a
+// row, one per 32 features, reduced with the same tie rule as argmax_kernel (same token, bit for bit:
+// a maximum does not depend on the order it is taken in).
+__global__ void __launch_bounds__(256) argmax_entries_kernel(const float *__restrict__ val, const int *__restrict__ idx,
+                                                            int n_entries, int vocab, int keep_last,
+                                                            uint32_t *__restrict__ tok_out) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    pdl_trigger();
+    pdl_wait();
+    const float *rv = val + (size_t)blockIdx.x * n_entries;
+    const int *ri = idx + (size_t)blockIdx.x * n_entries;
+    float best = -INFINITY;
+    int bi = keep_last ? -1 : 0x7fffffff;
+    for (int j = threadIdx.x; j < n_entries; j += blockDim.x) amax_merge(best, bi, rv[j], ri[j], keep_last);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        amax_merge(best, bi, ov, oi, keep_last);
+    }
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    if (lane == 0) { sv[w] = best; si[w] = bi; }
+    __syncthreads();
+    if (w == 0) {
+        best = lane < 8 ? sv[lane] : -INFINITY;
+        bi = lane < 8 ? si[lane] : (keep_last ? -1 : 0x7fffffff);
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            amax_merge(best, bi, ov, oi, keep_last);
+        }
+        if (lane == 0) tok_out[blockIdx.x] = (bi < 0 || bi >= vocab) ? 0u : (uint32_t)bi;
+    }
+}
+int launch_argmax_entries(b200nn_ctx *ctx, const float *val, const int *idx, int rows, int n_entries, int vocab,
+                          bool keep_last, uint32_t *tok_out) {
+    if (rows <= 0) return B200NN_OK;
+    PREFER_SMEM_ONCE(argmax_entries_kernel);
+    launch_pdl(ctx, argmax_entries_kernel, dim3(rows), dim3(256), 0, val, idx, n_entries, vocab, keep_last ? 1 : 0, tok_out);
+    CK_LAUNCH(ctx, "argmax_entries_kernel");
     return B200NN_OK;
 }
 

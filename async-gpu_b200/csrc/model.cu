@@ -7,7 +7,7 @@
 #include "model.h"
 
 int linear_forward(b200nn_ctx *ctx, const LinearAny &l, const void *x, bool x_half, int M, Epilogue epi) {
-    epi.bias = l.bias();
+    if (!epi.ln_stats) epi.bias = l.bias(); // a folded LayerNorm brings its own combined bias
     if (l.int4) return launch_int4_linear(ctx, l.q, x, x_half, M, epi);
     return launch_f32_linear(ctx, l.f, x, x_half, M, epi);
 }
@@ -160,6 +160,9 @@ int workspace_alloc(b200nn_gpt2 *m, size_t rows, size_t logit_rows, Workspace *w
     TRY(dev_alloc(ctx, logit_rows * V * 4, &ws->logits));
     TRY(dev_alloc(ctx, rows * 4, &ws->ids));
     TRY(dev_alloc(ctx, std::max(rows, logit_rows) * 4, &ws->tok));
+    ws->amax_entries = (int)((V + 127) / 128) * 4; // one entry per 32 features of the padded width
+    TRY(dev_alloc(ctx, std::max<size_t>(1, logit_rows) * ws->amax_entries * 4, &ws->amax_val));
+    TRY(dev_alloc(ctx, std::max<size_t>(1, logit_rows) * ws->amax_entries * 4, &ws->amax_idx));
     return B200NN_OK;
 }
 
@@ -185,7 +188,50 @@ static inline void prof_mark(b200nn_ctx *ctx, StepProfile *p, int fam) {
 
 // The seven launches of one transformer block, each on its own so that the forward pass (all of them,
 // in order) and the per-family timing routine (one family at a time) issue exactly the same launches.
+bool model_ln_fold_supported(const b200nn_gpt2 *m, int rows) {
+    const int d = m->cfg.n_embd;
+    if (!m->int4 || !m->ctx->ln_fold || rows <= m->ctx->gemv_max_rows || d % 8 != 0 || (d + TILE_N - 1) / TILE_N > 32) return false;
+    if (!model_act_half(m, rows)) return false;
+    const BlockW &b = m->blocks[0];
+    for (const LinearAny *l : {&b.qkv, &b.proj, &b.fc, &b.fcproj})
+        if (!l->q.fast || int4_via_f16_supported(m->ctx, l->q, rows)) return false;
+    return true;
+}
+
+int model_prepare_ln_fold(b200nn_gpt2 *m, Workspace *ws) {
+    b200nn_ctx *ctx = m->ctx;
+    if (!m->ln_fold_ready) {
+        for (BlockW &b : m->blocks) {
+            TRY(int4_weight_ln_fold(ctx, b.qkv.q, (const float *)b.ln1_g->p, (const float *)b.ln1_b->p, &b.qkv_gsum, &b.qkv_bc));
+            TRY(int4_weight_ln_fold(ctx, b.fc.q, (const float *)b.ln2_g->p, (const float *)b.ln2_b->p, &b.fc_gsum, &b.fc_bc));
+        }
+        m->ln_fold_ready = true;
+    }
+    ws->ln_nt = (m->cfg.n_embd + TILE_N - 1) / TILE_N;
+    return dev_alloc(ctx, (size_t)2 * m->cfg.n_layer * ws->rows * ws->ln_nt * 2 * sizeof(float), &ws->ln_stats);
+}
+
+// The consumer side of a folded LayerNorm: statistics slot, weighted column sums and combined bias.
+static void fold_consumer(const b200nn_gpt2 *m, const Workspace &ws, int slot, const std::shared_ptr<DevBuf> &gsum,
+                          const std::shared_ptr<DevBuf> &bc, Epilogue *e) {
+    e->ln_stats = ws.ln_slot(slot);
+    e->ln_nt = ws.ln_nt;
+    e->ln_gsum = (const float *)gsum->p;
+    e->bias = (const float *)bc->p;
+    e->ln_eps = m->cfg.layer_norm_epsilon;
+    e->ln_inv_d = 1.0f / (float)m->cfg.n_embd;
+}
+// The producer side: the residual GEMM also writes what the LayerNorm `slot` (scale next_g) will need.
+static void fold_producer(const Workspace &ws, int slot, const std::shared_ptr<DevBuf> &next_g, Epilogue *e) {
+    e->mode = EPI_RESID_LN;
+    e->xg_out = (__half *)ws.ln->p;
+    e->next_g = (const float *)next_g->p;
+    e->stats_out = ws.ln_slot(slot);
+    e->stats_nt = ws.ln_nt;
+}
+
 int BlockLaunch::ln1() const {
+    if (fold) return B200NN_OK;
     const BlockW &b = m->blocks[l];
     return launch_layernorm(m->ctx, (const float *)ws.x->p, nullptr, nullptr, (const float *)b.ln1_g->p, (const float *)b.ln1_b->p,
                             m->cfg.layer_norm_epsilon, B * S, m->cfg.n_embd, ws.ln->p, act_half);
@@ -205,6 +251,7 @@ int BlockLaunch::qkv() const {
     e.cap = (int)kv.cap;
     e.pos_ptr = pos_ptr;
     e.pos_off = pos_off;
+    if (fold) fold_consumer(m, ws, 2 * l, m->blocks[l].qkv_gsum, m->blocks[l].qkv_bc, &e);
     return linear_forward(m->ctx, m->blocks[l].qkv, ws.ln->p, act_half, B * S, e);
 }
 int BlockLaunch::attention() const {
@@ -220,9 +267,11 @@ int BlockLaunch::proj() const {
     r.mode = EPI_RESID;
     r.resid = (float *)ws.x->p;
     r.ldo = m->cfg.n_embd;
+    if (fold) fold_producer(ws, 2 * l + 1, m->blocks[l].ln2_g, &r);
     return linear_forward(m->ctx, m->blocks[l].proj, ws.att->p, act_half, B * S, r);
 }
 int BlockLaunch::ln2() const {
+    if (fold) return B200NN_OK;
     const BlockW &b = m->blocks[l];
     return launch_layernorm(m->ctx, (const float *)ws.x->p, nullptr, nullptr, (const float *)b.ln2_g->p, (const float *)b.ln2_b->p,
                             m->cfg.layer_norm_epsilon, B * S, m->cfg.n_embd, ws.ln->p, act_half);
@@ -234,6 +283,7 @@ int BlockLaunch::fc() const {
     f.out = ws.fc->p;
     f.ldo = 4 * m->cfg.n_embd;
     f.out_half = act_half;
+    if (fold) fold_consumer(m, ws, 2 * l + 1, m->blocks[l].fc_gsum, m->blocks[l].fc_bc, &f);
     return linear_forward(m->ctx, m->blocks[l].fc, ws.ln->p, act_half, B * S, f);
 }
 int BlockLaunch::fcproj() const {
@@ -241,19 +291,21 @@ int BlockLaunch::fcproj() const {
     r.mode = EPI_RESID;
     r.resid = (float *)ws.x->p;
     r.ldo = m->cfg.n_embd;
+    // the last block's output goes to the final LayerNorm, which runs as a kernel of its own
+    if (fold && l + 1 < m->cfg.n_layer) fold_producer(ws, 2 * l + 2, m->blocks[l + 1].ln1_g, &r);
     return linear_forward(m->ctx, m->blocks[l].fcproj, ws.fc->p, act_half, B * S, r);
 }
 
 int run_blocks(b200nn_gpt2 *m, Workspace &ws, b200nn_kvcache &kv, int B, int S, const int *pos_ptr, int pos_off,
-               bool act_half, StepProfile *prof) {
-    return run_blocks_range(m, ws, kv, B, S, pos_ptr, pos_off, act_half, prof, 0, m->cfg.n_layer);
+               bool act_half, StepProfile *prof, bool fold) {
+    return run_blocks_range(m, ws, kv, B, S, pos_ptr, pos_off, act_half, prof, 0, m->cfg.n_layer, fold);
 }
 
 int run_blocks_range(b200nn_gpt2 *m, Workspace &ws, b200nn_kvcache &kv, int B, int S, const int *pos_ptr, int pos_off,
-                     bool act_half, StepProfile *prof, int layer_begin, int layer_end) {
+                     bool act_half, StepProfile *prof, int layer_begin, int layer_end, bool fold) {
     b200nn_ctx *ctx = m->ctx;
     for (int l = layer_begin; l < layer_end; ++l) {
-        const BlockLaunch bl{m, ws, kv, l, B, S, pos_ptr, pos_off, act_half};
+        const BlockLaunch bl{m, ws, kv, l, B, S, pos_ptr, pos_off, act_half, fold};
         TRY(bl.ln1());
         prof_mark(ctx, prof, B200NN_PROF_LAYERNORM);
         TRY(bl.qkv());
@@ -296,4 +348,37 @@ int run_head(b200nn_gpt2 *m, Workspace &ws, const float *x, int rows, bool act_h
     TRY(launch_head_linear(m, ws, rows, head_half));
     prof_mark(ctx, prof, B200NN_PROF_LM_HEAD);
     return B200NN_OK;
+}
+
+// Which LM-head launches take the greedy pick in their epilogue: the tensor-core GEMMs and the two
+// GEMV kernels of an int4 head in the tiled layout, and the fp16 tensor-core GEMM of an f32 head.
+static bool head_fuses_pick(const b200nn_gpt2 *m, int rows, bool head_half) {
+    if (m->lm_head.int4) return m->lm_head.q.fast && rows < 2048;
+    return head_half && f16_gemm_tc_supported(m->ctx, m->lm_head.f, rows);
+}
+
+int run_head_pick(b200nn_gpt2 *m, Workspace &ws, const float *x, int rows, bool act_half, bool keep_last, bool tokens_only,
+                  uint32_t *tok_out, StepProfile *prof) {
+    b200nn_ctx *ctx = m->ctx;
+    const int V = m->cfg.vocab_size;
+    const bool head_half = head_act_half(m, rows, act_half);
+    TRY(launch_head_norm(m, ws, x, rows, head_half));
+    prof_mark(ctx, prof, B200NN_PROF_LAYERNORM);
+    if (!ctx->fused_argmax || !head_fuses_pick(m, rows, head_half)) {
+        TRY(launch_head_linear(m, ws, rows, head_half));
+        prof_mark(ctx, prof, B200NN_PROF_LM_HEAD);
+        return launch_argmax(ctx, (const float *)ws.logits->p, rows, V, V, keep_last, tok_out);
+    }
+    Epilogue e;
+    e.mode = EPI_STORE;
+    e.out = ws.logits->p;
+    e.ldo = V;
+    e.no_store = tokens_only ? 1 : 0;
+    e.amax_val = (float *)ws.amax_val->p;
+    e.amax_idx = (int *)ws.amax_idx->p;
+    e.amax_entries = ws.amax_entries;
+    e.amax_keep_last = keep_last ? 1 : 0;
+    TRY(linear_forward(ctx, m->lm_head, ws.last_ln->p, head_half, rows, e));
+    prof_mark(ctx, prof, B200NN_PROF_LM_HEAD);
+    return launch_argmax_entries(ctx, e.amax_val, e.amax_idx, rows, e.amax_entries, V, keep_last, tok_out);
 }

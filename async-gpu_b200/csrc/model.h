@@ -48,6 +48,9 @@ struct b200nn_attention {
 struct BlockW {
     std::shared_ptr<DevBuf> ln1_g, ln1_b, ln2_g, ln2_b;
     LinearAny qkv, proj, fc, fcproj;
+    // ln_1 folded into the q/k/v Linear and ln_2 into the MLP's first Linear (int4_weight_ln_fold);
+    // built by model_prepare_ln_fold on first use
+    std::shared_ptr<DevBuf> qkv_gsum, qkv_bc, fc_gsum, fc_bc;
 };
 
 struct b200nn_gpt2 {
@@ -59,6 +62,7 @@ struct b200nn_gpt2 {
     std::shared_ptr<DevBuf> wte, wpe, lnf_g, lnf_b;
     std::vector<BlockW> blocks;
     LinearAny lm_head;
+    bool ln_fold_ready = false;
     int act() const { return (flags & B200NN_GELU_SIGMOID) ? B200NN_ACT_GELU_SIGMOID : B200NN_ACT_GELU_TANH; }
 };
 
@@ -75,6 +79,13 @@ struct b200nn_kvcache {
 struct Workspace {
     size_t rows = 0, logit_rows = 0;
     std::shared_ptr<DevBuf> x, ln, q, att, fc, last_x, last_ln, logits, ids, tok;
+    std::shared_ptr<DevBuf> amax_val, amax_idx; // [logit_rows][entries]: partial greedy picks of the LM head's epilogue
+    int amax_entries = 0;
+    // folded LayerNorms: f32 [2 * n_layer][rows][ln_nt][2] partial (sum, sum of squares) of every row of the
+    // residual stream as it enters each LayerNorm (absent unless the workspace serves folded decode steps)
+    std::shared_ptr<DevBuf> ln_stats;
+    int ln_nt = 0;
+    float *ln_slot(int i) const { return static_cast<float *>(ln_stats->p) + (size_t)i * rows * ln_nt * 2; }
 };
 int workspace_alloc(b200nn_gpt2 *m, size_t rows, size_t logit_rows, Workspace *ws);
 
@@ -86,10 +97,15 @@ struct StepProfile {
 // Runs the transformer blocks over T = B*S rows already embedded in ws.x.  Row t belongs to
 // sequence t/S at position pos(t) = *pos_ptr + pos_off + t%S; K and V go straight into `kv`.
 int run_blocks(b200nn_gpt2 *m, Workspace &ws, b200nn_kvcache &kv, int B, int S, const int *pos_ptr, int pos_off,
-               bool act_half, StepProfile *prof);
+               bool act_half, StepProfile *prof, bool fold = false);
+// Whether decode steps over `rows` rows can run with the block LayerNorms folded into the GEMMs (int4
+// weights in the tiled layout, every Linear on the tensor-core GEMM), and the one-time preparation of the
+// per-Linear vectors and the workspace's statistics buffer.
+bool model_ln_fold_supported(const b200nn_gpt2 *m, int rows);
+int model_prepare_ln_fold(b200nn_gpt2 *m, Workspace *ws);
 // The same for blocks [layer_begin, layer_end) only (data-dependent depth: early exit).
 int run_blocks_range(b200nn_gpt2 *m, Workspace &ws, b200nn_kvcache &kv, int B, int S, const int *pos_ptr, int pos_off,
-                     bool act_half, StepProfile *prof, int layer_begin, int layer_end);
+                     bool act_half, StepProfile *prof, int layer_begin, int layer_end, bool fold = false);
 // The launches of transformer block `l` over B*S rows (arguments as run_blocks), one at a time.
 struct BlockLaunch {
     b200nn_gpt2 *m;
@@ -99,11 +115,17 @@ struct BlockLaunch {
     const int *pos_ptr;
     int pos_off;
     bool act_half;
+    bool fold = false; // block LayerNorms folded into the GEMMs around them: ln1() and ln2() launch nothing
     int ln1() const, qkv() const, attention() const, proj() const, ln2() const, fc() const, fcproj() const;
 };
 bool head_act_half(const b200nn_gpt2 *m, int rows, bool act_half);
 int launch_head_norm(b200nn_gpt2 *m, Workspace &ws, const float *x, int rows, bool head_half);
 int launch_head_linear(b200nn_gpt2 *m, Workspace &ws, int rows, bool head_half);
+// Final LayerNorm + LM head + greedy pick of every row -> tok_out [rows] (and ws.logits unless
+// tokens_only): the pick is taken in the LM head's epilogue when the kernel that runs it supports that,
+// else by argmax_kernel over the logits.
+int run_head_pick(b200nn_gpt2 *m, Workspace &ws, const float *x, int rows, bool act_half, bool keep_last, bool tokens_only,
+                  uint32_t *tok_out, StepProfile *prof);
 // Final LayerNorm + LM head over `rows` rows of `x` -> ws.logits [rows, vocab].
 int run_head(b200nn_gpt2 *m, Workspace &ws, const float *x, int rows, bool act_half, StepProfile *prof);
 bool model_act_half(const b200nn_gpt2 *m, int rows);

@@ -275,6 +275,45 @@ int int4_weight_upload(b200nn_ctx *ctx, const uint32_t *packed, const float *sca
     return B200NN_OK;
 }
 
+int int4_weight_ln_fold(b200nn_ctx *ctx, const Int4Weight &w, const float *g_dev, const float *beta_dev,
+                        std::shared_ptr<DevBuf> *gsum, std::shared_ptr<DevBuf> *bc) {
+    const size_t K = w.K, N = w.N, group = w.group;
+    std::vector<float> g(K), beta(K), bias(N, 0.0f);
+    CK(ctx, cudaMemcpy(g.data(), g_dev, K * 4, cudaMemcpyDeviceToHost));
+    CK(ctx, cudaMemcpy(beta.data(), beta_dev, K * 4, cudaMemcpyDeviceToHost));
+    if (w.bias) CK(ctx, cudaMemcpy(bias.data(), w.bias->p, N * 4, cudaMemcpyDeviceToHost));
+    std::vector<float> gs(N), cs(N);
+    const uint32_t *hp = w.host_packed.data();
+    const float *hs = w.host_scales.data(); // already fp16 values
+    const float *gp = g.data(), *bp = beta.data(), *biasp = bias.data();
+    float *gsp = gs.data(), *csp = cs.data();
+    parallel_for(N, [=](size_t n0, size_t n1) {
+        const size_t cnt = n1 - n0;
+        std::vector<double> ag(cnt, 0.0), ab(cnt, 0.0);
+        for (size_t kp = 0; kp < K / 8; ++kp) {
+            const float *sc = hs + ((kp * 8) / group) * N;
+            for (size_t n = n0; n < n1; ++n) {
+                const uint32_t word = hp[kp * N + n];
+                double sg = 0.0, sb = 0.0;
+                for (unsigned bit = 0; bit < 8; ++bit) {
+                    const float wv = host_f16_round((float)((int)((word >> (4 * bit)) & 0xFu) - 8) * sc[n]);
+                    sg += (double)gp[kp * 8 + bit] * wv;
+                    sb += (double)bp[kp * 8 + bit] * wv;
+                }
+                ag[n - n0] += sg;
+                ab[n - n0] += sb;
+            }
+        }
+        for (size_t n = n0; n < n1; ++n) {
+            gsp[n] = (float)ag[n - n0];
+            csp[n] = (float)(ab[n - n0] + (double)biasp[n]);
+        }
+    });
+    TRY(upload(ctx, gs.data(), N * 4, gsum));
+    TRY(upload(ctx, cs.data(), N * 4, bc));
+    return B200NN_OK;
+}
+
 int f32_weight_upload(b200nn_ctx *ctx, const float *wsrc, bool is_out_in, const float *bias, size_t K, size_t N,
                       F32Weight *w) {
     if (K == 0 || N == 0) return set_error(ctx, B200NN_ERR_SHAPE, "Linear: empty weight");

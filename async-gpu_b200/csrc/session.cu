@@ -133,6 +133,7 @@ extern "C" int32_t b200nn_session_create(b200nn_gpt2 *m, size_t batch, size_t ca
     CK(ctx, cudaMemsetAsync(s->counters->p, 0, 2 * sizeof(int), ctx->stream));
     TRY(dev_alloc(ctx, batch * s->hist_cap * 4, &s->history));
     CK(ctx, cudaMemsetAsync(s->history->p, 0, batch * s->hist_cap * 4, ctx->stream));
+    if (model_ln_fold_supported(m, (int)batch)) TRY(model_prepare_ln_fold(m, &s->ws_step));
     if (decode_persistent_supported(m, (int)batch)) {
         TRY(decode_persistent_prepare(s.get()));
         s->persist = true;
@@ -194,9 +195,8 @@ extern "C" int32_t b200nn_session_prefill(b200nn_session *s, const uint32_t *pro
     }
     s->kv.len = prompt_len;
     bool ah = model_act_half(m, (int)s->batch);
-    TRY(run_head(m, s->ws_step, last_x, (int)s->batch, ah, nullptr));
-    TRY(launch_argmax(ctx, (const float *)s->ws_step.logits->p, (int)s->batch, m->cfg.vocab_size, m->cfg.vocab_size,
-                      (s->flags & B200NN_ARGMAX_LAST) != 0, (uint32_t *)s->ws_step.tok->p));
+    TRY(run_head_pick(m, s->ws_step, last_x, (int)s->batch, ah, (s->flags & B200NN_ARGMAX_LAST) != 0,
+                      (s->flags & B200NN_TOKENS_ONLY) != 0, (uint32_t *)s->ws_step.tok->p, nullptr));
     TRY(set_counters(s, (int)prompt_len - 1, 0));
     // record: history[0] = first token, step = 1, position = prompt_len
     TRY(launch_record_tokens(ctx, (const uint32_t *)s->ws_step.tok->p, (int)s->batch, (uint32_t *)s->history->p,
@@ -215,8 +215,15 @@ static int decode_step(b200nn_session *s, StepProfile *prof) {
     const int B = (int)s->batch, d = m->cfg.n_embd;
     Workspace &ws = s->ws_step;
     bool ah = model_act_half(m, B);
-    TRY(launch_embedding(ctx, (const uint32_t *)ws.tok->p, (const float *)m->wte->p, (const float *)m->wpe->p, B, d, 1,
-                         s->pos_ptr(), 0, m->cfg.vocab_size, m->cfg.n_positions, (float *)ws.x->p));
+    const bool persistent = s->persist && ctx->persist;
+    const bool fold = !persistent && ws.ln_stats && ctx->ln_fold && model_ln_fold_supported(m, B);
+    if (fold)
+        TRY(launch_embedding_ln(ctx, (const uint32_t *)ws.tok->p, (const float *)m->wte->p, (const float *)m->wpe->p, B, d,
+                                s->pos_ptr(), m->cfg.vocab_size, m->cfg.n_positions, (float *)ws.x->p,
+                                (const float *)m->blocks[0].ln1_g->p, (__half *)ws.ln->p, ws.ln_slot(0), ws.ln_nt));
+    else
+        TRY(launch_embedding(ctx, (const uint32_t *)ws.tok->p, (const float *)m->wte->p, (const float *)m->wpe->p, B, d, 1,
+                             s->pos_ptr(), 0, m->cfg.vocab_size, m->cfg.n_positions, (float *)ws.x->p));
     if (prof) {
         cudaEvent_t e;
         cudaEventCreate(&e);
@@ -224,7 +231,7 @@ static int decode_step(b200nn_session *s, StepProfile *prof) {
         prof->ev.push_back(e);
         prof->fam.push_back(B200NN_PROF_EMBED);
     }
-    if (s->persist && ctx->persist) {
+    if (persistent) {
         // every transformer block in one cooperative launch; with `prof` its phases are timed inside the
         // kernel and the launch as a whole is booked under the attention family's event slot
         if (prof) CK(ctx, cudaMemsetAsync((char *)s->pd_sync->p + 64, 0, 128, ctx->stream));
@@ -237,11 +244,10 @@ static int decode_step(b200nn_session *s, StepProfile *prof) {
             prof->fam.push_back(-1); // split by the in-kernel phase times afterwards
         }
     } else {
-        TRY(run_blocks(m, ws, s->kv, B, 1, s->pos_ptr(), 0, ah, prof));
+        TRY(run_blocks(m, ws, s->kv, B, 1, s->pos_ptr(), 0, ah, prof, fold));
     }
-    TRY(run_head(m, ws, (const float *)ws.x->p, B, ah, prof));
-    TRY(launch_argmax(ctx, (const float *)ws.logits->p, B, m->cfg.vocab_size, m->cfg.vocab_size,
-                      (s->flags & B200NN_ARGMAX_LAST) != 0, (uint32_t *)ws.tok->p));
+    TRY(run_head_pick(m, ws, (const float *)ws.x->p, B, ah, (s->flags & B200NN_ARGMAX_LAST) != 0,
+                      (s->flags & B200NN_TOKENS_ONLY) != 0, (uint32_t *)ws.tok->p, prof));
     TRY(launch_record_tokens(ctx, (const uint32_t *)ws.tok->p, B, (uint32_t *)s->history->p, (int)s->hist_cap,
                              s->step_ptr(), s->pos_ptr()));
     if (prof) {
@@ -335,6 +341,8 @@ extern "C" int32_t b200nn_session_tokens(b200nn_session *s, uint32_t *out, size_
 extern "C" int32_t b200nn_session_logits(b200nn_session *s, float *out) {
     if (!s || !out) return B200NN_ERR_ARG;
     b200nn_ctx *ctx = s->m->ctx;
+    if (s->flags & B200NN_TOKENS_ONLY)
+        return set_error(ctx, B200NN_ERR_UNSUPPORTED, "session_logits: the session was created with B200NN_TOKENS_ONLY");
     CK(ctx, cudaSetDevice(ctx->device));
     CK(ctx, cudaMemcpyAsync(out, s->ws_step.logits->p, s->batch * (size_t)s->m->cfg.vocab_size * 4,
                             cudaMemcpyDeviceToHost, ctx->stream));
@@ -410,6 +418,7 @@ extern "C" int32_t b200nn_session_time_family(b200nn_session *s, int32_t family,
     CK(ctx, cudaSetDevice(ctx->device));
     const int B = (int)s->batch;
     const bool ah = model_act_half(m, B);
+    const bool fold = s->ws_step.ln_stats && ctx->ln_fold && model_ln_fold_supported(m, B); // as decode_step
     cudaEvent_t e0, e1;
     CK(ctx, cudaEventCreate(&e0));
     CK(ctx, cudaEventCreate(&e1));
@@ -420,7 +429,7 @@ extern "C" int32_t b200nn_session_time_family(b200nn_session *s, int32_t family,
     // carries no measurement switches)
     auto one_pass = [&]() -> int {
         for (int l = 0; l < m->cfg.n_layer; ++l) {
-            const BlockLaunch bl{m, s->ws_step, s->kv, l, B, 1, s->pos_ptr(), 0, ah};
+            const BlockLaunch bl{m, s->ws_step, s->kv, l, B, 1, s->pos_ptr(), 0, ah, fold};
             if (family == B200NN_PROF_LAYERNORM) {
                 TRY(bl.ln1());
                 TRY(bl.ln2());
@@ -475,7 +484,7 @@ extern "C" int32_t b200nn_gpt2_generate_batch(b200nn_gpt2 *m, const uint32_t *pr
     }
     if (max_new == 0) return B200NN_OK;
     b200nn_session *s = nullptr;
-    TRY(b200nn_session_create(m, batch, stride, flags, &s));
+    TRY(b200nn_session_create(m, batch, stride, flags | B200NN_TOKENS_ONLY, &s)); // greedy tokens are all that is returned
     std::unique_ptr<b200nn_session, void (*)(b200nn_session *)> guard(s, b200nn_session_destroy);
     TRY(b200nn_session_prefill(s, prompts, prompt_len));
     TRY(b200nn_session_step(s, max_new - 1));

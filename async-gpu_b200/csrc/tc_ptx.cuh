@@ -115,6 +115,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void *tmap,
                  "l"(tmap), "r"(bar), "r"(x), "r"(y)
                  : "memory");
 }
+// 3-D tiled copy through a tensor map (same alignment rule for x).
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const void *tmap, int x, int y, int z, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+                     smem_dst),
+                 "l"(tmap), "r"(bar), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
 // Asks the memory system to bring [gsrc, gsrc+bytes) into L2 (16-byte aligned, size a multiple of
 // 16); nothing is written anywhere and nothing needs to be waited for.
 __device__ __forceinline__ void bulk_prefetch_l2(const void *gsrc, uint32_t bytes) {
@@ -147,12 +154,19 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
     d |= (uint64_t)2 << 61;
     return d;
 }
+// Shared-memory operand, MN-major, 128-byte swizzle, 64 fp16 along M/N: row k of the tile holds the 64
+// M/N values of that k (128 bytes), 8-row groups 1024 bytes apart (stride byte offset); one MMA of
+// K = 16 takes two such groups, so consecutive MMAs start 2048 bytes apart.  The leading byte offset
+// (distance between 64-wide M/N blocks) is not used with a single block.
+__device__ __forceinline__ uint64_t umma_desc_sw128_mn64(uint32_t smem_addr) { return umma_desc_sw128(smem_addr); }
 // Instruction descriptor for kind::f16 with fp16 A and B (both K-major), f32 accumulator:
 // c_format [4,6) = 1 (F32), a_format [7,10) = 0 (F16), b_format [10,13) = 0, a/b major [15],[16] = 0 (K),
 // N>>3 at [17,23), M>>4 at [24,29).
 __host__ __device__ constexpr uint32_t umma_idesc_f16(int M, int N) {
     return (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
+// The same with the B operand MN-major (bit 16): B[k][n] lies with n contiguous in shared memory.
+__host__ __device__ constexpr uint32_t umma_idesc_f16_bmn(int M, int N) { return umma_idesc_f16(M, N) | (1u << 16); }
 // D[tmem] (+)= A[smem] * B[smem]; issued by one thread.
 __device__ __forceinline__ void umma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                             uint32_t accumulate) {

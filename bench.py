@@ -4,7 +4,7 @@
     python bench.py --gpus N --steps K --warmup W            # this library, one rank per GPU
     python bench.py --impl reference --steps K --warmup W    # the reference's CPU path (oracle port)
 
-Workload (BASELINE.json configs[4]): GPT-2 XL, every Linear int4 group-128 (LM head included), fp16
+Workload (the reference benchmark's largest case, its fifth configuration): GPT-2 XL, every Linear int4 group-128 (LM head included), fp16
 KV cache, 256 independent sequences sharded over the ranks (256/N each, no data-path collective),
 prompt of 128 random token ids, greedy decode of 128 tokens.  A "step" is one greedy decode step of
 every sequence of the batch (all layers, LM head, argmax, token fed back on the device) at context
@@ -251,7 +251,7 @@ def int4_linear_isolated(reg, hbm_peak, tf_peak, iters=64):
         for m in (1, 8, 64):
             x = torch.randn(m, k, device="cuda")
             y = torch.empty(m, n, device="cuda")
-            for l in lins[:2]:
+            for l in lins:  # every copy once outside the capture: staging buffers and scratch get their size
                 l.forward_dev(x.data_ptr(), m, y.data_ptr())
             reg.synchronize()
             nbytes = k * n // 2 + ((k + 127) // 128) * n * 2 + m * k * 4 + m * n * 4
@@ -317,7 +317,7 @@ def attention_isolated(reg, hbm_peak, tf_peak):
 
 
 def cpu_reference_form(steps=1):
-    """BASELINE config 1 the way the reference's CPU test runs it (tests_inference.rs:4393-4540): GPT-2
+    """The reference benchmark's first configuration the way the reference's CPU test runs it (tests_inference.rs:4393-4540): GPT-2
     Small, f32 weights, f64 accumulation, greedy decode WITHOUT a KV cache (every step recomputes the
     whole sequence), one thread.  Bounded sample: the 64-token prompt and `steps` generated tokens."""
     from oracle import oracle
@@ -383,7 +383,8 @@ def run_b200(args):
     prompts = np.ascontiguousarray(prompts_all[lo:hi])
 
     capacity = prompt_len + max_new + 8
-    sess = DecodeSession(model, batch, capacity)
+    # greedy decoding needs tokens only: the step's logits stay in the LM head's epilogue
+    sess = DecodeSession(model, batch, capacity, flags=b200nn.TOKENS_ONLY)
     sess.prefill(prompts)
     stream = torch.cuda.ExternalStream(reg.stream, device=torch.device("cuda", local))
     window = max_new  # context goes prompt_len .. prompt_len + window - 1, then wraps
@@ -445,11 +446,11 @@ def run_b200(args):
     sess.rewind(sess.position() - 1)
     # each family alone: its launches of one step, three passes back to back between two CUDA
     # events on the library's stream (the activations are scratch afterwards)
-    fam, fam_launches, reps = {}, {}, 3
+    fam, fam_launches, fam_reps = {}, {}, 3
     for name in ("attention", "linear", "layernorm", "lm_head"):
-        ms_f, n_f = sess.time_family(name, reps)
-        fam[name] = ms_f / reps
-        fam_launches[name] = n_f // reps
+        ms_f, n_f = sess.time_family(name, fam_reps)
+        fam[name] = ms_f / fam_reps
+        fam_launches[name] = n_f // fam_reps
     hbm_peak, tf_peak, peak_kind = peaks()
     H, L, d = cfg.n_head, cfg.n_layer, cfg.n_embd
     act_b = 2 if batch > 2 else 4

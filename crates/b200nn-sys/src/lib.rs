@@ -32,6 +32,7 @@ pub const B200NN_GELU_SIGMOID: u32 = 1 << 0;
 pub const B200NN_QUANT_LM_HEAD: u32 = 1 << 1;
 pub const B200NN_ARGMAX_LAST: u32 = 1 << 2;
 pub const B200NN_STOP_ON_EOS: u32 = 1 << 3;
+pub const B200NN_TOKENS_ONLY: u32 = 1 << 4;
 
 /// Kernel families of `b200nn_session_profile_step` / `b200nn_session_time_family`.
 pub const B200NN_PROF_EMBED: i32 = 0;
@@ -524,6 +525,8 @@ extern "C" {
     ) -> i32;
     pub fn b200nn_simple_rng_new(seed: u64) -> u64;
     pub fn b200nn_simple_rng_next_f32(state: *mut u64) -> f32;
+    pub fn b200nn_simple_rng_fill_uniform(state: *mut u64, n: usize, out: *mut f32) -> i32;
+    pub fn b200nn_simple_rng_fill_normal(state: *mut u64, n: usize, std_dev: f32, out: *mut f32) -> i32;
     pub fn b200nn_top_k_sample(
         logits: *const f32,
         n: usize,

@@ -58,7 +58,9 @@ enum {
     B200NN_GELU_SIGMOID = 1u << 0,   /* x*sigmoid(1.702x) (compute_transformer.rs:1473) instead of tanh */
     B200NN_QUANT_LM_HEAD = 1u << 1,  /* int4 models: quantise the tied LM head as well               */
     B200NN_ARGMAX_LAST = 1u << 2,    /* keep the last maximum on ties (GH/nn/models/gpt2.rs:991-997)  */
-    B200NN_STOP_ON_EOS = 1u << 3     /* stop before appending token 50256 (gpt2.rs:698-700)          */
+    B200NN_STOP_ON_EOS = 1u << 3,    /* stop before appending token 50256 (gpt2.rs:698-700)          */
+    B200NN_TOKENS_ONLY = 1u << 4     /* decode sessions: the step's logits are not written to memory (the greedy
+                                        pick is taken in the LM head's epilogue); b200nn_session_logits fails */
 };
 
 typedef struct b200nn_ctx b200nn_ctx;
@@ -369,6 +371,13 @@ B200NN_API int32_t b200nn_gpt2_forward_profiled(b200nn_gpt2 *m, const uint32_t *
  * (state >> 40) / 2^24 in [0,1). */
 B200NN_API uint64_t b200nn_simple_rng_new(uint64_t seed);
 B200NN_API float b200nn_simple_rng_next_f32(uint64_t *state);
+/* Seeded synthetic tensors from the reference's own generator, so that a Rust caller holding only
+ * SimpleRng (gpt2.rs:1000-1023) can regenerate them bit for bit: n uniforms in [0,1) (next_f32), or n
+ * normals N(0, std_dev) by Box-Muller in f64 on consecutive pairs of uniforms (u1, u2):
+ * sqrt(-2 ln(1-u1)) cos(2 pi u2), then sqrt(-2 ln(1-u1)) sin(2 pi u2), each times std_dev, cast to f32.
+ * No counterpart in the reference (it has no synthetic-weight generator). */
+B200NN_API int32_t b200nn_simple_rng_fill_uniform(uint64_t *state, size_t n, float *out);
+B200NN_API int32_t b200nn_simple_rng_fill_normal(uint64_t *state, size_t n, float std_dev, float *out);
 /* top_k_sample (gpt2.rs:1029-1058) on a host logits vector: logits / max(temperature, 1e-8), the k
  * largest in the order of a stable descending sort, f32 softmax over them, one draw, cumulative search. */
 B200NN_API int32_t b200nn_top_k_sample(const float *logits, size_t n, size_t k, float temperature, uint64_t *rng_state,

@@ -583,3 +583,95 @@ def test_two_contexts_in_one_process_one_host_thread_each(reg):
         assert err == 0
         assert (out == ref[i * 6:(i + 1) * 6]).mean() > 0.97
         assert np_ref.rel_rms(y, yref) < 1e-5
+
+
+@pytest.mark.parametrize("quant_head", [False, True])
+@pytest.mark.parametrize("B", [1, 2, 7, 40])
+def test_greedy_pick_in_the_lm_head_epilogue_equals_the_separate_kernel(reg, quant_head, B):
+    """Decode sessions take the greedy token inside the LM head's epilogue (a maximum and index per 32
+    features, reduced by a second small kernel).  Same tokens, bit for bit, as argmax_kernel over the
+    stored logits, under both tie rules; with every vocabulary row equal all logits of a row are equal
+    (tensor-core path: every column goes through the same operations), so the first-index rule must give
+    token 0 and the last-index rule the last token."""
+    cfg = _mini(n_layer=1, d=128, vocab=523)
+    w = synth.gpt2_weights(cfg, base_seed=97, std=0.08, random_ln=True)
+    w["wte"][400] = w["wte"][17]
+    w["wte"][522] = w["wte"][17]
+    prompts = synth.token_ids(B, (B, 5), cfg.vocab_size)
+    head = b200nn.QUANT_LM_HEAD if quant_head else 0
+    for tie in (0, b200nn.ARGMAX_LAST):
+        m = Int4Gpt2Model.from_weights(w, cfg, reg, flags=head | tie)
+        fused, _ = m.generate_batch(prompts, 6)
+        s = DecodeSession(m, batch=B, capacity=16)  # the same with the logits kept
+        s.prefill(prompts)
+        s.step(5)
+        assert np.array_equal(s.tokens(), fused[:, 5:])
+        assert np.array_equal(np.argmax(s.logits(), axis=1) if not tie else
+                              s.logits().shape[1] - 1 - np.argmax(s.logits()[:, ::-1], axis=1), s.tokens()[:, -1])
+        reg.set_tuning("fused_argmax", 0)
+        try:
+            plain, _ = m.generate_batch(prompts, 6)
+        finally:
+            reg.set_tuning("fused_argmax", 1)
+        assert np.array_equal(fused, plain)
+    if B > 2:
+        flat = dict(w)
+        flat["wte"] = np.repeat(w["wte"][:1], cfg.vocab_size, axis=0)
+        for tie, want in ((0, 0), (b200nn.ARGMAX_LAST, cfg.vocab_size - 1)):
+            m = Int4Gpt2Model.from_weights(flat, cfg, reg, flags=head | tie)
+            out, _ = m.generate_batch(prompts, 3)
+            assert (out[:, 5:] == want).all()
+    with pytest.raises(b200nn.NnError):  # a session that keeps no logits cannot hand them out
+        s = DecodeSession(m, batch=B, capacity=16, flags=b200nn.TOKENS_ONLY)
+        s.prefill(prompts)
+        s.logits()
+    assert reg.device_error() == 0
+
+
+@pytest.mark.parametrize("d,B,offset", [(192, 40, 0.0), (256, 33, 0.05), (320, 130, 0.0)])
+def test_block_layernorms_folded_into_the_gemms(reg, d, B, offset):
+    """Tuning key ln_fold = 1 (off by default: measured slower): decode steps of more than gemv_max_rows
+    sequences run no LayerNorm kernel inside the blocks; the residual GEMMs hand fp16(x * g) and the row
+    sums on, and the q/k/v and MLP GEMMs normalise after the product.  Same logits as the oracle and as
+    the step with LayerNorm kernels, with random scale and shift vectors, a width whose last feature tile
+    is ragged (192, 320), two token tiles (130 rows) and a residual stream whose mean is not small against
+    its spread (offset).  Tolerance against the oracle: 1.5x the path's relative RMS, because x * g is
+    rounded to fp16 before the mean is taken out instead of after."""
+    cfg = _mini(n_layer=3, d=d, vocab=389)
+    w = synth.gpt2_weights(cfg, base_seed=211, std=0.08, random_ln=True)
+    w["wpe"] = w["wpe"] + np.float32(offset)
+    m = Int4Gpt2Model.from_weights(w, cfg, reg, flags=b200nn.QUANT_LM_HEAD)
+    om = oracle.Model(cfg.as_dict(), _int4_oracle_weights(m, cfg, w, True))
+    P = 6
+    prompts = synth.token_ids(d + B, (B, P), cfg.vocab_size)
+
+    def first_steps(fold):
+        reg.set_tuning("ln_fold", fold)
+        try:
+            s = DecodeSession(m, batch=B, capacity=P + 8)
+            before = reg.launch_count()
+            s.prefill(prompts)
+            s.step(1)  # the tokens the prefill picked go through one decode step: same history on both paths
+            lg1 = s.logits()
+            n1 = reg.launch_count()
+            s.step(3)
+            return lg1, s.tokens(), s.logits(), n1 - before
+        finally:
+            reg.set_tuning("ln_fold", 0)
+
+    lg_f, tok_f, lg3_f, launches_f = first_steps(1)
+    lg_k, tok_k, lg3_k, launches_k = first_steps(0)
+    assert launches_k - launches_f == 2 * cfg.n_layer  # the block LayerNorms of the one eager decode step
+    assert (tok_f[:, :2] == tok_k[:, :2]).mean() > 0.97
+    # two GPU paths, each near the oracle: twice the tolerance between them
+    assert np.abs(lg_f - lg_k).max() < 2 * MAX_ABS and np_ref.rel_rms(lg_f, lg_k) < 2 * REL_RMS
+    same = (tok_f == tok_k).all(axis=1)
+    assert same.mean() > 0.9
+    assert np.abs(lg3_f[same] - lg3_k[same]).max() < 2 * MAX_ABS and np_ref.rel_rms(lg3_f[same], lg3_k[same]) < 2 * REL_RMS
+    for b in (0, B - 1):
+        ref, lg = om.generate_cached(prompts[b], 2, flags=oracle.KV_FP16, want_logits=True)
+        _check_tokens(np.concatenate([prompts[b], tok_f[b][:2]]), ref, lg, P)
+        if np.array_equal(tok_f[b][:2], ref[P:]):
+            assert np.abs(lg_f[b] - lg[-1]).max() < MAX_ABS and np_ref.rel_rms(lg_f[b], lg[-1]) < 1.5 * REL_RMS
+            print(f"fold vs oracle {np_ref.rel_rms(lg_f[b], lg[-1]):.2e}, kernels vs oracle {np_ref.rel_rms(lg_k[b], lg[-1]):.2e}")
+    assert reg.device_error() == 0

@@ -81,3 +81,43 @@ def test_softmax_max_prob_oracle():
     assert oracle.softmax_max_prob(np.zeros(4, np.float32)) == pytest.approx(0.25)
     x = np.array([10.0, 0.0, -3.0], np.float32)
     assert oracle.softmax_max_prob(x) == pytest.approx(float(np.exp(10.0) / np.exp(x.astype(np.float64)).sum()), rel=1e-6)
+
+
+def test_synthetic_weights_from_simple_rng_are_reproducible_from_the_reference_generator():
+    """synth's "simple_rng" source: per-tensor SimpleRng streams, normals by Box-Muller on pairs of
+    uniforms -- restated here in pure Python from the reference's xorshift64 (gpt2.rs:1000-1023), so a Rust
+    caller with nothing but SimpleRng gets the same bits."""
+    import math
+
+    from b200nn import Gpt2Config, synth
+
+    cfg = Gpt2Config(n_layer=1, n_embd=8, n_head=1, vocab_size=11, n_positions=4)
+    w = synth.gpt2_weights(cfg, base_seed=77, std=0.02, source="simple_rng")
+    w2 = synth.gpt2_weights(cfg, base_seed=77, std=0.02, source="simple_rng")
+    assert all(np.array_equal(w[k], w2[k]) for k in w)
+
+    def py_normals(seed, n, std):
+        x = seed or 0xDEADBEEFCAFE1234
+        out = []
+
+        def nxt():
+            nonlocal x
+            x ^= (x << 13) & 0xFFFFFFFFFFFFFFFF
+            x ^= x >> 7
+            x ^= (x << 17) & 0xFFFFFFFFFFFFFFFF
+            return float(np.float32((x >> 40) / float(1 << 24)))
+
+        while len(out) < n:
+            u1, u2 = nxt(), nxt()
+            r = math.sqrt(-2.0 * math.log(1.0 - u1))
+            out.append(np.float32(r * math.cos(2 * math.pi * u2) * float(np.float32(std))))
+            out.append(np.float32(r * math.sin(2 * math.pi * u2) * float(np.float32(std))))
+        return np.asarray(out[:n], dtype=np.float32)
+
+    assert np.allclose(w["wte"].ravel(), py_normals(77 + 1, 11 * 8, 0.02), rtol=0, atol=1e-9)
+    assert np.allclose(w["h.0.attn.c_attn.weight"].ravel(), py_normals(77 + 1000 + 3, 8 * 24, 0.02), rtol=0, atol=1e-9)
+    big = synth._normal(5, (200000,), 1.0, "simple_rng")
+    assert abs(float(big.mean())) < 0.01 and abs(float(big.std()) - 1.0) < 0.01
+    # the default source is unchanged
+    assert np.array_equal(synth.gpt2_weights(cfg, base_seed=77)["wte"],
+                          (np.random.Generator(np.random.PCG64(78)).standard_normal((11, 8), dtype=np.float32) * np.float32(0.02)))

@@ -109,3 +109,36 @@ def test_multi_head_attention_layer(reg, seq):
         assert np.abs(yc.to_host()[0] - y[past]).max() < 2e-3
         assert np.abs(nk.reshape(H, 64) - k[:, past]).max() < 2e-3
         assert np.abs(nv.reshape(H, 64) - v[:, past]).max() < 2e-3
+
+
+@pytest.mark.parametrize("B,H,S,past,cap", [(2, 3, 128, 0, 128), (1, 12, 1024, 0, 1024), (2, 2, 200, 77, 300),
+                                            (1, 1, 1, 0, 5), (3, 5, 257, 128, 640), (1, 2, 130, 511, 641)])
+def test_prefill_attention_fp16_buffers_tensor_cores(reg, B, H, S, past, cap):
+    """The tensor-core prefill kernel on caller-owned fp16 buffers (what the models call): several key
+    tiles, a query count and a history that are no multiples of the 128-row tiles, more capacity than
+    rows, several sequences and heads.  Cache rows past the last written one hold NaN: they must not
+    reach the result (the copies zero-fill past the written extent).  Oracle on the same fp16 values;
+    tolerance: the output's fp16 rounding plus f32 accumulation."""
+    import torch
+    dev = torch.device("cuda", reg.device)
+    rng = np.random.default_rng(B * 1000 + S + past)
+    n = past + S
+    q = oracle.f16_round(rng.standard_normal((B, S, H * 64)).astype(np.float32))
+    k = oracle.f16_round(rng.standard_normal((B, H, n, 64)).astype(np.float32))
+    v = oracle.f16_round(rng.standard_normal((B, H, n, 64)).astype(np.float32))
+    kc = np.full((B, H, cap, 64), np.nan, np.float16)
+    vc = np.full((B, H, cap, 64), np.nan, np.float16)
+    kc[:, :, :n] = k
+    vc[:, :, :n] = v
+    q_d = torch.from_numpy(q.astype(np.float16).reshape(B * S, H * 64)).to(dev)
+    k_d, v_d = torch.from_numpy(kc).to(dev), torch.from_numpy(vc).to(dev)
+    out_d = torch.zeros((B * S, H * 64), device=dev, dtype=torch.float16)
+    torch.cuda.synchronize()
+    ops.prefill_attention_f16(q_d.data_ptr(), k_d.data_ptr(), v_d.data_ptr(), B, H, cap, S, past, out_d.data_ptr(), reg)
+    reg.synchronize()
+    out = out_d.cpu().numpy().astype(np.float32).reshape(B, S, H * 64)
+    for b in range(B):
+        ref = oracle.mha(q[b], k[b], v[b], H, 64, S, past, n)
+        assert np.isfinite(out[b]).all()
+        assert np.abs(out[b] - ref).max() < 2e-3, (b, np.abs(out[b] - ref).max())
+    assert reg.device_error() == 0

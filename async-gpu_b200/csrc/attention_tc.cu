@@ -187,21 +187,26 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             int nvalid = row_valid ? min(a_pos, kv_end - 1) - j0 + 1 : 0;
             nvalid = max(0, min(nvalid, 128));
             const bool full = __all_sync(0xffffffffu, nvalid == 128);
-            float mloc = NEG_BIG;
+            float mx[4] = {NEG_BIG, NEG_BIG, NEG_BIG, NEG_BIG}; // four independent chains
 #pragma unroll 1
             for (int hf = 0; hf < 2; ++hf) { // pass 1: row maximum, 64 scores per round trip
                 uint32_t v[64];
                 tc::tmem_ld_x64(sbuf + 64 * hf, v);
                 if (full) {
 #pragma unroll
-                    for (int e = 0; e < 64; e += 2) mloc = tc::fmax3(mloc, __uint_as_float(v[e]), __uint_as_float(v[e + 1]));
+                    for (int e = 0; e < 64; e += 8) {
+                        mx[0] = tc::fmax3(mx[0], __uint_as_float(v[e]), __uint_as_float(v[e + 1]));
+                        mx[1] = tc::fmax3(mx[1], __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+                        mx[2] = tc::fmax3(mx[2], __uint_as_float(v[e + 4]), __uint_as_float(v[e + 5]));
+                        mx[3] = tc::fmax3(mx[3], __uint_as_float(v[e + 6]), __uint_as_float(v[e + 7]));
+                    }
                 } else {
 #pragma unroll
                     for (int e = 0; e < 64; ++e)
-                        if (64 * hf + e < nvalid) mloc = fmaxf(mloc, __uint_as_float(v[e]));
+                        if (64 * hf + e < nvalid) mx[e & 3] = fmaxf(mx[e & 3], __uint_as_float(v[e]));
                 }
-                asm volatile("" : "+f"(mloc)); // this half is reduced before the next load is issued (register budget)
             }
+            const float mloc = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
             const float m_new = fmaxf(m, mloc * SCALE_LOG2E);
             const float corr = tc::ex2_approx(m - m_new);
             if (j >= 1) { // the previous step's P V has had pass 1 to finish
@@ -212,7 +217,7 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 tc::tc_fence_before_sync();
                 tc::mbar_arrive(bar(bars.s_free[bf ^ 1])); // that buffer may take S_{j+1}
             }
-            float lsum = 0.0f;
+            float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll 1
             for (int hf = 0; hf < 2; ++hf) { // pass 2: p = 2^(s*scale - max) as fp16 pairs over the scores
                 uint32_t v[64], o[32];
@@ -225,16 +230,15 @@ prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                         if (64 * hf + e >= nvalid) p0 = 0.0f;
                         if (64 * hf + e + 1 >= nvalid) p1 = 0.0f;
                     }
-                    lsum += p0 + p1;
+                    ls[(e >> 1) & 3] += p0 + p1;
                     o[e >> 1] = pack_half2(p0, p1);
                 }
                 tc::tmem_st_x32(sbuf + 32 * hf, o);
-                asm volatile("" : "+f"(lsum));
             }
             tc::tmem_st_wait();
             tc::tc_fence_before_sync();
             tc::mbar_arrive(bar(bars.p_full[bf]));
-            l = l * corr + lsum;
+            l = l * corr + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
             m = m_new;
             corr_prev = corr;
         }

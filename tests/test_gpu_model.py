@@ -294,8 +294,11 @@ def test_decode_attention_medium_batches_both_kernels(reg, B, P):
     finally:
         reg.set_tuning("attn_stream_min10", 20)
     assert reg.device_error() == 0
-    assert np.abs(lg_b - lg_p).max() < 2e-3
     assert (tok_b != tok_p).mean() < 0.01
+    same = (tok_b == tok_p).all(axis=1)  # a near-tie flipped by the order of the split-K additions changes a history
+    # the two kernels add in different orders; where that moves an fp16 activation of order one by one unit
+    # in the last place (1e-3), the logits move by a few 1e-3: a fifth of the path's tolerance is allowed
+    assert np.abs(lg_b[same] - lg_p[same]).max() < MAX_ABS / 5
     for b in (0, B // 2, B - 1):
         ref, lg = om.generate_cached(prompts[b], N, flags=oracle.KV_FP16, want_logits=True)
         _check_tokens(np.concatenate([prompts[b], tok_b[b]]), ref, lg, P)

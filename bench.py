@@ -170,7 +170,7 @@ def run_reference(args):
     return 0
 
 
-def gemv_bandwidth(reg, cfg, hbm_peak, iters=96):
+def gemv_bandwidth(reg, cfg, hbm_peak, iters=96, only=None):
     """Dequant-GEMV (one input row, CUDA cores) HBM bandwidth on the model's four Linear shapes: each
     launch reads a different copy of the weight (copies add up to more than the L2), launches are
     back to back on the library's stream between two CUDA events.  Bytes per launch are algorithmic:
@@ -183,6 +183,8 @@ def gemv_bandwidth(reg, cfg, hbm_peak, iters=96):
     out = {}
     shapes = {"qkv": (d, 3 * d), "proj": (d, d), "fc": (d, 4 * d), "fcproj": (4 * d, d), "lm_head": (d, cfg.vocab_size)}
     for name, (k, n) in shapes.items():
+        if only and name != only:
+            continue
         packed, scales, _, _ = synth.int4_linear_case(11, 1, k, n, 128)
         copies = max(2, int(256e6 // (k * n / 2)))
         lins = [b200nn.Int4Linear(packed, scales, None, k, n, 128, reg) for _ in range(copies)]
@@ -267,7 +269,7 @@ def int4_linear_isolated(reg, hbm_peak, tf_peak, iters=64):
     return out
 
 
-def attention_isolated(reg, hbm_peak, tf_peak):
+def attention_isolated(reg, hbm_peak, tf_peak, seqs=(256, 512, 1024), decode=True):
     """Isolated attention on fp16 device buffers in the library's cache layout.  Prefill: causal, batch 8,
     12 heads, head_dim 64, seq 256 / 512 / 1024, Q/K/V N(0,1); flops 4 * 0.5 * B * H * n^2 * 64 (the
     convention of tests_transformer.rs:2219-2224 times the batch); both a single launch between events
@@ -279,7 +281,7 @@ def attention_isolated(reg, hbm_peak, tf_peak):
     stream = torch.cuda.ExternalStream(reg.stream)
     out = {"prefill": {}, "decode": {}}
     B, H = 8, 12
-    for n in (256, 512, 1024):
+    for n in seqs:
         q = torch.randn(B * n, H * 64, device="cuda", dtype=torch.float16)
         kc = torch.randn(B, H, n, 64, device="cuda", dtype=torch.float16)
         vc = torch.randn(B, H, n, 64, device="cuda", dtype=torch.float16)
@@ -299,6 +301,8 @@ def attention_isolated(reg, hbm_peak, tf_peak):
         out["prefill"][f"seq{n}"] = {"us_graph": round(us, 2), "us_single_launch": round(single_us, 2),
                                      "tflops": round(flops / us / 1e6, 2),
                                      "frac_of_bf16_peak": round(flops / us / 1e6 / tf_peak, 4)}
+    if not decode:
+        return out
     B, ctx = 64, 1024
     copies = 3  # 3 x 201 MB of K and V: more than the 126 MB L2 between two uses of a copy
     q = torch.randn(B, H * 64, device="cuda", dtype=torch.float16)
@@ -584,6 +588,12 @@ def main():
     ap.add_argument("--e2e-runs", type=int, default=2)
     ap.add_argument("--reps", type=int, default=5, help="repeats of the timed region (the median is reported)")
     ap.add_argument("--no-isolated", action="store_true", help="skip the isolated int4 Linear / attention measurements")
+    ap.add_argument("--isolated-only", action="store_true",
+                    help="profiling aid: only the isolated attention measurements (no model is built); with "
+                         "--attention-seq N only the causal prefill case of that length, with --gemv-shape NAME "
+                         "only the one-row dequant-GEMV of that GPT-2 XL shape (qkv, proj, fc, fcproj, lm_head)")
+    ap.add_argument("--attention-seq", type=int, default=0)
+    ap.add_argument("--gemv-shape", default="")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-cpu-reference-form", action="store_true",
                     help="skip the single-thread, cache-less GPT-2 Small CPU run (the reference's own CPU test form)")
@@ -595,6 +605,20 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.isolated_only:
+        sys.path.insert(0, os.path.join(ROOT, "async-gpu_b200"))
+        import b200nn
+        reg = b200nn.KernelRegistry(0)
+        hbm_peak, tf_peak, _ = peaks()
+        if args.gemv_shape:
+            from b200nn.gpt2 import Gpt2Config
+            print(json.dumps({"gemv": gemv_bandwidth(reg, Gpt2Config.xl(), hbm_peak, only=args.gemv_shape),
+                              "note": "isolated kernels only: not the benchmark line"}), flush=True)
+            return 0
+        seqs = (args.attention_seq,) if args.attention_seq else (256, 512, 1024)
+        print(json.dumps({"attention": attention_isolated(reg, hbm_peak, tf_peak, seqs, decode=not args.attention_seq),
+                          "note": "isolated kernels only: not the benchmark line"}), flush=True)
+        return 0
     if args.gpus > 1 and "RANK" not in os.environ:
         # convenience: relaunch under torchrun when called plainly with --gpus N
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",

@@ -246,27 +246,6 @@ __device__ __forceinline__ void tmem_ld_x64(uint32_t taddr, uint32_t (&v)[64]) {
         : "r"(taddr), "r"(taddr + 32)
         : "memory");
 }
-// 128 consecutive columns (a whole score row) in one round trip: four 32-column loads, then one wait.
-__device__ __forceinline__ void tmem_ld_x128(uint32_t taddr, uint32_t (&v)[128]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%128];\n\t"
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%129];\n\t"
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%64, %65, %66, %67, %68, %69, %70, %71, %72, %73, %74, %75, %76, %77, %78, %79, %80, %81, %82, %83, %84, %85, %86, %87, %88, %89, %90, %91, %92, %93, %94, %95}, [%130];\n\t"
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%96, %97, %98, %99, %100, %101, %102, %103, %104, %105, %106, %107, %108, %109, %110, %111, %112, %113, %114, %115, %116, %117, %118, %119, %120, %121, %122, %123, %124, %125, %126, %127}, [%131];\n\t"
-        "tcgen05.wait::ld.sync.aligned;"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31]), "=r"(v[32]), "=r"(v[33]), "=r"(v[34]), "=r"(v[35]), "=r"(v[36]), "=r"(v[37]), "=r"(v[38]), "=r"(v[39]), "=r"(v[40]), "=r"(v[41]), "=r"(v[42]), "=r"(v[43]), "=r"(v[44]), "=r"(v[45]), "=r"(v[46]), "=r"(v[47]), "=r"(v[48]), "=r"(v[49]), "=r"(v[50]), "=r"(v[51]), "=r"(v[52]), "=r"(v[53]), "=r"(v[54]), "=r"(v[55]), "=r"(v[56]), "=r"(v[57]), "=r"(v[58]), "=r"(v[59]), "=r"(v[60]), "=r"(v[61]), "=r"(v[62]), "=r"(v[63]), "=r"(v[64]), "=r"(v[65]), "=r"(v[66]), "=r"(v[67]), "=r"(v[68]), "=r"(v[69]), "=r"(v[70]), "=r"(v[71]), "=r"(v[72]), "=r"(v[73]), "=r"(v[74]), "=r"(v[75]), "=r"(v[76]), "=r"(v[77]), "=r"(v[78]), "=r"(v[79]), "=r"(v[80]), "=r"(v[81]), "=r"(v[82]), "=r"(v[83]), "=r"(v[84]), "=r"(v[85]), "=r"(v[86]), "=r"(v[87]), "=r"(v[88]), "=r"(v[89]), "=r"(v[90]), "=r"(v[91]), "=r"(v[92]), "=r"(v[93]), "=r"(v[94]), "=r"(v[95]), "=r"(v[96]), "=r"(v[97]), "=r"(v[98]), "=r"(v[99]), "=r"(v[100]), "=r"(v[101]), "=r"(v[102]), "=r"(v[103]), "=r"(v[104]), "=r"(v[105]), "=r"(v[106]), "=r"(v[107]), "=r"(v[108]), "=r"(v[109]), "=r"(v[110]), "=r"(v[111]), "=r"(v[112]), "=r"(v[113]), "=r"(v[114]), "=r"(v[115]), "=r"(v[116]), "=r"(v[117]), "=r"(v[118]), "=r"(v[119]), "=r"(v[120]), "=r"(v[121]), "=r"(v[122]), "=r"(v[123]), "=r"(v[124]), "=r"(v[125]), "=r"(v[126]), "=r"(v[127])
-        : "r"(taddr), "r"(taddr + 32), "r"(taddr + 64), "r"(taddr + 96)
-        : "memory");
-}
-// 32 consecutive columns, load and wait
-__device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
-        "tcgen05.wait::ld.sync.aligned;"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-}
 // registers -> TMEM: 32 consecutive columns
 __device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t (&v)[32]) {
     asm volatile(

@@ -114,7 +114,21 @@ B200NN_API int32_t b200nn_ctx_set_gemv_max_rows(b200nn_ctx *ctx, int32_t rows);
  * "tc_persistent" (default 1): the fp16 GEMM runs as one persistent block per SM from two 256-row
  * tiles per SM on; 0 = always one tile per block.  "int4_via_f16" (default 1): an int4 Linear over
  * such a pass of at least 2048 rows writes its weight out once as fp16 and uses that GEMM; 0 = the
- * int4 GEMM for every row count. */
+ * int4 GEMM for every row count.
+ * "fused_argmax" (default 1): greedy decode steps take the token inside the LM head's epilogue (one
+ * (maximum, index) entry per 32 logits, a second small kernel per row); 0 = a separate pass over the
+ * stored logits.  Same tokens either way.
+ * "ln_fold" (default 0): decode steps of an int4 model with more than gemv_max_rows sequences run without
+ * LayerNorm kernels inside the blocks: the residual GEMMs write fp16(x * scale) and per-tile row sums,
+ * the q/k/v and MLP GEMMs normalise in their epilogue.  Measured slower than the kernels it removes
+ * (the residual GEMMs then need complete sums, i.e. cluster splits); sessions read it when created.
+ * "persist" (default 0): decode steps of an int4 model run all transformer blocks as one cooperative
+ * kernel (decode sessions whose shape it supports).  Measured slower than the per-op CUDA graph.
+ * Its aids: "persist_min_rows" / "persist_max_rows" (batch range it is used for), "persist_prefetch_mb",
+ * "persist_wait_kcycles" (limit of its device-wide waits in thousands of SM cycles; default about one
+ * second), "persist_fault_phase" (test aid: one block skips its arrival in that phase, so that the
+ * bounded wait runs out and B200NN_ERR_DEVICE is reported; nothing hangs), "persist_trace" /
+ * "trace" (stamp buffers for b200nn_ctx_read_persist_trace / b200nn_ctx_read_trace). */
 B200NN_API int32_t b200nn_ctx_set_tuning(b200nn_ctx *ctx, const char *key, int32_t value);
 /* Measurement aid: after set_tuning("trace", 1) the first block of the next tensor-core GEMM
  * writes SM-clock stamps of its pipeline events into a 256-slot buffer; this copies it out. */

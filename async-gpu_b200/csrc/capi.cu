@@ -113,6 +113,7 @@ extern "C" int32_t b200nn_ctx_set_tuning(b200nn_ctx *ctx, const char *key, int32
     else if (!strcmp(key, "gemv_max_rows")) ctx->gemv_max_rows = value < 0 ? 2 : value;
     else if (!strcmp(key, "fused_argmax")) ctx->fused_argmax = value ? 1 : 0;
     else if (!strcmp(key, "ln_fold")) ctx->ln_fold = value ? 1 : 0;
+    else if (!strcmp(key, "ln_rows_min")) ctx->ln_rows_min = value > 0 ? value : 1024;
     else if (!strcmp(key, "persist")) ctx->persist = value ? 1 : 0;
     else if (!strcmp(key, "persist_min_rows")) ctx->persist_min_rows = value < 1 ? 3 : value;
     else if (!strcmp(key, "persist_max_rows")) ctx->persist_max_rows = value < 1 ? 256 : value;

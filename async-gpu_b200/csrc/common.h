@@ -38,6 +38,7 @@ struct b200nn_ctx {
     int last_cuda = 0;
     int sm_count = 148;
     int gemv_max_rows = 2;       // rows at or below this take the CUDA-core GEMV
+    int ln_rows_min = 1024;      // LayerNorm of at least this many rows (no residual) takes the warp-per-row kernel
     int ln_fold = 0;             // 1: decode steps of int4 models fold each block LayerNorm into the GEMMs around it (measured slower than the LayerNorm kernels: the residual GEMMs then need complete sums, i.e. cluster splits)
     int fused_argmax = 1;        // greedy decode steps take the argmax in the LM head's epilogue (0: separate kernel)
     uint64_t launches = 0;       // kernels launched by this library

@@ -66,10 +66,94 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const float *__restrict_
     }
 }
 
+// The same for many rows (prefill passes): one warp per row, eight rows per block at a time, blocks
+// walking the rows.  The row sits in the warp's registers (NV float4 per lane), both reductions are
+// shuffles, nothing waits on a block barrier, and scale / shift come from shared memory; 16-byte loads and
+// 8-byte (fp16) or 16-byte (f32) stores, all coalesced.  d a multiple of 4, at most 128 * NV.
+template <int NV, typename TOut>
+__global__ void __launch_bounds__(256) layernorm_rows_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
+                                                             const float *__restrict__ beta, float eps, int rows, int d,
+                                                             TOut *__restrict__ out) {
+    extern __shared__ float4 gb[]; // [d/4] scale, then [d/4] shift
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, d4 = d >> 2;
+    pdl_trigger();
+    for (int i = threadIdx.x; i < d4; i += 256) {
+        gb[i] = reinterpret_cast<const float4 *>(gamma)[i];
+        gb[d4 + i] = reinterpret_cast<const float4 *>(beta)[i];
+    }
+    __syncthreads();
+    pdl_wait();
+    const float inv_d = 1.0f / (float)d;
+    for (int row = blockIdx.x * 8 + warp; row < rows; row += gridDim.x * 8) {
+        const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)row * d);
+        float4 v[NV];
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int c = lane + 32 * i;
+            v[i] = c < d4 ? __ldcs(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        }
+        const float mean = warp_sum(s) * inv_d;
+        float q = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+            if (lane + 32 * i < d4) {
+                const float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, e = v[i].w - mean;
+                q += (a * a + b * b) + (c * c + e * e);
+            }
+        const float inv_std = rsqrtf(warp_sum(q) * inv_d + eps);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int c = lane + 32 * i;
+            if (c < d4) {
+                const float4 g = gb[c], b = gb[d4 + c];
+                float4 y;
+                y.x = (v[i].x - mean) * inv_std * g.x + b.x;
+                y.y = (v[i].y - mean) * inv_std * g.y + b.y;
+                y.z = (v[i].z - mean) * inv_std * g.z + b.z;
+                y.w = (v[i].w - mean) * inv_std * g.w + b.w;
+                if constexpr (sizeof(TOut) == 2) {
+                    __half2 lo = __floats2half2_rn(y.x, y.y), hi = __floats2half2_rn(y.z, y.w);
+                    reinterpret_cast<uint2 *>(out + (size_t)row * d)[c] =
+                        make_uint2(*reinterpret_cast<uint32_t *>(&lo), *reinterpret_cast<uint32_t *>(&hi));
+                } else {
+                    reinterpret_cast<float4 *>(out + (size_t)row * d)[c] = y;
+                }
+            }
+        }
+    }
+}
+
+template <int NV>
+static void launch_layernorm_rows(b200nn_ctx *ctx, const float *x, const float *gamma, const float *beta, float eps, int rows,
+                                  int d, void *out, bool out_half) {
+    const int grid = std::min((rows + 7) / 8, 8 * ctx->sm_count);
+    const size_t smem = (size_t)d * 2 * sizeof(float);
+    PREFER_SMEM_ONCE((layernorm_rows_kernel<NV, __half>));
+    PREFER_SMEM_ONCE((layernorm_rows_kernel<NV, float>));
+    if (out_half)
+        launch_pdl(ctx, layernorm_rows_kernel<NV, __half>, dim3(grid), dim3(256), smem, x, gamma, beta, eps, rows, d, (__half *)out);
+    else
+        launch_pdl(ctx, layernorm_rows_kernel<NV, float>, dim3(grid), dim3(256), smem, x, gamma, beta, eps, rows, d, (float *)out);
+}
+
 int launch_layernorm(b200nn_ctx *ctx, const float *x, const float *res_in, float *sum_out, const float *gamma,
                      const float *beta, float eps, int rows, int d, void *out, bool out_half) {
     if (rows <= 0) return B200NN_OK;
     if (d > 256 * 32) return set_error(ctx, B200NN_ERR_UNSUPPORTED, "layer_norm: d > 8192");
+    // many rows without a residual (prefill passes): a warp per row
+    if (rows >= ctx->ln_rows_min && !res_in && !sum_out && d % 4 == 0 && d <= 2048 && !((uintptr_t)x & 15) && !((uintptr_t)out & 15) &&
+        !((uintptr_t)gamma & 15) && !((uintptr_t)beta & 15)) {
+        const int nv = (d / 4 + 31) / 32;
+        if (nv <= 6) launch_layernorm_rows<6>(ctx, x, gamma, beta, eps, rows, d, out, out_half);
+        else if (nv <= 8) launch_layernorm_rows<8>(ctx, x, gamma, beta, eps, rows, d, out, out_half);
+        else if (nv <= 10) launch_layernorm_rows<10>(ctx, x, gamma, beta, eps, rows, d, out, out_half);
+        else if (nv <= 13) launch_layernorm_rows<13>(ctx, x, gamma, beta, eps, rows, d, out, out_half);
+        else launch_layernorm_rows<16>(ctx, x, gamma, beta, eps, rows, d, out, out_half);
+        CK_LAUNCH(ctx, "layernorm_rows_kernel");
+        return B200NN_OK;
+    }
 #define LN_LAUNCH(V)                                                                                              \
     do {                                                                                                          \
         PREFER_SMEM_ONCE((layernorm_kernel<V, __half>));                                                          \

@@ -118,6 +118,8 @@ B200NN_API int32_t b200nn_ctx_set_gemv_max_rows(b200nn_ctx *ctx, int32_t rows);
  * "fused_argmax" (default 1): greedy decode steps take the token inside the LM head's epilogue (one
  * (maximum, index) entry per 32 logits, a second small kernel per row); 0 = a separate pass over the
  * stored logits.  Same tokens either way.
+ * "ln_rows_min" (default 1024): a LayerNorm over at least this many rows (no residual input, width a
+ * multiple of 4 up to 2048) runs as one warp per row instead of one block per row.
  * "ln_fold" (default 0): decode steps of an int4 model with more than gemv_max_rows sequences run without
  * LayerNorm kernels inside the blocks: the residual GEMMs write fp16(x * scale) and per-tile row sums,
  * the q/k/v and MLP GEMMs normalise in their epilogue.  Measured slower than the kernels it removes

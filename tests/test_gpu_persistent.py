@@ -50,7 +50,7 @@ def test_persistent_decode_matches_oracle_and_per_operation_path(reg, d, layers,
     launches_o = reg.launch_count() - launches0
     assert launches_p < launches_o  # one launch per step for all blocks instead of seven per block
     same = (tok_p == tok_o).all(axis=1)  # a near-tie that flips a token changes everything after it
-    assert same.mean() >= 0.97
+    assert (~same).sum() <= max(2, B // 32)  # the order of the split-K additions differs between the two paths (and from run to run)
     assert np.abs(lg_p - lg_o)[same].max() < 5e-3
     om = oracle.Model(cfg.as_dict(), _int4_oracle_weights(m, cfg, w, False))
     for b in sorted({0, B // 2, B - 1}):

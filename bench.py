@@ -471,6 +471,7 @@ def run_b200(args):
     dominant = max(("attention", "linear"), key=lambda k2: fam[k2])
     roof = dict(roofs[dominant])
     roof["frac"] = roof["achieved"] / roof["peak"] if roof["peak"] else None
+    roof["frac_of_nominal_8000_GBps"] = roof["achieved"] / 8000.0  # the data-sheet HBM3e figure, for context
     # DRAM bytes per launch: the ratio dram bytes / algorithmic bytes of the kernel's ncu capture on a
     # smaller case of the same workload (2 layers, context 130: 218.1 MB moved for 213.0 MB), applied
     # to this launch's algorithmic bytes -- the kernel streams, so its traffic grows with the rows read

@@ -610,6 +610,9 @@ def main():
         sys.path.insert(0, os.path.join(ROOT, "async-gpu_b200"))
         import b200nn
         reg = b200nn.KernelRegistry(0)
+        for kv in args.tune:
+            key, val = kv.split("=")
+            reg.set_tuning(key, int(val))
         hbm_peak, tf_peak, _ = peaks()
         if args.gemv_shape:
             from b200nn.gpt2 import Gpt2Config

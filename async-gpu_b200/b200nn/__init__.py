@@ -19,7 +19,7 @@ LIB_PATH = os.path.join(os.path.dirname(_HERE), "libb200nn.so")
 
 OK, ERR_SHAPE, ERR_DIM, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE, ERR_ARG, ERR_IO, ERR_MISSING = range(9)
 ACT_NONE, ACT_GELU_TANH, ACT_GELU_SIGMOID, ACT_RELU = range(4)
-GELU_SIGMOID, QUANT_LM_HEAD, ARGMAX_LAST, STOP_ON_EOS, TOKENS_ONLY = 1, 2, 4, 8, 16
+GELU_SIGMOID, QUANT_LM_HEAD, ARGMAX_LAST, STOP_ON_EOS, TOKENS_ONLY, WEIGHTS_OUT_IN = 1, 2, 4, 8, 16, 32
 PROF_NAMES = ("embed", "layernorm", "linear", "attention", "lm_head", "argmax")
 
 _KINDS = {ERR_SHAPE: "ShapeMismatch", ERR_DIM: "DimOutOfRange", ERR_UNSUPPORTED: "KernelNotFound",
@@ -339,4 +339,5 @@ from .gpt2 import (Gpt2Config, Gpt2Model, Int4Gpt2Model, KvCache, DecodeSession,
 from .sampling import SimpleRng, top_k_sample  # noqa: E402
 from .tokenizer import Gpt2Tokenizer, TokenizerError, GPT2_VOCAB_SIZE, ENDOFTEXT_TOKEN_ID  # noqa: E402
 from .checkpoint import (SafeTensorsFile, TensorInfo, list_tensors, load_all_tensors, load_gpt2_weights,  # noqa: E402
-                         load_int4_tensors)
+                         load_int4_tensors, TensorData, WeightMapping, LoadedWeights, map_weight, map_weight_t,
+                         load_safetensors_raw, load_safetensors_mapped, load_safetensors, gpt2_weight_map)

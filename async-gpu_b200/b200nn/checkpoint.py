@@ -8,7 +8,7 @@ from dataclasses import dataclass
 
 import numpy as np
 
-from . import ERR_UNSUPPORTED, NnError, load_library
+from . import ERR_MISSING, ERR_SHAPE, ERR_UNSUPPORTED, NnError, load_library
 
 _NP = {"F64": np.float64, "F32": np.float32, "F16": np.float16, "I64": np.int64, "I32": np.int32, "I16": np.int16,
        "I8": np.int8, "U64": np.uint64, "U32": np.uint32, "U16": np.uint16, "U8": np.uint8, "BOOL": np.bool_}
@@ -150,3 +150,112 @@ def load_gpt2_weights(path):
     for k, v in t.items():
         out["wte" if k == "wte.weight" else "wpe" if k == "wpe.weight" else k] = v
     return out
+
+
+# ---------------------------------------------------------------------------------------------
+# The generic loader (gpu-host/src/model_generic.rs): weights by logical name, with the transforms a
+# weight map asks for.  Host code over the same safetensors reader.
+# ---------------------------------------------------------------------------------------------
+class TensorData:
+    """``TensorData`` (model_generic.rs:24-58): f32 data + shape."""
+
+    def __init__(self, data, shape):
+        self.data = np.ascontiguousarray(data, dtype=np.float32).reshape(-1)
+        self.shape = [int(s) for s in shape]
+        if int(np.prod(self.shape, dtype=np.int64)) != self.data.size:
+            raise NnError(ERR_SHAPE, f"TensorData: shape {self.shape} does not hold {self.data.size} elements")
+
+    def numel(self):
+        return int(self.data.size)
+
+    def transpose_2d(self):
+        """[rows, cols] -> [cols, rows]; anything but a 2-D tensor is the reference's MissingTensor error."""
+        if len(self.shape) != 2:
+            raise NnError(ERR_MISSING, f"transpose_2d requires 2D, got {self.shape}")
+        r, c = self.shape
+        return TensorData(self.data.reshape(r, c).T.copy(), [c, r])
+
+
+TRANSFORM_NONE, TRANSFORM_TRANSPOSE_2D = "None", "Transpose2D"  # ``Transform`` (model_generic.rs:61-67)
+
+
+class WeightMapping:
+    """``WeightMapping`` (model_generic.rs:70-78): safetensors key -> logical name, with a transform."""
+
+    def __init__(self, safetensors_key, name, transform=TRANSFORM_NONE):
+        self.safetensors_key, self.name, self.transform = safetensors_key, name, transform
+
+
+def map_weight(st_key, name):
+    """``map_weight`` (model_generic.rs:190-196)."""
+    return WeightMapping(st_key, name, TRANSFORM_NONE)
+
+
+def map_weight_t(st_key, name):
+    """``map_weight_t`` (model_generic.rs:199-205): with the Conv1D -> Linear transpose."""
+    return WeightMapping(st_key, name, TRANSFORM_TRANSPOSE_2D)
+
+
+class LoadedWeights:
+    """``LoadedWeights`` (model_generic.rs:84-120): tensors by logical name."""
+
+    def __init__(self, weights):
+        self._w = dict(weights)
+
+    def get(self, name):
+        return self._w.get(name)
+
+    def require(self, name):
+        t = self._w.get(name)
+        if t is None:
+            raise NnError(ERR_MISSING, name)
+        return t
+
+    def __len__(self):
+        return len(self._w)
+
+    def is_empty(self):
+        return not self._w
+
+    def total_params(self):
+        return sum(t.numel() for t in self._w.values())
+
+    def items(self):
+        return self._w.items()
+
+
+def load_safetensors_raw(path):
+    """``load_safetensors_raw`` (model_generic.rs:126-150): key -> TensorData; a tensor that is not F32 is
+    ``UnexpectedDtype``."""
+    return {k: TensorData(v, v.shape) for k, v in load_all_tensors(path).items()}
+
+
+def load_safetensors_mapped(path, weight_map):
+    """``load_safetensors_mapped`` (model_generic.rs:156-177): a missing key is ``MissingTensor``."""
+    raw = load_safetensors_raw(path)
+    out = {}
+    for m in weight_map:
+        t = raw.get(m.safetensors_key)
+        if t is None:
+            raise NnError(ERR_MISSING, m.safetensors_key)
+        out[m.name] = t.transpose_2d() if m.transform == TRANSFORM_TRANSPOSE_2D else TensorData(t.data.copy(), t.shape)
+    return LoadedWeights(out)
+
+
+def load_safetensors(path):
+    """``load_safetensors`` (model_generic.rs:183-187): every tensor under its own key, no transform."""
+    return LoadedWeights(load_safetensors_raw(path))
+
+
+def gpt2_weight_map(num_layers):
+    """``gpt2_weight_map`` (model_generic.rs:210-277): GPT-2's keys under their own names, the four Conv1D
+    weights of every block transposed to Linear layout [out,in]."""
+    m = [map_weight(k, k) for k in ("wte.weight", "wpe.weight", "ln_f.weight", "ln_f.bias")]
+    for i in range(num_layers):
+        p = f"h.{i}"
+        for k in ("ln_1.weight", "ln_1.bias", "ln_2.weight", "ln_2.bias"):
+            m.append(map_weight(f"{p}.{k}", f"{p}.{k}"))
+        for k in ("attn.c_attn", "attn.c_proj", "mlp.c_fc", "mlp.c_proj"):
+            m.append(map_weight_t(f"{p}.{k}.weight", f"{p}.{k}.weight"))
+            m.append(map_weight(f"{p}.{k}.bias", f"{p}.{k}.bias"))
+    return m

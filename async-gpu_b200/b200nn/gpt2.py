@@ -131,6 +131,28 @@ class Gpt2Model:
         return cls(weights, config, reg, **kw)
 
     @classmethod
+    def from_generic_weights(cls, weights, config, reg, **kw):
+        """``Gpt2Model::from_generic_weights`` / ``Int4Gpt2Model::from_generic_weights`` (gpt2.rs:410-476,
+        1436-1500): ``weights`` is the generic loader's ``LoadedWeights`` under GPT-2's key names, the four
+        dense weights of every block already transposed to Linear layout [out,in] (``gpt2_weight_map``).
+        A key that is missing is the reference's ``ShapeMismatch { expected: key, .. }``."""
+        from . import WEIGHTS_OUT_IN
+
+        def need(key):
+            t = weights.get(key)
+            if t is None:
+                raise NnError(ERR_SHAPE, f"ShapeMismatch: expected {key}, got MissingTensor")
+            return t.data
+
+        w = {"wte": need("wte.weight"), "wpe": need("wpe.weight"), "ln_f.weight": need("ln_f.weight"),
+             "ln_f.bias": need("ln_f.bias")}
+        for i in range(config.n_layer):
+            for _, key, _ in _LAYER_KEYS:
+                w[f"h.{i}.{key}"] = need(f"h.{i}.{key}")
+        kw["flags"] = kw.get("flags", 0) | WEIGHTS_OUT_IN
+        return cls(w, config, reg, **kw)
+
+    @classmethod
     def from_safetensors(cls, path, reg: KernelRegistry, config: Gpt2Config | None = None, flags: int = 0,
                          group_size: int = 128):
         """``load_gpt2_weights`` (model.rs:308-386) + ``from_weights`` in the library: an F32 checkpoint

@@ -20,13 +20,21 @@ static int upload_vec(b200nn_ctx *ctx, const float *h, size_t n, std::shared_ptr
 }
 
 // Builds one Linear from a checkpoint-layout weight [K,N] (= [in,out]).
+// `out_in`: the weight is given in Linear layout [N,K] = [out,in] (what from_generic_weights holds).
 static int make_linear(b200nn_ctx *ctx, const float *w_kn, const float *bias, size_t K, size_t N, bool int4,
-                       size_t group, LinearAny *out) {
+                       size_t group, LinearAny *out, bool out_in = false) {
     if (!w_kn) return set_error(ctx, B200NN_ERR_ARG, "null weight pointer");
     out->K = (int)K;
     out->N = (int)N;
     out->int4 = int4;
-    if (!int4) return f32_weight_upload(ctx, w_kn, false, bias, K, N, &out->f);
+    if (!int4) return f32_weight_upload(ctx, w_kn, out_in, bias, K, N, &out->f);
+    std::vector<float> transposed;
+    if (out_in) { // the quantiser groups along K per output column of [K,N]
+        transposed.resize(K * N);
+        for (size_t o = 0; o < N; ++o)
+            for (size_t i = 0; i < K; ++i) transposed[i * N + o] = w_kn[o * K + i];
+        w_kn = transposed.data();
+    }
     std::vector<uint32_t> packed((K / 8) * N);
     std::vector<float> scales(((K + group - 1) / group) * N);
     int rc = host_quantize_weight_int4(w_kn, K, N, group, packed.data(), scales.data());
@@ -63,10 +71,11 @@ static int model_create(b200nn_ctx *ctx, const b200nn_gpt2_config *cfg, const b2
         TRY(upload_vec(ctx, lw.ln_1_bias, d, &b.ln1_b));
         TRY(upload_vec(ctx, lw.ln_2_weight, d, &b.ln2_g));
         TRY(upload_vec(ctx, lw.ln_2_bias, d, &b.ln2_b));
-        TRY(make_linear(ctx, lw.c_attn_weight, lw.c_attn_bias, d, 3 * d, int4, group, &b.qkv));
-        TRY(make_linear(ctx, lw.c_proj_weight, lw.c_proj_bias, d, d, int4, group, &b.proj));
-        TRY(make_linear(ctx, lw.mlp_fc_weight, lw.mlp_fc_bias, d, ffn, int4, group, &b.fc));
-        TRY(make_linear(ctx, lw.mlp_proj_weight, lw.mlp_proj_bias, ffn, d, int4, group, &b.fcproj));
+        const bool oi = (flags & B200NN_WEIGHTS_OUT_IN) != 0;
+        TRY(make_linear(ctx, lw.c_attn_weight, lw.c_attn_bias, d, 3 * d, int4, group, &b.qkv, oi));
+        TRY(make_linear(ctx, lw.c_proj_weight, lw.c_proj_bias, d, d, int4, group, &b.proj, oi));
+        TRY(make_linear(ctx, lw.mlp_fc_weight, lw.mlp_fc_bias, d, ffn, int4, group, &b.fc, oi));
+        TRY(make_linear(ctx, lw.mlp_proj_weight, lw.mlp_proj_bias, ffn, d, int4, group, &b.fcproj, oi));
     }
     // tied LM head: logits = h * wte^T, i.e. a Linear with weight [K=d, N=V] = wte transposed
     m->lm_head.K = (int)d;

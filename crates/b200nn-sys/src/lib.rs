@@ -33,6 +33,7 @@ pub const B200NN_QUANT_LM_HEAD: u32 = 1 << 1;
 pub const B200NN_ARGMAX_LAST: u32 = 1 << 2;
 pub const B200NN_STOP_ON_EOS: u32 = 1 << 3;
 pub const B200NN_TOKENS_ONLY: u32 = 1 << 4;
+pub const B200NN_WEIGHTS_OUT_IN: u32 = 1 << 5;
 
 /// Kernel families of `b200nn_session_profile_step` / `b200nn_session_time_family`.
 pub const B200NN_PROF_EMBED: i32 = 0;

@@ -59,8 +59,12 @@ enum {
     B200NN_QUANT_LM_HEAD = 1u << 1,  /* int4 models: quantise the tied LM head as well               */
     B200NN_ARGMAX_LAST = 1u << 2,    /* keep the last maximum on ties (GH/nn/models/gpt2.rs:991-997)  */
     B200NN_STOP_ON_EOS = 1u << 3,    /* stop before appending token 50256 (gpt2.rs:698-700)          */
-    B200NN_TOKENS_ONLY = 1u << 4     /* decode sessions: the step's logits are not written to memory (the greedy
+    B200NN_TOKENS_ONLY = 1u << 4,    /* decode sessions: the step's logits are not written to memory (the greedy
                                         pick is taken in the LM head's epilogue); b200nn_session_logits fails */
+    B200NN_WEIGHTS_OUT_IN = 1u << 5  /* model creation: the four Linear weights of every block are given in Linear
+                                        layout [out,in], as Gpt2Model::from_generic_weights holds them after the
+                                        generic loader's Conv1D transposes (gpt2.rs:410-476, 1436-1500;
+                                        model_generic.rs:222-277), instead of checkpoint layout [in,out] */
 };
 
 typedef struct b200nn_ctx b200nn_ctx;

@@ -184,3 +184,54 @@ def test_load_int4_tensors_layout_of_the_reference_script(tmp_path):
     write_safetensors(path, bad)
     with pytest.raises(b200nn.NnError):
         checkpoint.load_int4_tensors(path)
+
+
+def _tiny_gpt2_checkpoint(n_layer=2, d=8, vocab=11, npos=6, seed=3):
+    """A checkpoint with Hugging Face GPT-2 key names: dense weights in Conv1D layout [in,out]."""
+    rng = np.random.default_rng(seed)
+    t = {"wte.weight": rng.standard_normal((vocab, d)), "wpe.weight": rng.standard_normal((npos, d)),
+         "ln_f.weight": rng.standard_normal(d), "ln_f.bias": rng.standard_normal(d)}
+    for i in range(n_layer):
+        p = f"h.{i}"
+        for k in ("ln_1", "ln_2"):
+            t[f"{p}.{k}.weight"], t[f"{p}.{k}.bias"] = rng.standard_normal(d), rng.standard_normal(d)
+        for k, (a, b) in {"attn.c_attn": (d, 3 * d), "attn.c_proj": (d, d), "mlp.c_fc": (d, 4 * d), "mlp.c_proj": (4 * d, d)}.items():
+            t[f"{p}.{k}.weight"], t[f"{p}.{k}.bias"] = rng.standard_normal((a, b)), rng.standard_normal(b)
+    return {k: np.asarray(v, np.float32) for k, v in t.items()}
+
+
+def test_generic_loader_maps_names_and_transposes(tmp_path):
+    """model_generic.rs: raw loading (F32 only), a weight map with renames and Conv1D -> Linear transposes,
+    GPT-2's own map, the LoadedWeights accessors and their errors."""
+    t = _tiny_gpt2_checkpoint()
+    path = str(tmp_path / "model.safetensors")
+    write_safetensors(path, t)
+    raw = checkpoint.load_safetensors_raw(path)
+    assert set(raw) == set(t) and raw["h.1.mlp.c_fc.weight"].shape == [8, 32]
+    assert np.array_equal(raw["wte.weight"].data.reshape(11, 8), t["wte.weight"])
+    lw = checkpoint.load_safetensors(path)
+    assert len(lw) == len(t) and not lw.is_empty() and lw.total_params() == sum(v.size for v in t.values())
+    m = [checkpoint.map_weight("wte.weight", "embedding.tokens"), checkpoint.map_weight_t("h.0.attn.c_attn.weight", "block.0.qkv")]
+    mapped = checkpoint.load_safetensors_mapped(path, m)
+    assert len(mapped) == 2 and mapped.get("wte.weight") is None
+    qkv = mapped.require("block.0.qkv")
+    assert qkv.shape == [24, 8] and np.array_equal(qkv.data.reshape(24, 8), t["h.0.attn.c_attn.weight"].T)
+    with pytest.raises(b200nn.NnError) as e:
+        mapped.require("block.1.qkv")
+    assert e.value.code == b200nn.ERR_MISSING
+    with pytest.raises(b200nn.NnError) as e:
+        checkpoint.load_safetensors_mapped(path, [checkpoint.map_weight("no.such.key", "x")])
+    assert e.value.code == b200nn.ERR_MISSING
+    with pytest.raises(b200nn.NnError):  # transpose_2d of a vector is the reference's error, too
+        checkpoint.load_safetensors_mapped(path, [checkpoint.map_weight_t("ln_f.bias", "x")])
+    gm = checkpoint.gpt2_weight_map(2)
+    assert len(gm) == 4 + 2 * 12 and sum(x.transform == checkpoint.TRANSFORM_TRANSPOSE_2D for x in gm) == 8
+    g = checkpoint.load_safetensors_mapped(path, gm)
+    assert g.require("h.1.mlp.c_proj.weight").shape == [8, 32]  # [out,in]
+    assert g.require("h.1.mlp.c_proj.bias").shape == [8] and g.require("ln_f.weight").shape == [8]
+    # a tensor of another dtype is refused by the raw loader
+    t2 = dict(t)
+    t2["extra"] = np.arange(4, dtype=np.uint32)
+    write_safetensors(path, t2)
+    with pytest.raises(b200nn.NnError):
+        checkpoint.load_safetensors_raw(path)

@@ -402,6 +402,15 @@ def test_models_from_safetensors_checkpoint(reg, tmp_path):
         same = lambda x, y: np.abs(x - y).max() < 2e-3
         assert same(a.forward(toks).to_host(), ref)
         assert same(b.forward(toks).to_host(), ref)
+        # the generic loader (model_generic.rs) + from_generic_weights: GPT-2's weight map hands the dense
+        # weights over transposed to Linear layout; same logits as from_weights, as the reference's own
+        # test_gpt2_generic_loader_regression asks (gpt2.rs:1690-1745)
+        g = b200nn.load_safetensors_mapped(str(p), b200nn.gpt2_weight_map(cfg.n_layer))
+        assert g.require("h.0.mlp.c_fc.weight").shape == [4 * d, d]
+        assert same(cls.from_generic_weights(g, cfg, reg).forward(toks).to_host(), ref)
+        with pytest.raises(b200nn.NnError) as e:  # a missing key: ShapeMismatch { expected: key, .. }
+            cls.from_generic_weights(b200nn.load_safetensors_mapped(str(p), b200nn.gpt2_weight_map(1)), cfg, reg)
+        assert e.value.code == b200nn.ERR_SHAPE and "h.1." in str(e.value)
     assert Int4Gpt2Model.from_safetensors(p, reg).quantized_memory_bytes() > 0
     # errors of the reference's loader (ModelError, model.rs:30-62)
     with pytest.raises(b200nn.NnError) as e:

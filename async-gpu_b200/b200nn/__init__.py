@@ -125,6 +125,7 @@ def load_library() -> C.CDLL:
             "b200nn_embedding_forward_tokens": (i32, [vp, _u32p, sz, sz, vpp]),
             "b200nn_embedding_destroy": (None, [vp]),
             "b200nn_attention_create": (i32, [vp, _f32p, _f32p, _f32p, _f32p, sz, sz, vpp]),
+            "b200nn_int4_attention_create": (i32, [vp, _f32p, _f32p, _f32p, _f32p, sz, sz, sz, vpp]),
             "b200nn_attention_forward_causal": (i32, [vp, vp, vpp]),
             "b200nn_attention_forward_cached": (i32, [vp, vp, _f32p, _f32p, sz, vpp, _f32p, _f32p]),
             "b200nn_attention_destroy": (None, [vp]),
@@ -333,7 +334,8 @@ def _out(reg, rc, h):
 
 
 from . import ops  # noqa: E402
-from .layers import Embedding, Int4Linear, LayerNorm, Linear, MultiHeadAttention, GELU  # noqa: E402
+from .layers import (Embedding, Int4Linear, LayerNorm, Linear, MultiHeadAttention, Int4MultiHeadAttention,  # noqa: E402
+                     GELU)
 from .gpt2 import (Gpt2Config, Gpt2Model, Int4Gpt2Model, KvCache, DecodeSession, TransformerBlock,  # noqa: E402
                    Int4TransformerBlock)
 from .sampling import SimpleRng, top_k_sample  # noqa: E402

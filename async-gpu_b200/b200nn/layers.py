@@ -166,6 +166,23 @@ class MultiHeadAttention(_Module):
         return GpuTensor(self.reg, h), nk, nv
 
 
+class Int4MultiHeadAttention(MultiHeadAttention):
+    """``Int4MultiHeadAttention::new(qkv_w [3d,d], qkv_b, out_w [d,d], out_b, d, heads, group_size, &registry)``
+    (models/gpt2.rs:1127-1214): both projections quantised to int4 at construction."""
+
+    def __init__(self, qkv_weight, qkv_bias, out_weight, out_bias, n_embd, n_heads, group_size, reg: KernelRegistry):
+        qw, qwp = _f32(qkv_weight)
+        qb, qbp = _f32(qkv_bias)
+        ow, owp = _f32(out_weight)
+        ob, obp = _f32(out_bias)
+        if qw.size != 3 * n_embd * n_embd or qb.size != 3 * n_embd or ow.size != n_embd * n_embd or ob.size != n_embd:
+            raise NnError(ERR_SHAPE, "attention weights do not match n_embd")
+        self.reg = reg
+        self.n_heads, self.d_head = n_heads, n_embd // n_heads
+        self.h = C.c_void_p()
+        reg.check(reg.lib.b200nn_int4_attention_create(reg.h, qwp, qbp, owp, obp, n_embd, n_heads, group_size, C.byref(self.h)))
+
+
 class GELU:
     """``GELU::new(&registry)`` (layers/activation.rs:15-33)."""
 

@@ -222,6 +222,39 @@ extern "C" int32_t b200nn_attention_create(b200nn_ctx *ctx, const float *qkv_wei
     return B200NN_OK;
 }
 
+// Int4MultiHeadAttention::new (gpt2.rs:1141-1188): the same layer with both projections quantised at
+// construction (weights given [out,in], quantised as [in,out] per group along K).
+extern "C" int32_t b200nn_int4_attention_create(b200nn_ctx *ctx, const float *qkv_weight, const float *qkv_bias,
+                                                const float *out_weight, const float *out_bias, size_t n_embd,
+                                                size_t n_heads, size_t group_size, b200nn_attention **out) {
+    if (!ctx || !qkv_weight || !qkv_bias || !out_weight || !out_bias || !out) return B200NN_ERR_ARG;
+    if (n_heads == 0 || n_embd % n_heads != 0 || n_embd / n_heads != 64)
+        return set_error(ctx, B200NN_ERR_UNSUPPORTED, "Int4MultiHeadAttention: d_head must be 64");
+    if (group_size == 0) return set_error(ctx, B200NN_ERR_SHAPE, "group_size must be positive");
+    auto a = std::unique_ptr<b200nn_attention>(new b200nn_attention());
+    a->ctx = ctx;
+    a->d = n_embd;
+    a->n_heads = n_heads;
+    const float *ws[2] = {qkv_weight, out_weight}, *bs[2] = {qkv_bias, out_bias};
+    LinearAny *ls[2] = {&a->qkv, &a->proj};
+    for (int i = 0; i < 2; ++i) {
+        const size_t K = n_embd, N = i ? n_embd : 3 * n_embd;
+        ls[i]->K = (int)K;
+        ls[i]->N = (int)N;
+        ls[i]->int4 = true;
+        std::vector<float> w_kn(K * N);
+        for (size_t o = 0; o < N; ++o)
+            for (size_t k = 0; k < K; ++k) w_kn[k * N + o] = ws[i][o * K + k];
+        std::vector<uint32_t> packed((K / 8) * N);
+        std::vector<float> scales(((K + group_size - 1) / group_size) * N);
+        int rc = host_quantize_weight_int4(w_kn.data(), K, N, group_size, packed.data(), scales.data());
+        if (rc != B200NN_OK) return set_error(ctx, rc, "quantize_weight_int4: K must be divisible by 8");
+        TRY(int4_weight_upload(ctx, packed.data(), scales.data(), bs[i], K, N, group_size, &ls[i]->q));
+    }
+    *out = a.release();
+    return B200NN_OK;
+}
+
 // x [new_len,d] at positions past..; cache_k/v (optional, host f32 [H][past*64]) precede the new rows.
 static int attention_run(b200nn_attention *a, const b200nn_tensor *x, const float *cached_k, const float *cached_v,
                          size_t past, b200nn_tensor **y, float *new_k_out, float *new_v_out) {
@@ -241,9 +274,20 @@ static int attention_run(b200nn_attention *a, const b200nn_tensor *x, const floa
     }
     TRY(dev_alloc(ctx, n * d * 4, &q));
     TRY(dev_alloc(ctx, n * d * 4, &att));
+    // the int4 layer with more rows than the GEMV serves: fp16 activations, tensor-core GEMMs and attention
+    const bool half = a->qkv.int4 && (int)n > ctx->gemv_max_rows && int4_gemm_tc_supported(a->qkv.q, (int)n) &&
+                      int4_gemm_tc_supported(a->proj.q, (int)n);
+    std::shared_ptr<DevBuf> xh;
+    const void *xin = x->data();
+    if (half) {
+        TRY(dev_alloc(ctx, n * d * sizeof(__half), &xh));
+        TRY(launch_f32_to_half(ctx, x->data(), (__half *)xh->p, n * d));
+        xin = xh->p;
+    }
     Epilogue e;
     e.mode = EPI_QKV;
     e.out = q->p;
+    e.out_half = half;
     e.ldo = (int)d;
     e.kc = (__half *)kc->p;
     e.vc = (__half *)vc->p;
@@ -252,19 +296,19 @@ static int attention_run(b200nn_attention *a, const b200nn_tensor *x, const floa
     e.rows_per_seq = (int)n;
     e.cap = (int)cap;
     e.pos_off = (int)past;
-    TRY(linear_forward(ctx, a->qkv, x->data(), false, (int)n, e));
+    TRY(linear_forward(ctx, a->qkv, xin, half, (int)n, e));
     if (n == 1)
-        TRY(launch_decode_attention(ctx, q->p, false, (int)d, (const __half *)kc->p, (const __half *)vc->p, 1, (int)H,
-                                    (int)cap, nullptr, (int)past, att->p, false, (int)cap));
+        TRY(launch_decode_attention(ctx, q->p, half, (int)d, (const __half *)kc->p, (const __half *)vc->p, 1, (int)H,
+                                    (int)cap, nullptr, (int)past, att->p, half, (int)cap));
     else
-        TRY(launch_prefill_attention(ctx, q->p, false, (int)d, (const __half *)kc->p, (const __half *)vc->p, 1, (int)H,
-                                     (int)cap, (int)n, (int)past, att->p, false));
+        TRY(launch_prefill_attention(ctx, q->p, half, (int)d, (const __half *)kc->p, (const __half *)vc->p, 1, (int)H,
+                                     (int)cap, (int)n, (int)past, att->p, half));
     b200nn_tensor *o = nullptr;
     TRY(tensor_alloc(ctx, {n, d}, false, &o));
     Epilogue p;
     p.out = o->data();
     p.ldo = (int)d;
-    int rc = linear_forward(ctx, a->proj, att->p, false, (int)n, p);
+    int rc = linear_forward(ctx, a->proj, att->p, half, (int)n, p);
     if (rc == B200NN_OK && (new_k_out || new_v_out)) {
         // new K,V rows back to the host as f32 [H][n*64] (values as held in the fp16 cache)
         std::shared_ptr<DevBuf> f;

@@ -372,6 +372,17 @@ extern "C" {
         n_heads: usize,
         out: *mut *mut b200nn_attention,
     ) -> i32;
+    pub fn b200nn_int4_attention_create(
+        ctx: *mut b200nn_ctx,
+        qkv_weight: *const f32,
+        qkv_bias: *const f32,
+        out_weight: *const f32,
+        out_bias: *const f32,
+        n_embd: usize,
+        n_heads: usize,
+        group_size: usize,
+        out: *mut *mut b200nn_attention,
+    ) -> i32;
     pub fn b200nn_attention_forward_causal(
         a: *mut b200nn_attention,
         x: *const b200nn_tensor,

@@ -245,6 +245,12 @@ B200NN_API void b200nn_embedding_destroy(b200nn_embedding *e);
 B200NN_API int32_t b200nn_attention_create(b200nn_ctx *ctx, const float *qkv_weight, const float *qkv_bias,
                                            const float *out_weight, const float *out_bias, size_t n_embd,
                                            size_t n_heads, b200nn_attention **out);
+/* Int4MultiHeadAttention::new (gpt2.rs:1141-1188): the same layer with both projections quantised to int4 at
+ * construction (weights given [out,in]; quantised per group of `group_size` along the input dimension).
+ * forward_causal / forward_cached / destroy are those of b200nn_attention. */
+B200NN_API int32_t b200nn_int4_attention_create(b200nn_ctx *ctx, const float *qkv_weight, const float *qkv_bias,
+                                                const float *out_weight, const float *out_bias, size_t n_embd,
+                                                size_t n_heads, size_t group_size, b200nn_attention **out);
 B200NN_API int32_t b200nn_attention_forward_causal(b200nn_attention *a, const b200nn_tensor *x, b200nn_tensor **y);
 /* forward_cached: x [new_len,d]; cached_k/cached_v host f32 [n_heads][kv_len*d_head] flattened head
  * after head; returns y and the new K,V rows [n_heads][new_len*d_head] in host buffers. */

@@ -142,3 +142,41 @@ def test_prefill_attention_fp16_buffers_tensor_cores(reg, B, H, S, past, cap):
         assert np.isfinite(out[b]).all()
         assert np.abs(out[b] - ref).max() < 2e-3, (b, np.abs(out[b] - ref).max())
     assert reg.device_error() == 0
+
+
+@pytest.mark.parametrize("seq", [1, 2, 7, 150])
+def test_int4_multi_head_attention_layer(reg, seq):
+    """Int4MultiHeadAttention (gpt2.rs:1127-1214): both projections quantised at construction (group 128 along
+    the input dimension of the transposed weight); reference = the f64 path on the dequantised weights the
+    quantisation rule gives, K and V rounded to fp16 as the layer's cache holds them.  1 and 2 rows take the
+    GEMV, 7 and 150 the tensor-core GEMMs and attention with fp16 activations."""
+    rng = np.random.default_rng(seq + 40)
+    d, H, g = 128, 2, 128
+    qkv_w = (rng.standard_normal((3 * d, d)) * 0.08).astype(np.float32)
+    qkv_b = (rng.standard_normal(3 * d) * 0.1).astype(np.float32)
+    out_w = (rng.standard_normal((d, d)) * 0.08).astype(np.float32)
+    out_b = (rng.standard_normal(d) * 0.1).astype(np.float32)
+    x = rng.standard_normal((seq, d)).astype(np.float32)
+    layer = b200nn.Int4MultiHeadAttention(qkv_w, qkv_b, out_w, out_b, d, H, g, reg)
+    y = layer.forward_causal(GpuTensor.from_host(x, (seq, d), reg)).to_host()
+
+    def deq(w_out_in):  # the weight the layer multiplies with: quantise [in,out], fp16 scales, dequantise
+        k, n = w_out_in.shape[1], w_out_in.shape[0]
+        p, s = oracle.quantize_weight_int4(np.ascontiguousarray(w_out_in.T), k, n, g)
+        return oracle.dequant_weight_int4(p, oracle.f16_round(s), k, n, g).astype(np.float64)  # [in,out]
+
+    qkv = x.astype(np.float64) @ deq(qkv_w) + qkv_b
+    k = qkv[:, d:2 * d].reshape(seq, H, 64).transpose(1, 0, 2).astype(np.float32)
+    v = qkv[:, 2 * d:].reshape(seq, H, 64).transpose(1, 0, 2).astype(np.float32)
+    att = oracle.mha(qkv[:, :d].astype(np.float32), oracle.f16_round(k), oracle.f16_round(v), H, 64, seq, 0, seq)
+    ref = att.astype(np.float64) @ deq(out_w) + out_b
+    tol = 2e-3 if seq <= 2 else 6e-3  # fp16 activations on the tensor-core path
+    assert np.abs(y - ref).max() < tol, np.abs(y - ref).max()
+    if seq > 2:
+        past = seq - 1
+        ck = oracle.f16_round(k[:, :past]).reshape(H, past * 64)
+        cv = oracle.f16_round(v[:, :past]).reshape(H, past * 64)
+        yc, nk, nv = layer.forward_cached(GpuTensor.from_host(x[past:], (1, d), reg), ck, cv, past)
+        assert np.abs(yc.to_host()[0] - y[past]).max() < tol
+        assert np.abs(nk.reshape(H, 64) - k[:, past]).max() < 2e-3
+    assert reg.device_error() == 0

@@ -96,6 +96,9 @@ def load_library() -> C.CDLL:
             "b200nn_tensor_ndim": (i32, [vp]), "b200nn_tensor_numel": (sz, [vp]),
             "b200nn_tensor_shape": (i32, [vp, szp, i32]), "b200nn_tensor_reshape": (i32, [vp, szp, i32, vpp]),
             "b200nn_tensor_clone": (i32, [vp, vpp]), "b200nn_tensor_data": (vp, [vp]),
+            "b200nn_tensor_transpose": (i32, [vp, sz, sz, vpp]),
+            "b200nn_tensor_concat": (i32, [vpp, sz, sz, vpp]),
+            "b200nn_tensor_split": (i32, [vp, sz, szp, sz, vpp]),
             "b200nn_tensor_destroy": (None, [vp]),
             "b200nn_quantize_weight_int4": (i32, [_f32p, sz, sz, sz, _u32p, _f32p]),
             "b200nn_quantize_int4_per_group": (i32, [_f32p, sz, sz, _u32p, _f32p]),
@@ -311,6 +314,46 @@ class GpuTensor:
         h = C.c_void_p()
         self.reg.check(self.reg.lib.b200nn_tensor_reshape(self.h, sh, nd, C.byref(h)))
         return GpuTensor(self.reg, h)
+
+    def ndim(self):
+        return len(self.shape())
+
+    def strides(self):
+        """Row-major strides in elements (tensor.rs:140; every tensor here is contiguous)."""
+        st, acc = [], 1
+        for n in reversed(self.shape()):
+            st.append(acc)
+            acc *= n
+        return tuple(reversed(st))
+
+    def is_contiguous(self):
+        return True
+
+    def size_bytes(self):
+        return self.numel() * 4
+
+    def transpose(self, dim0: int, dim1: int):
+        """``GpuTensor::transpose`` (tensor.rs:227-268), on the device."""
+        h = C.c_void_p()
+        return _out(self.reg, self.reg.lib.b200nn_tensor_transpose(self.h, dim0, dim1, C.byref(h)), h)
+
+    @staticmethod
+    def concat(tensors, dim: int):
+        """``GpuTensor::concat`` (tensor.rs:287-349), on the device."""
+        if not tensors:
+            raise NnError(ERR_SHAPE, "ShapeMismatch: expected at least one tensor, got empty list")
+        reg = tensors[0].reg
+        arr = (C.c_void_p * len(tensors))(*[t.h for t in tensors])
+        h = C.c_void_p()
+        return _out(reg, reg.lib.b200nn_tensor_concat(arr, len(tensors), dim, C.byref(h)), h)
+
+    def split(self, dim: int, sizes):
+        """``GpuTensor::split`` (tensor.rs:351-393), on the device."""
+        sizes = [int(x) for x in sizes]
+        arr = (C.c_size_t * max(1, len(sizes)))(*sizes)
+        outs = (C.c_void_p * max(1, len(sizes)))()
+        self.reg.check(self.reg.lib.b200nn_tensor_split(self.h, dim, arr, len(sizes), outs))
+        return [GpuTensor(self.reg, C.c_void_p(outs[i])) for i in range(len(sizes))]
 
     def clone_tensor(self):
         h = C.c_void_p()

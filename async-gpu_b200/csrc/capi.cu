@@ -210,6 +210,105 @@ extern "C" int32_t b200nn_tensor_clone(const b200nn_tensor *t, b200nn_tensor **o
     *out = c;
     return B200NN_OK;
 }
+// GpuTensor::transpose / concat / split (tensor.rs:227-393), on the device.
+extern "C" int32_t b200nn_tensor_transpose(const b200nn_tensor *t, size_t dim0, size_t dim1, b200nn_tensor **out) {
+    if (!t || !out) return B200NN_ERR_ARG;
+    b200nn_ctx *ctx = t->ctx;
+    const size_t nd = t->shape.size();
+    if (dim0 >= nd || dim1 >= nd)
+        return set_error(ctx, B200NN_ERR_DIM, "transpose: dim " + std::to_string(dim0 >= nd ? dim0 : dim1) + " out of range for " +
+                                                  std::to_string(nd) + " dimensions");
+    if (dim0 == dim1) return b200nn_tensor_clone(t, out);
+    std::vector<size_t> oshape(t->shape);
+    std::swap(oshape[dim0], oshape[dim1]);
+    b200nn_tensor *r = nullptr;
+    TRY(tensor_alloc(ctx, oshape, false, &r));
+    int rc = launch_tensor_transpose(ctx, t->data(), r->data(), t->shape, (int)dim0, (int)dim1);
+    if (rc != B200NN_OK) { delete r; return rc; }
+    *out = r;
+    return B200NN_OK;
+}
+
+// A contiguous tensor seen as [outer][shape[dim]][inner].
+static void outer_inner(const std::vector<size_t> &shape, size_t dim, size_t *outer, size_t *inner) {
+    *outer = *inner = 1;
+    for (size_t d = 0; d < dim; ++d) *outer *= shape[d];
+    for (size_t d = dim + 1; d < shape.size(); ++d) *inner *= shape[d];
+}
+
+extern "C" int32_t b200nn_tensor_concat(const b200nn_tensor *const *tensors, size_t count, size_t dim, b200nn_tensor **out) {
+    if (!tensors || !out) return B200NN_ERR_ARG;
+    if (count == 0) return B200NN_ERR_SHAPE; // "at least one tensor"
+    for (size_t i = 0; i < count; ++i)
+        if (!tensors[i]) return B200NN_ERR_ARG;
+    b200nn_ctx *ctx = tensors[0]->ctx;
+    const std::vector<size_t> &s0 = tensors[0]->shape;
+    const size_t nd = s0.size();
+    if (dim >= nd) return set_error(ctx, B200NN_ERR_DIM, "concat: dim out of range");
+    size_t total = 0;
+    for (size_t i = 0; i < count; ++i) {
+        const std::vector<size_t> &si = tensors[i]->shape;
+        if (si.size() != nd) return set_error(ctx, B200NN_ERR_SHAPE, "concat: tensor " + std::to_string(i) + " has another number of dimensions");
+        for (size_t d = 0; d < nd; ++d)
+            if (d != dim && si[d] != s0[d])
+                return set_error(ctx, B200NN_ERR_SHAPE, "concat: tensor " + std::to_string(i) + " differs in dim " + std::to_string(d));
+        total += si[dim];
+    }
+    std::vector<size_t> oshape(s0);
+    oshape[dim] = total;
+    size_t outer, inner;
+    outer_inner(oshape, dim, &outer, &inner);
+    b200nn_tensor *r = nullptr;
+    TRY(tensor_alloc(ctx, oshape, false, &r));
+    size_t off = 0;
+    for (size_t i = 0; i < count; ++i) {
+        const size_t w = tensors[i]->shape[dim] * inner * sizeof(float);
+        if (w && outer) {
+            cudaError_t e = cudaMemcpy2DAsync(r->data() + off * inner, total * inner * sizeof(float), tensors[i]->data(), w, w, outer,
+                                              cudaMemcpyDeviceToDevice, ctx->stream);
+            if (e != cudaSuccess) { delete r; return set_cuda_error(ctx, e, "tensor_concat"); }
+        }
+        off += tensors[i]->shape[dim];
+    }
+    *out = r;
+    return B200NN_OK;
+}
+
+extern "C" int32_t b200nn_tensor_split(const b200nn_tensor *t, size_t dim, const size_t *sizes, size_t count, b200nn_tensor **outs) {
+    if (!t || !sizes || !outs) return B200NN_ERR_ARG;
+    b200nn_ctx *ctx = t->ctx;
+    const size_t nd = t->shape.size();
+    if (dim >= nd) return set_error(ctx, B200NN_ERR_DIM, "split: dim out of range");
+    size_t total = 0;
+    for (size_t i = 0; i < count; ++i) total += sizes[i];
+    if (total != t->shape[dim])
+        return set_error(ctx, B200NN_ERR_SHAPE, "split: sizes sum to " + std::to_string(total) + ", dimension holds " + std::to_string(t->shape[dim]));
+    size_t outer, inner;
+    outer_inner(t->shape, dim, &outer, &inner);
+    size_t off = 0;
+    for (size_t i = 0; i < count; ++i) outs[i] = nullptr;
+    for (size_t i = 0; i < count; ++i) {
+        std::vector<size_t> cshape(t->shape);
+        cshape[dim] = sizes[i];
+        b200nn_tensor *c = nullptr;
+        int rc = tensor_alloc(ctx, cshape, false, &c);
+        const size_t w = sizes[i] * inner * sizeof(float);
+        if (rc == B200NN_OK && w && outer) {
+            cudaError_t e = cudaMemcpy2DAsync(c->data(), w, t->data() + off * inner, t->shape[dim] * inner * sizeof(float), w, outer,
+                                              cudaMemcpyDeviceToDevice, ctx->stream);
+            if (e != cudaSuccess) rc = set_cuda_error(ctx, e, "tensor_split");
+        }
+        if (rc != B200NN_OK) {
+            delete c;
+            for (size_t j = 0; j < i; ++j) { delete outs[j]; outs[j] = nullptr; }
+            return rc;
+        }
+        outs[i] = c;
+        off += sizes[i];
+    }
+    return B200NN_OK;
+}
+
 extern "C" float *b200nn_tensor_data(b200nn_tensor *t) { return t ? t->data() : nullptr; }
 extern "C" void b200nn_tensor_destroy(b200nn_tensor *t) { delete t; }
 

@@ -281,6 +281,7 @@ int launch_bias_add(b200nn_ctx *ctx, float *data, const float *bias, size_t tota
 int launch_add(b200nn_ctx *ctx, float *a, const float *b, size_t n);
 int launch_split_qkv(b200nn_ctx *ctx, const float *qkv, int seq, int H, int dh, float *q, float *k, float *v);
 int launch_concat_heads(b200nn_ctx *ctx, const float *heads, int seq, int H, int dh, float *out);
+int launch_tensor_transpose(b200nn_ctx *ctx, const float *in, float *out, const std::vector<size_t> &shape, int dim0, int dim1);
 int launch_f32_to_half(b200nn_ctx *ctx, const float *x, __half *y, size_t n);
 int launch_half_to_f32(b200nn_ctx *ctx, const __half *x, float *y, size_t n);
 // rows of `src` ([n_seq*rows_per_seq, d]) at index rows_per_seq-1 of each sequence -> dst [n_seq, d]

@@ -511,3 +511,47 @@ int launch_record_tokens(b200nn_ctx *ctx, const uint32_t *tok, int rows, uint32_
     CK_LAUNCH(ctx, "record_tokens_kernel");
     return B200NN_OK;
 }
+
+
+// ---------------------------------------------------------------------------------------------
+// GpuTensor::transpose (tensor.rs:227-268): out[..., i, ..., j, ...] = in[..., j, ..., i, ...] for any two
+// dimensions of a contiguous tensor of up to 8 dimensions.  The reference goes through the host; here each
+// thread walks from its output index to the input index over the swapped strides.
+// ---------------------------------------------------------------------------------------------
+struct TransposeDims {
+    int ndim;
+    unsigned long long out_stride[8], src_stride[8]; // src strides already swapped
+};
+__global__ void tensor_transpose_kernel(const float *__restrict__ in, float *__restrict__ out, size_t n, TransposeDims td) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    size_t rem = i, src = 0;
+    for (int d = 0; d < td.ndim; ++d) {
+        const size_t idx = rem / td.out_stride[d];
+        rem -= idx * td.out_stride[d];
+        src += idx * td.src_stride[d];
+    }
+    out[i] = in[src];
+}
+
+int launch_tensor_transpose(b200nn_ctx *ctx, const float *in, float *out, const std::vector<size_t> &shape, int dim0, int dim1) {
+    const int nd = (int)shape.size();
+    if (nd > 8) return set_error(ctx, B200NN_ERR_UNSUPPORTED, "transpose: more than 8 dimensions");
+    std::vector<size_t> stride(nd, 1), oshape(shape);
+    for (int d = nd - 2; d >= 0; --d) stride[d] = stride[d + 1] * shape[d + 1];
+    std::swap(oshape[dim0], oshape[dim1]);
+    std::swap(stride[dim0], stride[dim1]);
+    TransposeDims td;
+    td.ndim = nd;
+    size_t n = 1, os = 1;
+    for (int d = nd - 1; d >= 0; --d) {
+        td.out_stride[d] = os;
+        os *= oshape[d];
+        td.src_stride[d] = stride[d];
+        n *= shape[d];
+    }
+    if (n == 0) return B200NN_OK;
+    tensor_transpose_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(in, out, n, td);
+    CK_LAUNCH(ctx, "tensor_transpose_kernel");
+    return B200NN_OK;
+}

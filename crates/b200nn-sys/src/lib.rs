@@ -185,6 +185,25 @@ extern "C" {
         out: *mut *mut b200nn_tensor,
     ) -> i32;
     pub fn b200nn_tensor_clone(t: *const b200nn_tensor, out: *mut *mut b200nn_tensor) -> i32;
+    pub fn b200nn_tensor_transpose(
+        t: *const b200nn_tensor,
+        dim0: usize,
+        dim1: usize,
+        out: *mut *mut b200nn_tensor,
+    ) -> i32;
+    pub fn b200nn_tensor_concat(
+        tensors: *const *const b200nn_tensor,
+        count: usize,
+        dim: usize,
+        out: *mut *mut b200nn_tensor,
+    ) -> i32;
+    pub fn b200nn_tensor_split(
+        t: *const b200nn_tensor,
+        dim: usize,
+        sizes: *const usize,
+        count: usize,
+        outs: *mut *mut b200nn_tensor,
+    ) -> i32;
     pub fn b200nn_tensor_data(t: *mut b200nn_tensor) -> *mut f32;
     pub fn b200nn_tensor_destroy(t: *mut b200nn_tensor);
     pub fn b200nn_quantize_weight_int4(

@@ -159,6 +159,14 @@ B200NN_API size_t b200nn_tensor_numel(const b200nn_tensor *t);
 B200NN_API int32_t b200nn_tensor_shape(const b200nn_tensor *t, size_t *shape_out, int32_t capacity);
 B200NN_API int32_t b200nn_tensor_reshape(const b200nn_tensor *t, const size_t *shape, int32_t ndim, b200nn_tensor **out);
 B200NN_API int32_t b200nn_tensor_clone(const b200nn_tensor *t, b200nn_tensor **out);
+/* GpuTensor::transpose(dim0, dim1), GpuTensor::concat(tensors, dim), GpuTensor::split(dim, sizes)
+ * (tensor.rs:227-393; the reference goes through the host, these stay on the device).  Errors as there:
+ * B200NN_ERR_DIM for a dimension out of range, B200NN_ERR_SHAPE for an empty list, mismatched shapes or
+ * sizes that do not add up.  split writes `count` new tensors into outs. */
+B200NN_API int32_t b200nn_tensor_transpose(const b200nn_tensor *t, size_t dim0, size_t dim1, b200nn_tensor **out);
+B200NN_API int32_t b200nn_tensor_concat(const b200nn_tensor *const *tensors, size_t count, size_t dim, b200nn_tensor **out);
+B200NN_API int32_t b200nn_tensor_split(const b200nn_tensor *t, size_t dim, const size_t *sizes, size_t count,
+                                       b200nn_tensor **outs);
 B200NN_API float *b200nn_tensor_data(b200nn_tensor *t); /* device pointer */
 B200NN_API void b200nn_tensor_destroy(b200nn_tensor *t);
 

@@ -312,3 +312,49 @@ def test_linear_tensor_core_many_tiles_take_the_persistent_kernel(reg, m, k, n, 
     ref16 = np_ref.gelu_tanh(x.astype(np.float16).astype(np.float64) @ w_used.T + bias)
     assert np_ref.rel_rms(y, ref16) < 5e-6
     assert reg.device_error() == 0
+
+
+def test_tensor_transpose_concat_split(reg):
+    """GpuTensor::transpose / concat / split (tensor.rs:227-393) on the device, against numpy, with the
+    reference's errors (DimOutOfRange, ShapeMismatch)."""
+    rng = np.random.default_rng(21)
+    a = rng.standard_normal((3, 4, 5, 2)).astype(np.float32)
+    t = GpuTensor.from_host(a, a.shape, reg)
+    assert t.ndim() == 4 and t.strides() == (40, 10, 2, 1) and t.is_contiguous() and t.size_bytes() == a.size * 4
+    for d0, d1 in [(0, 1), (1, 3), (0, 3), (2, 2), (3, 1)]:
+        got = t.transpose(d0, d1)
+        ref = np.swapaxes(a, d0, d1)
+        assert got.shape() == ref.shape and np.array_equal(got.to_host(), ref)
+    m = rng.standard_normal((257, 130)).astype(np.float32)  # a 2-D case larger than a block
+    assert np.array_equal(GpuTensor.from_host(m, m.shape, reg).transpose(0, 1).to_host(), m.T)
+    with pytest.raises(b200nn.NnError) as e:
+        t.transpose(0, 4)
+    assert e.value.code == b200nn.ERR_DIM
+    parts = [rng.standard_normal(s).astype(np.float32) for s in [(3, 2, 5), (3, 4, 5), (3, 1, 5)]]
+    tp = [GpuTensor.from_host(p, p.shape, reg) for p in parts]
+    for dim, ps in [(1, parts), (0, [parts[0], parts[0]]), (2, [parts[1], parts[1], parts[1]])]:
+        got = GpuTensor.concat([GpuTensor.from_host(p, p.shape, reg) for p in ps], dim)
+        ref = np.concatenate(ps, axis=dim)
+        assert got.shape() == ref.shape and np.array_equal(got.to_host(), ref)
+    with pytest.raises(b200nn.NnError) as e:
+        GpuTensor.concat([tp[0], tp[1]], 0)  # sizes differ in a dimension that is not the concatenated one
+    assert e.value.code == b200nn.ERR_SHAPE
+    with pytest.raises(b200nn.NnError) as e:
+        GpuTensor.concat([tp[0]], 3)
+    assert e.value.code == b200nn.ERR_DIM
+    with pytest.raises(b200nn.NnError):
+        GpuTensor.concat([], 0)
+    big = np.concatenate(parts, axis=1)
+    tb = GpuTensor.from_host(big, big.shape, reg)
+    chunks = tb.split(1, [2, 4, 1])
+    assert [c.shape() for c in chunks] == [(3, 2, 5), (3, 4, 5), (3, 1, 5)]
+    for c, p in zip(chunks, parts):
+        assert np.array_equal(c.to_host(), p)
+    last = tb.split(2, [1, 4])
+    assert np.array_equal(last[0].to_host(), big[:, :, :1]) and np.array_equal(last[1].to_host(), big[:, :, 1:])
+    with pytest.raises(b200nn.NnError) as e:
+        tb.split(1, [2, 4])  # sizes must add up to the dimension
+    assert e.value.code == b200nn.ERR_SHAPE
+    with pytest.raises(b200nn.NnError) as e:
+        tb.split(5, [7])
+    assert e.value.code == b200nn.ERR_DIM

@@ -18,7 +18,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(os.path.dirname(_HERE), "libb200nn.so")
 
 OK, ERR_SHAPE, ERR_DIM, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE, ERR_ARG, ERR_IO, ERR_MISSING = range(9)
-ACT_NONE, ACT_GELU_TANH, ACT_GELU_SIGMOID, ACT_RELU = range(4)
+ACT_NONE, ACT_GELU_TANH, ACT_GELU_SIGMOID, ACT_RELU, ACT_SILU, ACT_SIGMOID = range(6)
 GELU_SIGMOID, QUANT_LM_HEAD, ARGMAX_LAST, STOP_ON_EOS, TOKENS_ONLY, WEIGHTS_OUT_IN = 1, 2, 4, 8, 16, 32
 PROF_NAMES = ("embed", "layernorm", "linear", "attention", "lm_head", "argmax")
 
@@ -114,6 +114,7 @@ def load_library() -> C.CDLL:
             "b200nn_multi_head_flash_attention": (i32, [vp, vp, vp, vp, sz, sz, sz, i32, vpp]),
             "b200nn_attention_kv": (i32, [vp, vp, vp, vp, i32, sz, vpp]),
             "b200nn_int4_matmul": (i32, [vp, vp, _f32p, sz, sz, sz, vpp]),
+            "b200nn_matmul": (i32, [vp, vp, vp, vpp]),
             "b200nn_linear_create": (i32, [vp, _f32p, _f32p, sz, sz, vpp]),
             "b200nn_linear_forward": (i32, [vp, vp, vpp]), "b200nn_linear_forward_fused": (i32, [vp, vp, i32, vpp]),
             "b200nn_linear_destroy": (None, [vp]),

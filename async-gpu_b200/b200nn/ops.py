@@ -5,7 +5,7 @@ import ctypes as C
 
 import numpy as np
 
-from . import (ACT_GELU_SIGMOID, ACT_GELU_TANH, ACT_RELU, ERR_SHAPE, GpuTensor, KernelRegistry, NnError, _f32,
+from . import (ACT_GELU_SIGMOID, ACT_GELU_TANH, ACT_RELU, ACT_SIGMOID, ACT_SILU, ERR_SHAPE, GpuTensor, KernelRegistry, NnError, _f32,
                _f32p, _out, _u32p, load_library)
 
 
@@ -80,6 +80,45 @@ def relu(x, reg):
     return _act(x, ACT_RELU, reg)
 
 
+def silu(x, reg):
+    """``ops::silu`` (ops/activation.rs:21-26): x * sigmoid(x)."""
+    return _act(x, ACT_SILU, reg)
+
+
+def sigmoid(x, reg):
+    """``ops::sigmoid`` (ops/activation.rs:28-33)."""
+    return _act(x, ACT_SIGMOID, reg)
+
+
+def matmul(a: GpuTensor, b: GpuTensor, reg: KernelRegistry):
+    """``ops::matmul`` (ops/gemm.rs:20-212): [M,K] x [K,N] -> [M,N] on device tensors."""
+    h = C.c_void_p()
+    return _out(reg, reg.lib.b200nn_matmul(reg.h, a.h, b.h, C.byref(h)), h)
+
+
+def layer_norm_residual(x, residual, gamma, beta, eps, reg):
+    """``ops::layer_norm_residual`` (ops/norm.rs:88-246): LayerNorm(x + residual); the sum itself is not kept."""
+    return layer_norm_residual_dual(x, residual, gamma, beta, eps, reg)[1]
+
+
+def elementwise_add_out(a, b, reg):
+    """``ops::elementwise_add_out`` (ops/reshape.rs:219-290): a + b into a new tensor."""
+    if a.numel() != b.numel():
+        raise NnError(ERR_SHAPE, f"ShapeMismatch: expected same numel, a has {a.numel()}, b has {b.numel()}")
+    out = a.clone_tensor()
+    elementwise_add(out, b, reg)
+    return out
+
+
+def embedding_lookup(wte: GpuTensor, wpe: GpuTensor, token_ids, seq_len, reg):
+    """``ops::embedding_lookup`` (ops/reshape.rs:301-335): out[p] = wte[tok[p]] + wpe[p] for the first
+    ``seq_len`` ids.  The tables are device tensors; the layer form that keeps them is ``Embedding``."""
+    from .layers import Embedding
+    v, d = wte.shape()
+    e = Embedding(wte.to_host(), wpe.to_host(), v, wpe.shape()[0], d, reg)
+    return e.forward_tokens(np.asarray(token_ids, dtype=np.uint32)[:seq_len])
+
+
 def bias_add(data, bias, reg):
     reg.check(reg.lib.b200nn_bias_add(reg.h, data.h, bias.h))
 
@@ -103,6 +142,13 @@ def multi_head_flash_attention(q, k, v, seq_len, n_heads, d_head, causal, reg):
     h = C.c_void_p()
     return _out(reg, reg.lib.b200nn_multi_head_flash_attention(reg.h, q.h, k.h, v.h, seq_len, n_heads, d_head,
                                                                int(causal), C.byref(h)), h)
+
+
+def scaled_dot_product_attention(q, k, v, causal, reg):
+    """``ops::scaled_dot_product_attention`` (ops/attention.rs:17-103): one head, q, k, v [seq_len, d_head]."""
+    if len(q.shape()) != 2 or len(k.shape()) != 2 or len(v.shape()) != 2:
+        raise NnError(ERR_SHAPE, "ShapeMismatch: expected 2D tensors [seq_len, d_head]")
+    return scaled_dot_product_attention_kv(q, k, v, causal, k.shape()[0] - q.shape()[0], reg)
 
 
 def scaled_dot_product_attention_kv(q, k, v, causal, q_offset, reg):

@@ -47,11 +47,37 @@ extern "C" int32_t b200nn_layer_norm_residual_dual(b200nn_ctx *ctx, const b200nn
 
 extern "C" int32_t b200nn_activation(b200nn_ctx *ctx, const b200nn_tensor *x, int32_t act, b200nn_tensor **out) {
     if (!ctx || !x || !out) return B200NN_ERR_ARG;
-    if (act < B200NN_ACT_NONE || act > B200NN_ACT_RELU) return set_error(ctx, B200NN_ERR_UNSUPPORTED, "unknown activation");
+    if (act < B200NN_ACT_NONE || act > B200NN_ACT_SIGMOID) return set_error(ctx, B200NN_ERR_UNSUPPORTED, "unknown activation");
     b200nn_tensor *y = nullptr;
     TRY(tensor_alloc(ctx, x->shape, false, &y));
     int rc = launch_activation(ctx, x->data(), y->data(), x->numel, act);
     if (rc != B200NN_OK) { delete y; return rc; }
+    *out = y;
+    return B200NN_OK;
+}
+
+// ops::matmul (ops/gemm.rs:20-36): [M,K] x [K,N]; b is used where it lies as a [K,N] weight of the f32 FMA kernels.
+extern "C" int32_t b200nn_matmul(b200nn_ctx *ctx, const b200nn_tensor *a, const b200nn_tensor *b, b200nn_tensor **out) {
+    if (!ctx || !a || !b || !out) return B200NN_ERR_ARG;
+    if (a->shape.size() != 2 || b->shape.size() != 2)
+        return set_error(ctx, B200NN_ERR_SHAPE, "matmul: expected 2D tensors");
+    if (a->shape[1] != b->shape[0])
+        return set_error(ctx, B200NN_ERR_SHAPE, "matmul: a is [" + std::to_string(a->shape[0]) + "," + std::to_string(a->shape[1]) +
+                                                    "], b is [" + std::to_string(b->shape[0]) + "," + std::to_string(b->shape[1]) + "]");
+    const size_t M = a->shape[0], K = a->shape[1], N = b->shape[1];
+    b200nn_tensor *y = nullptr;
+    TRY(tensor_alloc(ctx, {M, N}, M == 0 || N == 0 || K == 0, &y));
+    if (M && N && K) {
+        F32Weight w;
+        w.K = (int)K;
+        w.N = (int)N;
+        w.w_kn = b->buf; // shared, not copied; no fp16 copy: the FMA kernels run
+        Epilogue e;
+        e.out = y->data();
+        e.ldo = (int)N;
+        int rc = launch_f32_linear(ctx, w, a->data(), false, (int)M, e);
+        if (rc != B200NN_OK) { delete y; return rc; }
+    }
     *out = y;
     return B200NN_OK;
 }

@@ -32,7 +32,7 @@ extern "C" int32_t b200nn_linear_forward_fused(b200nn_linear *l, const b200nn_te
     if (last_dim(x) != (size_t)l->l.K) // linear.rs:284-293
         return set_error(ctx, B200NN_ERR_SHAPE, "Linear: expected last dimension " + std::to_string(l->l.K) + ", got " +
                                                     std::to_string(last_dim(x)));
-    if (act < B200NN_ACT_NONE || act > B200NN_ACT_RELU) return set_error(ctx, B200NN_ERR_UNSUPPORTED, "unknown activation");
+    if (act < B200NN_ACT_NONE || act > B200NN_ACT_SIGMOID) return set_error(ctx, B200NN_ERR_UNSUPPORTED, "unknown activation");
     b200nn_tensor *o = nullptr;
     TRY(tensor_alloc(ctx, out_shape(x, l->l.N), false, &o));
     Epilogue e;

@@ -29,6 +29,8 @@ __device__ __forceinline__ float apply_act(float v, int act) {
         case B200NN_ACT_GELU_TANH: return gelu_tanh_f(v);
         case B200NN_ACT_GELU_SIGMOID: return gelu_sigmoid_f(v);
         case B200NN_ACT_RELU: return fmaxf(v, 0.0f);
+        case B200NN_ACT_SILU: return v / (1.0f + __expf(-v));
+        case B200NN_ACT_SIGMOID: return 1.0f / (1.0f + __expf(-v));
         default: return v;
     }
 }

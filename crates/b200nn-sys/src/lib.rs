@@ -26,6 +26,8 @@ pub const B200NN_ACT_NONE: i32 = 0;
 pub const B200NN_ACT_GELU_TANH: i32 = 1;
 pub const B200NN_ACT_GELU_SIGMOID: i32 = 2;
 pub const B200NN_ACT_RELU: i32 = 3;
+pub const B200NN_ACT_SILU: i32 = 4;
+pub const B200NN_ACT_SIGMOID: i32 = 5;
 
 /// Model / generation flags.
 pub const B200NN_GELU_SIGMOID: u32 = 1 << 0;
@@ -290,6 +292,12 @@ extern "C" {
         v: *const b200nn_tensor,
         causal: i32,
         q_offset: usize,
+        out: *mut *mut b200nn_tensor,
+    ) -> i32;
+    pub fn b200nn_matmul(
+        ctx: *mut b200nn_ctx,
+        a: *const b200nn_tensor,
+        b: *const b200nn_tensor,
         out: *mut *mut b200nn_tensor,
     ) -> i32;
     pub fn b200nn_int4_matmul(

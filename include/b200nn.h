@@ -51,7 +51,9 @@ enum {
 };
 
 /* Activation selector (GH/nn/layers/linear.rs:24-33 `Activation`). */
-enum { B200NN_ACT_NONE = 0, B200NN_ACT_GELU_TANH = 1, B200NN_ACT_GELU_SIGMOID = 2, B200NN_ACT_RELU = 3 };
+/* Activation (layers/linear.rs:24-33): Gelu (tanh form, or the sigmoid form of gelu_forward_v2), Relu, Silu, Sigmoid */
+enum { B200NN_ACT_NONE = 0, B200NN_ACT_GELU_TANH = 1, B200NN_ACT_GELU_SIGMOID = 2, B200NN_ACT_RELU = 3, B200NN_ACT_SILU = 4,
+       B200NN_ACT_SIGMOID = 5 };
 
 /* Model / generation flags. */
 enum {
@@ -209,6 +211,9 @@ B200NN_API int32_t b200nn_multi_head_flash_attention(b200nn_ctx *ctx, const b200
 B200NN_API int32_t b200nn_attention_kv(b200nn_ctx *ctx, const b200nn_tensor *q, const b200nn_tensor *k,
                                        const b200nn_tensor *v, int32_t causal, size_t q_offset, b200nn_tensor **out);
 /* ops::int4_matmul (ops/gemm.rs:1186-1266): quantise B [K,N] on the host, then A[M,K] x dequant(B). */
+/* ops::matmul (ops/gemm.rs:20-212): a [M,K] x b [K,N] -> [M,N], both device tensors, f32 FMA arithmetic
+ * (the weights of a Linear are better held by b200nn_linear_create, which keeps them in kernel layouts). */
+B200NN_API int32_t b200nn_matmul(b200nn_ctx *ctx, const b200nn_tensor *a, const b200nn_tensor *b, b200nn_tensor **out);
 B200NN_API int32_t b200nn_int4_matmul(b200nn_ctx *ctx, const b200nn_tensor *a, const float *b_host, size_t k, size_t n,
                                       size_t group, b200nn_tensor **out);
 

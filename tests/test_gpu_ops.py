@@ -358,3 +358,53 @@ def test_tensor_transpose_concat_split(reg):
     with pytest.raises(b200nn.NnError) as e:
         tb.split(5, [7])
     assert e.value.code == b200nn.ERR_DIM
+
+
+def test_ops_matmul_activations_and_small_wrappers(reg):
+    """ops::matmul (gemm.rs:20-212), the Activation kinds Silu and Sigmoid (linear.rs:24-33, activation.rs:21-33),
+    scaled_dot_product_attention, layer_norm_residual, elementwise_add_out, embedding_lookup: against numpy."""
+    rng = np.random.default_rng(33)
+    for m, k, n in [(1, 64, 5), (3, 130, 257), (7, 768, 96), (200, 96, 33)]:
+        a = rng.standard_normal((m, k)).astype(np.float32)
+        b = rng.standard_normal((k, n)).astype(np.float32)
+        y = ops.matmul(GpuTensor.from_host(a, a.shape, reg), GpuTensor.from_host(b, b.shape, reg), reg).to_host()
+        ref = a.astype(np.float64) @ b.astype(np.float64)
+        assert y.shape == (m, n) and np_ref.rel_rms(y, ref) < 1e-5
+    with pytest.raises(b200nn.NnError) as e:
+        ops.matmul(GpuTensor.from_host(a, a.shape, reg), GpuTensor.from_host(a, a.shape, reg), reg)
+    assert e.value.code == b200nn.ERR_SHAPE
+    x = np.linspace(-6, 6, 999).astype(np.float32)
+    t = GpuTensor.from_host(x, x.shape, reg)
+    sig = 1.0 / (1.0 + np.exp(-x.astype(np.float64)))
+    assert np.abs(ops.sigmoid(t, reg).to_host() - sig).max() < 1e-6
+    assert np.abs(ops.silu(t, reg).to_host() - x * sig).max() < 1e-5
+    # Linear::forward_fused with the two kinds (more than four rows: tensor-core path; one row: GEMV)
+    w = (rng.standard_normal((40, 64)) * 0.1).astype(np.float32)
+    bias = rng.standard_normal(40).astype(np.float32)
+    lin = b200nn.Linear(w, bias, 64, 40, reg)
+    for rows in (1, 9):
+        xi = rng.standard_normal((rows, 64)).astype(np.float32)
+        pre = xi.astype(np.float64) @ w.T.astype(np.float64) + bias
+        got = lin.forward_fused(GpuTensor.from_host(xi, xi.shape, reg), b200nn.ACT_SILU).to_host()
+        assert np.abs(got - pre / (1 + np.exp(-pre))).max() < (1e-5 if rows == 1 else 5e-3)
+        got = lin.forward_fused(GpuTensor.from_host(xi, xi.shape, reg), b200nn.ACT_SIGMOID).to_host()
+        assert np.abs(got - 1 / (1 + np.exp(-pre))).max() < (1e-5 if rows == 1 else 2e-3)
+    # one head, full causal attention == the kv form with no offset
+    q, k, v = [rng.standard_normal((33, 64)).astype(np.float32) for _ in range(3)]
+    tq, tk, tv = [GpuTensor.from_host(z, z.shape, reg) for z in (q, k, v)]
+    full = ops.scaled_dot_product_attention(tq, tk, tv, True, reg).to_host()
+    ref = oracle.mha(q, oracle.f16_round(k)[None], oracle.f16_round(v)[None], 1, 64, 33, 0, 33)
+    assert np.abs(full - ref).max() < 1e-4
+    # LayerNorm(x + r), the sum not kept; a + b into a new tensor
+    xr, rr = rng.standard_normal((5, 96)).astype(np.float32), rng.standard_normal((5, 96)).astype(np.float32)
+    g, be = rng.standard_normal(96).astype(np.float32), rng.standard_normal(96).astype(np.float32)
+    tg, tb = GpuTensor.from_host(g, g.shape, reg), GpuTensor.from_host(be, be.shape, reg)
+    ta, tr = GpuTensor.from_host(xr, xr.shape, reg), GpuTensor.from_host(rr, rr.shape, reg)
+    nrm = ops.layer_norm_residual(ta, tr, tg, tb, 1e-5, reg).to_host()
+    assert np.abs(nrm - oracle.layer_norm(xr + rr, g, be).reshape(5, 96)).max() < 2e-4
+    s = ops.elementwise_add_out(ta, tr, reg)
+    assert np.array_equal(s.to_host(), xr + rr) and np.array_equal(ta.to_host(), xr)
+    wte, wpe = rng.standard_normal((11, 8)).astype(np.float32), rng.standard_normal((6, 8)).astype(np.float32)
+    ids = np.array([3, 0, 10, 7], dtype=np.uint32)
+    out = ops.embedding_lookup(GpuTensor.from_host(wte, wte.shape, reg), GpuTensor.from_host(wpe, wpe.shape, reg), ids, 4, reg)
+    assert np.array_equal(out.to_host(), wte[ids] + wpe[:4])

@@ -382,7 +382,7 @@ from .layers import (Embedding, Int4Linear, LayerNorm, Linear, MultiHeadAttentio
                      GELU)
 from .gpt2 import (Gpt2Config, Gpt2Model, Int4Gpt2Model, KvCache, DecodeSession, TransformerBlock,  # noqa: E402
                    Int4TransformerBlock)
-from .sampling import SimpleRng, top_k_sample  # noqa: E402
+from .sampling import SimpleRng, top_k_sample, argmax, softmax_max_prob  # noqa: E402
 from .tokenizer import Gpt2Tokenizer, TokenizerError, GPT2_VOCAB_SIZE, ENDOFTEXT_TOKEN_ID  # noqa: E402
 from .checkpoint import (SafeTensorsFile, TensorInfo, list_tensors, load_all_tensors, load_gpt2_weights,  # noqa: E402
                          load_int4_tensors, TensorData, WeightMapping, LoadedWeights, map_weight, map_weight_t,

@@ -413,6 +413,10 @@ class TransformerBlock:
 
     forward_auto_fused = forward  # the fused epilogues are always on (gpt2.rs:206-243)
 
+    def forward_auto_fused(self, x: GpuTensor) -> GpuTensor:
+        """``TransformerBlock::forward_auto_fused`` (gpt2.rs:206-247): the fused epilogues are always on here."""
+        return self.forward(x)
+
     def forward_cached(self, x: GpuTensor, cached_k, cached_v, kv_len: int):
         """``forward_cached(input, cached_k, cached_v, kv_len) -> (output, new_k, new_v)`` (gpt2.rs:249-288);
         cached_k / cached_v: [n_head][kv_len*64]; new_k / new_v: [n_head, new_len*64]."""

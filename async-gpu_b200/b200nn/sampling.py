@@ -26,3 +26,19 @@ def top_k_sample(logits, k: int, temperature: float, rng: SimpleRng) -> int:
     if rc != 0:
         raise NnError(rc, "top_k_sample: empty logits or k == 0")
     return int(tok.value)
+
+
+def argmax(data) -> int:
+    """``argmax`` (gpt2.rs:991-997): Rust's ``max_by`` keeps the LAST maximum on ties; an empty slice gives 0.
+    (On the device the same rule is the flag ``ARGMAX_LAST``; the CPU reference of the test harness keeps
+    the first.)"""
+    a = np.ravel(np.asarray(data, dtype=np.float32))
+    if a.size == 0:
+        return 0
+    return int(a.size - 1 - np.argmax(a[::-1]))
+
+
+def softmax_max_prob(logits) -> float:
+    """``softmax_max_prob`` (gpt2.rs:983-988): the probability of the most likely token, in f32 as there."""
+    a = np.ravel(np.asarray(logits, dtype=np.float32))
+    return float(np.float32(1.0) / np.sum(np.exp(a - a.max(), dtype=np.float32), dtype=np.float32))

@@ -121,3 +121,15 @@ def test_synthetic_weights_from_simple_rng_are_reproducible_from_the_reference_g
     # the default source is unchanged
     assert np.array_equal(synth.gpt2_weights(cfg, base_seed=77)["wte"],
                           (np.random.Generator(np.random.PCG64(78)).standard_normal((11, 8), dtype=np.float32) * np.float32(0.02)))
+
+
+def test_argmax_and_softmax_max_prob_helpers():
+    """gpt2.rs:983-997: the last maximum wins a tie (Rust max_by), an empty slice gives 0; the confidence of
+    early exit is 1 / sum exp(x - max) in f32."""
+    assert b200nn.argmax([1.0, 5.0, 2.0, 5.0, 0.0]) == 3
+    assert b200nn.argmax([7.0]) == 0 and b200nn.argmax([]) == 0
+    assert b200nn.argmax([-1.0, -1.0, -1.0]) == 2
+    x = np.array([0.5, 2.0, -1.0, 2.0], dtype=np.float32)
+    want = 1.0 / np.exp(x.astype(np.float64) - 2.0).sum()
+    assert abs(b200nn.softmax_max_prob(x) - want) < 1e-6
+    assert abs(b200nn.softmax_max_prob([3.0]) - 1.0) < 1e-7

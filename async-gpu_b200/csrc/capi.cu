@@ -93,7 +93,7 @@ extern "C" int32_t b200nn_ctx_set_tuning(b200nn_ctx *ctx, const char *key, int32
     if (!ctx || !key) return B200NN_ERR_ARG;
     if (!strcmp(key, "tc_mb")) ctx->tc_mb = value;
     else if (!strcmp(key, "tc_splits")) ctx->tc_splits = value;
-    else if (!strcmp(key, "tc_min_kb")) ctx->tc_min_kb = value < 1 ? 1 : value;
+    else if (!strcmp(key, "tc_min_kb")) ctx->tc_min_kb = value < 0 ? 0 : value;
     else if (!strcmp(key, "tc_min_kb_cluster")) ctx->tc_min_kb_cluster = value < 1 ? 1 : value;
     else if (!strcmp(key, "pdl")) ctx->pdl = value ? 1 : 0;
     else if (!strcmp(key, "f32_tc")) ctx->f32_tc = value < 0 ? 2 : (value > 2 ? 2 : value);

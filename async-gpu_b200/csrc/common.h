@@ -53,8 +53,10 @@ struct b200nn_ctx {
     void *encode_tiled = nullptr; // cuTensorMapEncodeTiled, resolved through the runtime
     int tc_mb = 0, tc_splits = 0; // tensor-core GEMM tuning overrides (0 = automatic)
     int tc_min_kb_cluster = 6;    // the same for splits that run as a cluster (their partial tiles cross shared memory)
-    int tc_min_kb = 3;            // fewest 64-wide K blocks a K split may get (3 measured best at 16..128 rows:
-                                  // 1.69 against 1.76 ms per GPT-2 XL step at 32 rows with 4; no difference at 256)
+    int tc_min_kb = 0;            // fewest 64-wide K blocks a K split of the residual epilogue may get; 0 = by row count:
+                                  // 2 up to 64 rows, 3 above (GPT-2 XL step, ms with 2 / 3: 32 rows 1.717 / 1.723,
+                                  // 48 rows 2.164 / 2.202, 64 rows 2.433 / 2.475, 96 rows 3.099 / 3.085, 128 rows
+                                  // 3.404 / 3.399; 4 is slower everywhere below 256 rows, where nothing splits)
     long long *trace = nullptr;  // optional device buffer for in-kernel time stamps (measurement aid)
     int attn_tc = 1;              // prefill attention with fp16 q and output runs on the tensor cores
     int attn_stream = 1;          // decode attention over many (sequence, head) pairs uses the TMA-fed kernel

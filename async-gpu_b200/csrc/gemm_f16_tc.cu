@@ -508,7 +508,7 @@ int launch_cfg(b200nn_ctx *ctx, const WOperand &w, const __half *x, int M, const
     const int target = ctx->sm_count;
     int splits;
     if (epi.mode == EPI_RESID)
-        splits = std::min(std::max(1, target / base_ctas), std::max(1, k_blocks / ctx->tc_min_kb));
+        splits = std::min(std::max(1, target / base_ctas), std::max(1, k_blocks / (ctx->tc_min_kb > 0 ? ctx->tc_min_kb : 3)));
     else
         splits = std::min(std::min(8, std::max(1, target / base_ctas)), std::max(1, k_blocks / ctx->tc_min_kb_cluster));
     splits = std::max(1, std::min(splits, 32));

@@ -420,8 +420,9 @@ int launch_cfg(b200nn_ctx *ctx, const Int4Weight &w, const __half *x, int M, con
     // override) go through scratch, where the last block to arrive makes a second pass.
     const int target = ctx->sm_count * ctas_per_sm;
     int splits = 1;
+    const int min_kb = ctx->tc_min_kb > 0 ? ctx->tc_min_kb : (M <= 64 ? 2 : 3);
     if (epi.mode == EPI_RESID)
-        splits = std::min(std::max(1, target / base_ctas), std::max(1, w.k_blocks / ctx->tc_min_kb));
+        splits = std::min(std::max(1, target / base_ctas), std::max(1, w.k_blocks / min_kb));
     else
         splits = std::min(std::min(8, std::max(1, target / base_ctas)), std::max(1, w.k_blocks / ctx->tc_min_kb_cluster));
     splits = std::max(1, std::min(splits, 32));

@@ -103,7 +103,7 @@ B200NN_API uint64_t b200nn_ctx_launch_count(b200nn_ctx *ctx);
 B200NN_API int32_t b200nn_ctx_set_gemv_max_rows(b200nn_ctx *ctx, int32_t rows);
 /* Tuning overrides of the tensor-core GEMM's launch policy, for measurements: "tc_mb" (cap of the
  * token-tile width: 16..256, 0 = default), "tc_splits" (K splits, 0 = automatic), "tc_min_kb"
- * (fewest 64-wide K blocks per split; default 3), "tc_min_kb_cluster" (the same for splits that run as
+ * (fewest 64-wide K blocks per split; 0 = default: 2 up to 64 rows, else 3), "tc_min_kb_cluster" (the same for splits that run as
  * a cluster; default 6, measured best among 3, 4, 6, 8), "gemv_max_rows", "pdl" (programmatic dependent launch on/off),
  * "attn_tc" (0 = run fp16 prefill attention on the CUDA cores instead of the tensor cores),
  * "attn_stream" (0 = never use the TMA-fed decode-attention kernel), "attn_stream_min10" (tenths of

@@ -1,6 +1,8 @@
 """Builds libb200nn.so (CUDA, sm_100a only) in this directory with nvcc.
 
 Usage: python build.py [--force] [--verbose]
+Environment: NVCC (compiler path), B200NN_TRACE (in-kernel time stamps), B200NN_CFLAGS (extra
+compiler flags, e.g. a measurement switch such as -DB200NN_ATTN_PROBE=1; rebuild with --force).
 The library needs only the CUDA runtime (linked statically); it resolves the one driver entry
 point it uses (tensor-map encoding) through the runtime at context creation.
 """
@@ -17,7 +19,7 @@ INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 OUT = os.path.join(HERE, "libb200nn.so")
 OBJ_DIR = os.path.join(HERE, "build")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-FLAGS = (["-DB200NN_TRACE"] if os.environ.get("B200NN_TRACE") else []) + [
+FLAGS = (["-DB200NN_TRACE"] if os.environ.get("B200NN_TRACE") else []) + os.environ.get("B200NN_CFLAGS", "").split() + [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "-I", INCLUDE, "-I", CSRC,
 ]

@@ -178,6 +178,11 @@ decode_attn_kernel(const QT *__restrict__ q, int ldq, const __half *__restrict__
 // (4 lane groups x 8 lanes, merged with shuffles at the end), so there is no block-level
 // synchronisation at all after start-up.  Every mbarrier wait is bounded.
 // ---------------------------------------------------------------------------------------------
+// B200NN_ATTN_PROBE (compile-time, default 0): builds of decode_attn_stream_kernel without parts of its
+// arithmetic, to time the TMA ring alone.  Any other value than 0 gives wrong results.
+#ifndef B200NN_ATTN_PROBE
+#define B200NN_ATTN_PROBE 0
+#endif
 namespace stream_attn {
 constexpr int WARPS = 8, NST = 3, ROWS = 32;
 constexpr int STAGE_BYTES = 2 * ROWS * 128 + 256; // K rows, V rows, query row (fp16 or f32)
@@ -310,6 +315,9 @@ decode_attn_stream_kernel(const QT *__restrict__ q, int ldq, const __half *__res
         const int rows = min(ROWS, ctx - mt.y * ROWS);
         const uint4 *ks = reinterpret_cast<const uint4 *>(st);
         const uint4 *vs = reinterpret_cast<const uint4 *>(st + ROWS * 128);
+#if B200NN_ATTN_PROBE == 1
+        if (rows < 0) // measurement build: no arithmetic, the warp only waits for its stages and releases them
+#endif
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             constexpr int R = 4;
@@ -323,7 +331,9 @@ decode_attn_stream_kernel(const QT *__restrict__ q, int ldq, const __half *__res
                 vr[r] = kr[r];
                 if (valid[r]) {
                     kr[r] = ks[row * 8 + c];
+#if B200NN_ATTN_PROBE != 3
                     vr[r] = vs[row * 8 + c];
+#endif
                 }
             }
             float sc[R];
@@ -353,10 +363,16 @@ decode_attn_stream_kernel(const QT *__restrict__ q, int ldq, const __half *__res
             for (int r = 0; r < R; ++r) {
                 const float p = valid[r] ? exp2f(sc[r] - m_new) : 0.0f;
                 l += p;
+#if B200NN_ATTN_PROBE == 2   // measurement build: V rows read, no conversion and no p·V
+                acc[r] += p * __uint_as_float(vr[r].x ^ vr[r].y ^ vr[r].z ^ vr[r].w);
+#elif B200NN_ATTN_PROBE == 3 // measurement build: V rows not read from shared memory either
+                acc[r] += p;
+#else
                 float vf[8];
                 half8_to_float(vr[r], vf);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) acc[i] = fmaf(p, vf[i], acc[i]);
+#endif
             }
             m = m_new;
         }

@@ -269,7 +269,8 @@ decode_attn_stream_kernel(const QT *__restrict__ q, int ldq, const __half *__res
     };
     open_unit((unsigned)gw);
     int issued = 0, consumed = 0;   // chunks requested / finished by this warp
-    float m = NEG_BIG, l = 0.0f, acc[8], qf[8];
+    float m = NEG_BIG, l = 0.0f;
+    float2 acc2[4], qf2[4]; // dims (2i, 2i+1) of this lane's eight: accumulator and scaled query
     bool ok = true;
 
     while (true) {
@@ -307,10 +308,12 @@ decode_attn_stream_kernel(const QT *__restrict__ q, int ldq, const __half *__res
             m = NEG_BIG;
             l = 0.0f;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+            for (int i = 0; i < 4; ++i) acc2[i] = make_float2(0.0f, 0.0f);
             const QT *qs = reinterpret_cast<const QT *>(st + 2 * ROWS * 128);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) qf[i] = load_as_float<QT>(qs, c * 8 + i) * ATT_SCALE_LOG2E;
+            for (int i = 0; i < 4; ++i)
+                qf2[i] = make_float2(load_as_float<QT>(qs, c * 8 + 2 * i) * ATT_SCALE_LOG2E,
+                                     load_as_float<QT>(qs, c * 8 + 2 * i + 1) * ATT_SCALE_LOG2E);
         }
         const int rows = min(ROWS, ctx - mt.y * ROWS);
         const uint4 *ks = reinterpret_cast<const uint4 *>(st);
@@ -339,12 +342,12 @@ decode_attn_stream_kernel(const QT *__restrict__ q, int ldq, const __half *__res
             float sc[R];
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-                float kf[8];
-                half8_to_float(kr[r], kf);
-                float t = 0.0f;
+                // packed f32x2 FMAs: even dims in .x, odd dims in .y, one add at the end
+                const __half2 *kh = reinterpret_cast<const __half2 *>(&kr[r]);
+                float2 t2 = make_float2(0.0f, 0.0f);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) t = fmaf(qf[i], kf[i], t);
-                sc[r] = t;
+                for (int i = 0; i < 4; ++i) t2 = __ffma2_rn(qf2[i], __half22float2(kh[i]), t2);
+                sc[r] = t2.x + t2.y;
             }
 #pragma unroll
             for (int o = 1; o < 8; o <<= 1) {
@@ -358,20 +361,20 @@ decode_attn_stream_kernel(const QT *__restrict__ q, int ldq, const __half *__res
             const float corr = exp2f(m - m_new);
             l *= corr;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] *= corr;
+            for (int i = 0; i < 4; ++i) acc2[i] = __fmul2_rn(acc2[i], make_float2(corr, corr));
 #pragma unroll
             for (int r = 0; r < R; ++r) {
                 const float p = valid[r] ? exp2f(sc[r] - m_new) : 0.0f;
                 l += p;
 #if B200NN_ATTN_PROBE == 2   // measurement build: V rows read, no conversion and no p·V
-                acc[r] += p * __uint_as_float(vr[r].x ^ vr[r].y ^ vr[r].z ^ vr[r].w);
+                acc2[r].x += p * __uint_as_float(vr[r].x ^ vr[r].y ^ vr[r].z ^ vr[r].w);
 #elif B200NN_ATTN_PROBE == 3 // measurement build: V rows not read from shared memory either
-                acc[r] += p;
+                acc2[r].x += p;
 #else
-                float vf[8];
-                half8_to_float(vr[r], vf);
+                const __half2 *vh = reinterpret_cast<const __half2 *>(&vr[r]);
+                const float2 p2 = make_float2(p, p);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) acc[i] = fmaf(p, vf[i], acc[i]);
+                for (int i = 0; i < 4; ++i) acc2[i] = __ffma2_rn(p2, __half22float2(vh[i]), acc2[i]);
 #endif
             }
             m = m_new;
@@ -379,6 +382,9 @@ decode_attn_stream_kernel(const QT *__restrict__ q, int ldq, const __half *__res
         __syncwarp(); // every lane has read the stage: it may be requested again
         ++consumed;
         if (u_last) {
+            float acc[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { acc[2 * i] = acc2[i].x; acc[2 * i + 1] = acc2[i].y; }
             // merge the four lane groups (lanes 8 and 16 apart hold the same 8 dims)
 #pragma unroll
             for (int off = 8; off <= 16; off <<= 1) {

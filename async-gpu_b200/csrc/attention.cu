@@ -184,20 +184,25 @@ decode_attn_kernel(const QT *__restrict__ q, int ldq, const __half *__restrict__
 #define B200NN_ATTN_PROBE 0
 #endif
 namespace stream_attn {
-constexpr int WARPS = 8, NST = 3, ROWS = 32;
-constexpr int STAGE_BYTES = 2 * ROWS * 128 + 256; // K rows, V rows, query row (fp16 or f32)
-constexpr int SMEM_BYTES = WARPS * NST * STAGE_BYTES + 128;
+// Two shapes of the block: 8 warps with 32-row stages (fewest pairs per warp needed), and 16 warps with
+// 16-row stages (same bytes in flight; a warp's own instruction stream is what limits it, so twice the
+// warps hide more of the arithmetic: 52.5 against 54.3 µs per launch at 6400 pairs, but slower below
+// ~2.5 pairs per warp, where the last round of items is long).
+constexpr int NST = 3;
+__host__ __device__ constexpr int stage_bytes(int rows) { return 2 * rows * 128 + 256; } // K rows, V rows, query row (fp16 or f32)
+__host__ __device__ constexpr int smem_bytes(int warps, int rows) { return warps * NST * stage_bytes(rows) + 128; }
 constexpr uint32_t ERR_FULL = 0x51;
 constexpr int REC_FLOATS = 80; // half-item record: [0] max, [1] sum, [8..71] output (16-byte aligned parts)
 }  // namespace stream_attn
 
-template <typename QT, typename OT>
-__global__ void __launch_bounds__(256, 1)
+template <typename QT, typename OT, int WARPS, int ROWS>
+__global__ void __launch_bounds__(WARPS * 32, 1)
 decode_attn_stream_kernel(const QT *__restrict__ q, int ldq, const __half *__restrict__ kc,
                           const __half *__restrict__ vc, int H, int cap, const int *__restrict__ pos_ptr, int pos_off,
                           OT *__restrict__ out, int ldo, int n_items, int pf_items, int split_items,
                           unsigned *__restrict__ work, float *__restrict__ scratch, unsigned *__restrict__ counters, uint32_t *__restrict__ dev_err) {
     using namespace stream_attn;
+    constexpr int STAGE_BYTES = stage_bytes(ROWS);
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[WARPS][NST];
     __shared__ int2 meta[WARPS][NST]; // (item, chunk) held by each stage
@@ -322,7 +327,7 @@ decode_attn_stream_kernel(const QT *__restrict__ q, int ldq, const __half *__res
         if (rows < 0) // measurement build: no arithmetic, the warp only waits for its stages and releases them
 #endif
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
+        for (int half = 0; half < ROWS / 16; ++half) {
             constexpr int R = 4;
             uint4 kr[R], vr[R];
             bool valid[R];
@@ -480,37 +485,45 @@ int launch_decode_attention(b200nn_ctx *ctx, const void *q, bool q_half, int ldq
     if (B <= 0) return B200NN_OK;
     int pairs = B * H;
     const size_t q_elem = q_half ? 2 : 4;
-    if (ctx->attn_stream && 10LL * pairs >= (long long)ctx->attn_stream_min10 * ctx->sm_count * stream_attn::WARPS &&
-        cap <= 255 * stream_attn::ROWS &&
+    // block shape of the TMA-fed kernel by pairs per warp of its grid: 16 warps, else 8 warps, else the split kernel
+    const bool wide = ctx->attn_stream_wide_min10 > 0 && 10LL * pairs >= (long long)ctx->attn_stream_wide_min10 * ctx->sm_count * 16;
+    const int s_warps = wide ? 16 : 8, s_rows = wide ? 16 : 32;
+    if (ctx->attn_stream && 10LL * pairs >= (long long)ctx->attn_stream_min10 * ctx->sm_count * s_warps &&
+        cap <= 255 * s_rows &&
         ((uintptr_t)q & 15) == 0 &&
         (ldq * q_elem) % 16 == 0 && ((uintptr_t)out & 15) == 0) {
         const int ldo_s = H * 64;
         unsigned *work = reinterpret_cast<unsigned *>(ctx->dev_err) + 2;
         // records and counters of the half-items the grid finishes on (two halves of n_warps items)
-        const size_t n_w = (size_t)ctx->sm_count * stream_attn::WARPS;
+        const size_t n_w = (size_t)ctx->sm_count * s_warps;
         TRY(ensure_scratch(ctx, n_w * 2 * stream_attn::REC_FLOATS * sizeof(float), n_w));
         // items whose cached rows are requested into L2 ahead of the dependency wait
         const size_t item_bytes = (size_t)2 * cap * 128;
         const int pf_items = (int)std::min<size_t>((size_t)pairs, ((size_t)ctx->kv_prefetch_mb << 20) / item_bytes);
-#define DS(QT, OT)                                                                                                  \
+#define DS2(QT, OT, W, R)                                                                                            \
     {                                                                                                                \
         static bool attr_done[16] = {};                                                                              \
         if (!attr_done[ctx->device & 15]) {                                                                          \
-            CK(ctx, cudaFuncSetAttribute(decode_attn_stream_kernel<QT, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                         stream_attn::SMEM_BYTES));                                                  \
-            prefer_max_smem(decode_attn_stream_kernel<QT, OT>);                                                      \
+            CK(ctx, cudaFuncSetAttribute(decode_attn_stream_kernel<QT, OT, W, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         stream_attn::smem_bytes(W, R)));                                            \
+            prefer_max_smem(decode_attn_stream_kernel<QT, OT, W, R>);                                                \
             attr_done[ctx->device & 15] = true;                                                                      \
         }                                                                                                            \
-        launch_pdl(ctx, decode_attn_stream_kernel<QT, OT>, dim3(ctx->sm_count), dim3(256), stream_attn::SMEM_BYTES,  \
-                   (const QT *)q, ldq, kc, vc, H, cap, pos_ptr, pos_off, (OT *)out, ldo_s, pairs, pf_items,          \
-                   std::min(ctx->attn_split_items, (int)n_w), work,                                                  \
-                   ctx->scratch, ctx->counters, ctx->dev_err);                                                       \
+        launch_pdl(ctx, decode_attn_stream_kernel<QT, OT, W, R>, dim3(ctx->sm_count), dim3(W * 32),                  \
+                   stream_attn::smem_bytes(W, R), (const QT *)q, ldq, kc, vc, H, cap, pos_ptr, pos_off, (OT *)out,   \
+                   ldo_s, pairs, pf_items, std::min(ctx->attn_split_items, (int)n_w), work, ctx->scratch,           \
+                   ctx->counters, ctx->dev_err);                                                                     \
+    }
+#define DS(QT, OT)                                                                                                   \
+    {                                                                                                                \
+        if (wide) DS2(QT, OT, 16, 16) else DS2(QT, OT, 8, 32)                                                        \
     }
         if (q_half && out_half) DS(__half, __half)
         else if (q_half) DS(__half, float)
         else if (out_half) DS(float, __half)
         else DS(float, float)
 #undef DS
+#undef DS2
         CK_LAUNCH(ctx, "decode_attn_stream_kernel");
         return B200NN_OK;
     }

@@ -102,6 +102,7 @@ extern "C" int32_t b200nn_ctx_set_tuning(b200nn_ctx *ctx, const char *key, int32
     else if (!strcmp(key, "attn_tc")) ctx->attn_tc = value ? 1 : 0;
     else if (!strcmp(key, "attn_stream")) ctx->attn_stream = value ? 1 : 0;
     else if (!strcmp(key, "attn_stream_min10")) ctx->attn_stream_min10 = value < 1 ? 1 : value;
+    else if (!strcmp(key, "attn_stream_wide_min10")) ctx->attn_stream_wide_min10 = value < 0 ? 0 : value;
     else if (!strcmp(key, "kv_prefetch_mb")) ctx->kv_prefetch_mb = value < 0 ? 0 : value;
     else if (!strcmp(key, "attn_split_items")) ctx->attn_split_items = value < 0 ? 0 : value;
     else if (!strcmp(key, "attn_blocks_per_sm")) ctx->attn_blocks_per_sm = value < 1 ? 4 : value;

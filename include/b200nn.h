@@ -107,7 +107,8 @@ B200NN_API int32_t b200nn_ctx_set_gemv_max_rows(b200nn_ctx *ctx, int32_t rows);
  * a cluster; default 6, measured best among 3, 4, 6, 8), "gemv_max_rows", "pdl" (programmatic dependent launch on/off),
  * "attn_tc" (0 = run fp16 prefill attention on the CUDA cores instead of the tensor cores),
  * "attn_stream" (0 = never use the TMA-fed decode-attention kernel), "attn_stream_min10" (tenths of
- * a (sequence, head) pair per warp of its grid from which it is used; default 20), "kv_prefetch_mb" (KV-cache
+ * a (sequence, head) pair per warp of its grid from which it is used; default 20), "attn_stream_wide_min10" (the same for
+ * its 16-warp block shape; default 25, 0 = never), "kv_prefetch_mb" (KV-cache
  * megabytes that kernel asks into L2 before its dependency wait), "attn_split_items" (items it
  * hands out as two halves at the end of the grid; 0 = none), "attn_blocks_per_sm" (blocks per SM the
  * split-context decode attention aims for when it splits the context of few pairs; default 4, measured

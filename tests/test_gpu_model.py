@@ -276,6 +276,17 @@ def test_decode_attention_streaming_kernel_many_sequences(reg):
     assert np.abs(lg_h - lg_s).max() < 2e-3
     assert (tok_h != tok_s).mean() < 0.01
     assert reg.device_error() == 0
+    # the 16-warp shape of the block (16-row stages; by default only from 2.5 pairs per warp of its grid)
+    reg.set_tuning("attn_stream_wide_min10", 1)
+    reg.set_tuning("attn_stream_min10", 5)
+    try:
+        tok_w, lg_w = run()
+    finally:
+        reg.set_tuning("attn_stream_wide_min10", 25)
+        reg.set_tuning("attn_stream_min10", 20)
+    assert np.abs(lg_w - lg_s).max() < 2e-3
+    assert (tok_w != tok_s).mean() < 0.01
+    assert reg.device_error() == 0
 
 
 @pytest.mark.parametrize("B,P", [(300, 37), (230, 270)])
@@ -309,6 +320,17 @@ def test_decode_attention_medium_batches_both_kernels(reg, B, P):
     # the two kernels add in different orders; where that moves an fp16 activation of order one by one unit
     # in the last place (1e-3), the logits move by a few 1e-3: a fifth of the path's tolerance is allowed
     assert np.abs(lg_b[same] - lg_p[same]).max() < MAX_ABS / 5
+    reg.set_tuning("attn_stream_min10", 1)
+    reg.set_tuning("attn_stream_wide_min10", 1)  # its 16-warp shape: 16-row stages, ragged last stage
+    try:
+        tok_w, lg_w = run()
+    finally:
+        reg.set_tuning("attn_stream_min10", 20)
+        reg.set_tuning("attn_stream_wide_min10", 25)
+    assert reg.device_error() == 0
+    assert (tok_b != tok_w).mean() < 0.01
+    same = (tok_b == tok_w).all(axis=1)
+    assert np.abs(lg_b[same] - lg_w[same]).max() < MAX_ABS / 5
     for b in (0, B // 2, B - 1):
         ref, lg = om.generate_cached(prompts[b], N, flags=oracle.KV_FP16, want_logits=True)
         _check_tokens(np.concatenate([prompts[b], tok_b[b]]), ref, lg, P)

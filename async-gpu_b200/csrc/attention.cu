@@ -167,12 +167,12 @@ decode_attn_kernel(const QT *__restrict__ q, int ldq, const __half *__restrict__
 // ---------------------------------------------------------------------------------------------
 // decode_attn_stream_kernel: the same computation for many (sequence, head) pairs, fed by TMA.
 //
-// One persistent block per SM, eight warps, each warp an independent pipeline: it takes
+// One persistent block per SM, WARPS (8 or 16) warps, each warp an independent pipeline: it takes
 // (sequence, head) items from a device-side work counter (whole items, then half-items for the
 // units the grid finishes on, merged through a small scratch record) and streams the item's K and V rows
-// through its own ring of shared-memory stages with bulk async copies (32 rows of K + 32 rows of V
-// per stage, 8 KB, plus the query row with the item's first stage), always two stages ahead of the
-// rows it is working on.  The memory system therefore sees ~128 KB in flight per SM regardless of
+// through its own ring of shared-memory stages with bulk async copies (ROWS = 32 or 16 rows of K and of V
+// per stage, 8 or 4 KB, plus the query row with the item's first stage), always two stages ahead of the
+// rows it is working on.  The memory system therefore sees up to ~200 KB in flight per SM regardless of
 // what the arithmetic is doing, where the plain-load kernel above stalls its loads behind its own
 // shuffles and exponentials.  A warp keeps the online-softmax state of its item in registers
 // (4 lane groups x 8 lanes, merged with shuffles at the end), so there is no block-level

@@ -63,7 +63,7 @@ struct b200nn_ctx {
     int attn_stream_min10 = 20;   // ... when there are at least this many tenths of a pair per warp of its grid
                                   // (measured: 2.7 pairs per warp 9 % faster than the split kernel, 1.35 pairs 13 % slower)
     int attn_stream_wide_min10 = 25; // ... and its 16-warp shape from this many tenths of a pair per warp of that grid (0 = never;
-                                  // GPT-2 XL, ms of attention per step with 16 / 8 warps: 256 sequences 2.49–2.52 / 2.61, 192: 2.11 / 2.05)
+                                  // GPT-2 XL, ms of attention per step with 16 / 8 warps: 256 sequences 2.49–2.52 / 2.61, 224: 2.36 / 2.33, 192: 2.11 / 2.05)
     int attn_split_items = 0;    // items the streaming decode attention hands out as two halves at the end
     int attn_blocks_per_sm = 4;  // blocks per SM the split-context decode attention aims for when it splits the context
     int kv_prefetch_mb = 64;     // KV-cache bytes the streaming decode attention asks into L2 before its wait

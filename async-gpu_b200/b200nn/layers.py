@@ -37,6 +37,13 @@ class Linear(_Module):
         self.h = C.c_void_p()
         reg.check(reg.lib.b200nn_linear_create(reg.h, wp, bp, in_features, out_features, C.byref(self.h)))
 
+    @classmethod
+    def with_codegen(cls, weight, bias, in_features, out_features, reg: KernelRegistry, codegen=None):
+        """``Linear::with_codegen`` (layers/linear.rs:94-125).  The reference hands over its run-time kernel
+        generator for ``forward_auto_fused``; the epilogues are compiled into the library here, so the
+        argument is accepted and not used."""
+        return cls(weight, bias, in_features, out_features, reg)
+
     def forward(self, x: GpuTensor) -> GpuTensor:
         h = C.c_void_p()
         return _out(self.reg, self.reg.lib.b200nn_linear_forward(self.h, x.h, C.byref(h)), h)
@@ -101,6 +108,19 @@ class LayerNorm(_Module):
         self.reg = reg
         self.h = C.c_void_p()
         reg.check(reg.lib.b200nn_layernorm_create(reg.h, gp, bp, g.size, eps, C.byref(self.h)))
+        self._g, self._b, self._gt, self._bt = g.copy(), b.copy(), None, None
+
+    def gamma(self) -> GpuTensor:
+        """``LayerNorm::gamma`` (layers/norm.rs:41-43): the scale vector as a device tensor."""
+        if self._gt is None:
+            self._gt = GpuTensor.from_host(self._g, (self._g.size,), self.reg)
+        return self._gt
+
+    def beta(self) -> GpuTensor:
+        """``LayerNorm::beta`` (layers/norm.rs:46-48): the shift vector as a device tensor."""
+        if self._bt is None:
+            self._bt = GpuTensor.from_host(self._b, (self._b.size,), self.reg)
+        return self._bt
 
     def forward(self, x: GpuTensor) -> GpuTensor:
         h = C.c_void_p()

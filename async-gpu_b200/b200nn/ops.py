@@ -96,6 +96,27 @@ def matmul(a: GpuTensor, b: GpuTensor, reg: KernelRegistry):
     return _out(reg, reg.lib.b200nn_matmul(reg.h, a.h, b.h, C.byref(h)), h)
 
 
+FUSED_GELU, FUSED_RELU = "gelu", "relu"  # ``FusedActivation`` (ops/gemm.rs:803-808)
+
+
+def matmul_fused(a: GpuTensor, b: GpuTensor, bias: GpuTensor, activation, reg: KernelRegistry):
+    """``ops::matmul_fused`` (ops/gemm.rs:814-977): activation(a [M,K] x b [K,N] + bias [N]); its GELU is the
+    sigmoid form x * sigmoid(1.702 x).  Device tensors in, a new tensor out; the product, the bias and the
+    activation run as three launches here (a Linear that keeps its weight fuses them: ``Linear.forward_fused``)."""
+    if a.ndim() != 2 or b.ndim() != 2:
+        raise NnError(ERR_SHAPE, f"ShapeMismatch: expected 2D tensors, actual a.ndim={a.ndim()}, b.ndim={b.ndim()}")
+    if a.shape()[1] != b.shape()[0]:
+        raise NnError(ERR_SHAPE, f"ShapeMismatch: expected a.shape[1]={a.shape()[1]} == b.shape[0], actual b.shape[0]={b.shape()[0]}")
+    n = b.shape()[1]
+    if bias.ndim() != 1 or bias.shape()[0] != n:
+        raise NnError(ERR_SHAPE, f"ShapeMismatch: expected bias.shape=[{n}], actual bias.shape={list(bias.shape())}")
+    if activation not in (FUSED_GELU, FUSED_RELU):
+        raise NnError(ERR_SHAPE, "activation must be FUSED_GELU or FUSED_RELU")
+    y = matmul(a, b, reg)
+    bias_add(y, bias, reg)
+    return gelu(y, reg, sigmoid_form=True) if activation == FUSED_GELU else relu(y, reg)
+
+
 def layer_norm_residual(x, residual, gamma, beta, eps, reg):
     """``ops::layer_norm_residual`` (ops/norm.rs:88-246): LayerNorm(x + residual); the sum itself is not kept."""
     return layer_norm_residual_dual(x, residual, gamma, beta, eps, reg)[1]

@@ -408,3 +408,33 @@ def test_ops_matmul_activations_and_small_wrappers(reg):
     ids = np.array([3, 0, 10, 7], dtype=np.uint32)
     out = ops.embedding_lookup(GpuTensor.from_host(wte, wte.shape, reg), GpuTensor.from_host(wpe, wpe.shape, reg), ids, 4, reg)
     assert np.array_equal(out.to_host(), wte[ids] + wpe[:4])
+
+
+@pytest.mark.gpu
+def test_matmul_fused_layernorm_accessors_and_with_codegen(reg):
+    """ops::matmul_fused (gemm.rs:814-977: bias then the sigmoid-form GELU or ReLU, with its shape errors),
+    LayerNorm::gamma / beta (norm.rs:41-48) and Linear::with_codegen (linear.rs:94-125)."""
+    rng = np.random.default_rng(91)
+    a = rng.standard_normal((6, 70)).astype(np.float32)
+    b = (rng.standard_normal((70, 45)) * 0.2).astype(np.float32)
+    bias = rng.standard_normal(45).astype(np.float32)
+    ta, tb, tbias = [GpuTensor.from_host(z, z.shape, reg) for z in (a, b, bias)]
+    pre = a.astype(np.float64) @ b.astype(np.float64) + bias
+    got = ops.matmul_fused(ta, tb, tbias, ops.FUSED_GELU, reg).to_host()
+    assert got.shape == (6, 45) and np.abs(got - pre / (1 + np.exp(-1.702 * pre))).max() < 3e-5
+    got = ops.matmul_fused(ta, tb, tbias, ops.FUSED_RELU, reg).to_host()
+    assert np.abs(got - np.maximum(pre, 0)).max() < 3e-5
+    assert np.array_equal(ta.to_host(), a) and np.array_equal(tb.to_host(), b)  # inputs untouched
+    for bad in [(ta.reshape((6, 70, 1)), tb, tbias), (ta, ta, tbias), (ta, tb, GpuTensor.from_host(a[0], (70,), reg)),
+                (ta, tb, tbias.reshape((1, 45)))]:
+        with pytest.raises(b200nn.NnError) as e:
+            ops.matmul_fused(*bad, ops.FUSED_RELU, reg)
+        assert e.value.code == b200nn.ERR_SHAPE and "ShapeMismatch" in str(e.value)
+    g, be = rng.standard_normal(96).astype(np.float32), rng.standard_normal(96).astype(np.float32)
+    ln = b200nn.LayerNorm(g, be, 1e-5, reg)
+    assert np.array_equal(ln.gamma().to_host(), g) and np.array_equal(ln.beta().to_host(), be)
+    assert ln.gamma().shape() == (96,) and ln.gamma() is ln.gamma()
+    w = (rng.standard_normal((45, 70)) * 0.2).astype(np.float32)
+    lin = b200nn.Linear.with_codegen(w, bias, 70, 45, reg, codegen=None)
+    y = lin.forward(ta).to_host()
+    assert np.abs(y - (a.astype(np.float64) @ w.T.astype(np.float64) + bias)).max() < 5e-3

@@ -379,7 +379,7 @@ def _out(reg, rc, h):
 
 from . import ops  # noqa: E402
 from .layers import (Embedding, Int4Linear, LayerNorm, Linear, MultiHeadAttention, Int4MultiHeadAttention,  # noqa: E402
-                     GELU)
+                     GELU, SiLU, Sigmoid, ReLU)
 from .gpt2 import (Gpt2Config, Gpt2Model, Int4Gpt2Model, KvCache, DecodeSession, TransformerBlock,  # noqa: E402
                    Int4TransformerBlock)
 from .sampling import SimpleRng, top_k_sample, argmax, softmax_max_prob  # noqa: E402

@@ -211,3 +211,33 @@ class GELU:
 
     def forward(self, x: GpuTensor) -> GpuTensor:
         return ops.gelu(x, self.reg, self.sigmoid_form)
+
+
+class SiLU:
+    """``SiLU::new(&registry)`` (layers/activation.rs:36-54): x * sigmoid(x)."""
+
+    def __init__(self, reg: KernelRegistry):
+        self.reg = reg
+
+    def forward(self, x: GpuTensor) -> GpuTensor:
+        return ops.silu(x, self.reg)
+
+
+class Sigmoid:
+    """``Sigmoid::new(&registry)`` (layers/activation.rs:57-75)."""
+
+    def __init__(self, reg: KernelRegistry):
+        self.reg = reg
+
+    def forward(self, x: GpuTensor) -> GpuTensor:
+        return ops.sigmoid(x, self.reg)
+
+
+class ReLU:
+    """``ReLU::new(&registry)`` (layers/activation.rs:78-96)."""
+
+    def __init__(self, reg: KernelRegistry):
+        self.reg = reg
+
+    def forward(self, x: GpuTensor) -> GpuTensor:
+        return ops.relu(x, self.reg)

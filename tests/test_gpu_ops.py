@@ -438,3 +438,11 @@ def test_matmul_fused_layernorm_accessors_and_with_codegen(reg):
     lin = b200nn.Linear.with_codegen(w, bias, 70, 45, reg, codegen=None)
     y = lin.forward(ta).to_host()
     assert np.abs(y - (a.astype(np.float64) @ w.T.astype(np.float64) + bias)).max() < 5e-3
+    # the zero-parameter activation layers (layers/activation.rs:36-96)
+    x = np.linspace(-6, 6, 501).astype(np.float32)
+    t = GpuTensor.from_host(x, x.shape, reg)
+    sig = 1.0 / (1.0 + np.exp(-x.astype(np.float64)))
+    assert np.abs(b200nn.SiLU(reg).forward(t).to_host() - x * sig).max() < 1e-5
+    assert np.abs(b200nn.Sigmoid(reg).forward(t).to_host() - sig).max() < 1e-6
+    assert np.array_equal(b200nn.ReLU(reg).forward(t).to_host(), np.maximum(x, 0))
+    assert np.array_equal(t.to_host(), x)

@@ -92,6 +92,7 @@ def load_library() -> C.CDLL:
             "b200nn_ctx_read_trace": (i32, [vp, C.POINTER(C.c_longlong)]),
             "b200nn_ctx_read_persist_trace": (i32, [vp, C.POINTER(C.c_uint64), sz]),
             "b200nn_tensor_from_host": (i32, [vp, _f32p, szp, i32, vpp]),
+            "b200nn_tensor_from_device": (i32, [vp, vp, szp, i32, vpp]),
             "b200nn_tensor_zeros": (i32, [vp, szp, i32, vpp]), "b200nn_tensor_to_host": (i32, [vp, _f32p, sz]),
             "b200nn_tensor_ndim": (i32, [vp]), "b200nn_tensor_numel": (sz, [vp]),
             "b200nn_tensor_shape": (i32, [vp, szp, i32]), "b200nn_tensor_reshape": (i32, [vp, szp, i32, vpp]),
@@ -287,6 +288,15 @@ class GpuTensor:
             raise NnError(ERR_SHAPE, f"expected {int(np.prod(shape))} elements, got {a.size}")
         h = C.c_void_p()
         reg.check(reg.lib.b200nn_tensor_from_host(reg.h, p, sh, nd, C.byref(h)))
+        return cls(reg, h)
+
+    @classmethod
+    def from_data(cls, device_ptr: int, shape, reg: KernelRegistry):
+        """``GpuTensor::from_data`` (tensor.rs:67-77): a tensor over f32 data already on the registry's device
+        (``device_ptr`` = its address).  The values are copied; the caller keeps its buffer."""
+        sh, nd = _shape(shape)
+        h = C.c_void_p()
+        reg.check(reg.lib.b200nn_tensor_from_device(reg.h, C.c_void_p(int(device_ptr)), sh, nd, C.byref(h)))
         return cls(reg, h)
 
     @classmethod

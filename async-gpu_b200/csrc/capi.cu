@@ -171,6 +171,20 @@ extern "C" int32_t b200nn_tensor_from_host(b200nn_ctx *ctx, const float *host, c
     *out = t;
     return B200NN_OK;
 }
+extern "C" int32_t b200nn_tensor_from_device(b200nn_ctx *ctx, const float *dev, const size_t *shape, int32_t ndim,
+                                             b200nn_tensor **out) {
+    if (!ctx || !shape || ndim <= 0 || !out) return B200NN_ERR_ARG;
+    b200nn_tensor *t = nullptr;
+    TRY(tensor_alloc(ctx, shape_vec(shape, ndim), false, &t));
+    if (t->numel) {
+        if (!dev) { delete t; return B200NN_ERR_ARG; }
+        cudaError_t e = cudaMemcpyAsync(t->buf->p, dev, t->numel * 4, cudaMemcpyDeviceToDevice, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) { delete t; return set_cuda_error(ctx, e, "tensor_from_device"); }
+    }
+    *out = t;
+    return B200NN_OK;
+}
 extern "C" int32_t b200nn_tensor_zeros(b200nn_ctx *ctx, const size_t *shape, int32_t ndim, b200nn_tensor **out) {
     if (!ctx || !shape || ndim <= 0 || !out) return B200NN_ERR_ARG;
     return tensor_alloc(ctx, shape_vec(shape, ndim), true, out);

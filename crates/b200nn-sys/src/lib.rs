@@ -170,6 +170,13 @@ extern "C" {
         ndim: i32,
         out: *mut *mut b200nn_tensor,
     ) -> i32;
+    pub fn b200nn_tensor_from_device(
+        ctx: *mut b200nn_ctx,
+        dev: *const f32,
+        shape: *const usize,
+        ndim: i32,
+        out: *mut *mut b200nn_tensor,
+    ) -> i32;
     pub fn b200nn_tensor_zeros(
         ctx: *mut b200nn_ctx,
         shape: *const usize,

@@ -156,6 +156,12 @@ B200NN_API int32_t b200nn_ctx_read_persist_trace(b200nn_ctx *ctx, unsigned long 
 B200NN_API int32_t b200nn_tensor_from_host(b200nn_ctx *ctx, const float *host, const size_t *shape, int32_t ndim,
                                            b200nn_tensor **out);
 B200NN_API int32_t b200nn_tensor_zeros(b200nn_ctx *ctx, const size_t *shape, int32_t ndim, b200nn_tensor **out);
+/* GpuTensor::from_data (tensor.rs:67-77): a tensor over data that is already on this context's device.
+ * The reference takes ownership of the caller's device slice; a foreign allocation cannot change owner
+ * across this boundary, so the numel f32 values at dev are copied (device to device, on the context's
+ * stream, complete on return) and the caller keeps its buffer. */
+B200NN_API int32_t b200nn_tensor_from_device(b200nn_ctx *ctx, const float *dev, const size_t *shape, int32_t ndim,
+                                             b200nn_tensor **out);
 B200NN_API int32_t b200nn_tensor_to_host(const b200nn_tensor *t, float *host, size_t capacity_elems);
 B200NN_API int32_t b200nn_tensor_ndim(const b200nn_tensor *t);
 B200NN_API size_t b200nn_tensor_numel(const b200nn_tensor *t);

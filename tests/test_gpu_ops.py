@@ -446,3 +446,17 @@ def test_matmul_fused_layernorm_accessors_and_with_codegen(reg):
     assert np.abs(b200nn.Sigmoid(reg).forward(t).to_host() - sig).max() < 1e-6
     assert np.array_equal(b200nn.ReLU(reg).forward(t).to_host(), np.maximum(x, 0))
     assert np.array_equal(t.to_host(), x)
+    # GpuTensor::from_data (tensor.rs:67-77): over device data of another owner; a copy, so later writes
+    # to the source do not show
+    import torch
+    src = torch.arange(24, dtype=torch.float32, device="cuda").reshape(2, 3, 4) * 0.5
+    torch.cuda.synchronize()
+    d = GpuTensor.from_data(src.data_ptr(), (2, 3, 4), reg)
+    assert d.shape() == (2, 3, 4) and np.array_equal(d.to_host(), src.cpu().numpy())
+    src += 1.0
+    torch.cuda.synchronize()
+    assert np.array_equal(d.to_host(), src.cpu().numpy() - 1.0)
+    own = GpuTensor.from_data(t.data_ptr(), (501,), reg)
+    assert np.array_equal(own.to_host(), x)
+    with pytest.raises(b200nn.NnError):
+        GpuTensor.from_data(0, (4,), reg)

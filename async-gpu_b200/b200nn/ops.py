@@ -96,6 +96,10 @@ def matmul(a: GpuTensor, b: GpuTensor, reg: KernelRegistry):
     return _out(reg, reg.lib.b200nn_matmul(reg.h, a.h, b.h, C.byref(h)), h)
 
 
+# ``matmul_v2`` / ``matmul_v4`` / ``matmul_v4_1`` (ops/gemm.rs:220-346, 353-560, 568-800) are the reference's other
+# kernels for the same contract, [M,K] x [K,N] -> [M,N] row-major; one implementation serves them here.
+matmul_v2 = matmul_v4 = matmul_v4_1 = matmul
+
 FUSED_GELU, FUSED_RELU = "gelu", "relu"  # ``FusedActivation`` (ops/gemm.rs:803-808)
 
 
@@ -163,6 +167,11 @@ def multi_head_flash_attention(q, k, v, seq_len, n_heads, d_head, causal, reg):
     h = C.c_void_p()
     return _out(reg, reg.lib.b200nn_multi_head_flash_attention(reg.h, q.h, k.h, v.h, seq_len, n_heads, d_head,
                                                                int(causal), C.byref(h)), h)
+
+
+# ``multi_head_flash_attention_v3`` / ``_nvrtc`` (ops/attention.rs:210-374): the same contract through the
+# reference's run-time compiled kernels (their last argument is the device; the registry stands for it here).
+multi_head_flash_attention_v3 = multi_head_flash_attention_nvrtc = multi_head_flash_attention
 
 
 def scaled_dot_product_attention(q, k, v, causal, reg):

@@ -129,3 +129,40 @@ def test_null_handles_are_rejected():
     assert lib.b200nn_session_step(None, 1) == b200nn.ERR_ARG
     assert lib.b200nn_tensor_numel(None) == 0
     assert lib.b200nn_kvcache_len(None) == 0
+
+
+def test_mirror_carries_the_reference_names_of_the_path():
+    """The host-side mirror keeps the reference's public names for the GPT-2 inference path, so that a test
+    written against ``gpu_host::nn`` reads the same here (nn/ops/*.rs, nn/layers/*.rs, nn/tensor.rs,
+    nn/models/gpt2.rs, by file)."""
+    want = {
+        ops: ["matmul", "matmul_v2", "matmul_v4", "matmul_v4_1", "matmul_fused", "int4_matmul",           # ops/gemm.rs
+              "layer_norm", "layer_norm_residual", "layer_norm_residual_dual",                             # ops/norm.rs
+              "scaled_dot_product_attention", "scaled_dot_product_attention_kv", "split_qkv", "concat_heads",
+              "multi_head_flash_attention", "multi_head_flash_attention_v3", "multi_head_flash_attention_nvrtc",
+              "gelu", "silu", "sigmoid", "relu",                                                           # ops/activation.rs
+              "bias_add", "elementwise_add", "elementwise_add_out", "embedding_lookup",                    # ops/reshape.rs
+              "quantize_int4_per_group", "quantize_weight_int4", "unpack_int4"],                           # ops/quantize.rs
+        b200nn.GpuTensor: ["from_data", "from_host", "to_host", "zeros", "numel", "ndim", "shape", "strides",
+                           "is_contiguous", "size_bytes", "reshape", "transpose", "clone_tensor", "concat", "split"],
+        b200nn.Linear: ["with_codegen", "forward", "forward_fused", "forward_auto_fused"],
+        b200nn.Int4Linear: ["forward", "memory_bytes"],
+        b200nn.LayerNorm: ["forward", "gamma", "beta"],
+        b200nn.Embedding: ["forward_tokens", "forward_tokens_with_offset"],
+        b200nn.MultiHeadAttention: ["forward_causal", "forward_cached"],
+        b200nn.Int4MultiHeadAttention: ["forward_causal"],
+        b200nn.Gpt2Config: ["small", "medium", "large", "xl", "head_dim", "ffn_dim"],
+        b200nn.Gpt2Model: ["from_weights", "from_generic_weights", "forward", "forward_auto_fused", "forward_profiled",
+                           "forward_features", "embedding_table", "forward_diagnostic", "generate", "forward_cached",
+                           "generate_cached", "forward_early_exit", "generate_cached_early_exit",
+                           "generate_cached_sampling"],
+        b200nn.Int4Gpt2Model: ["from_weights", "from_generic_weights", "group_size", "forward", "generate",
+                               "quantized_memory_bytes"],
+        b200nn.TransformerBlock: ["forward", "forward_auto_fused", "forward_cached"],
+        b200nn.Int4TransformerBlock: ["forward"],
+        b200nn.KernelRegistry: ["init_default"],
+        b200nn.SimpleRng: ["next_f32"],
+        b200nn: ["GELU", "SiLU", "Sigmoid", "ReLU", "KvCache", "top_k_sample", "NnError"],
+    }
+    missing = [f"{getattr(o, '__name__', o)}.{n}" for o, names in want.items() for n in names if not hasattr(o, n)]
+    assert not missing, missing

@@ -166,3 +166,23 @@ def test_mirror_carries_the_reference_names_of_the_path():
     }
     missing = [f"{getattr(o, '__name__', o)}.{n}" for o, names in want.items() for n in names if not hasattr(o, n)]
     assert not missing, missing
+
+
+def test_safe_rust_crate_names_only_what_the_sys_crate_declares():
+    """crates/b200nn (the safe layer with the reference's names; not compiled where there is no cargo): every
+    `sys::` item it uses is declared by crates/b200nn-sys, its brackets balance, and it carries the same types
+    as the C++ host layer it follows (include/b200nn.hpp)."""
+    safe = open(os.path.join(ROOT, "crates", "b200nn", "src", "lib.rs")).read()
+    sysrs = open(os.path.join(ROOT, "crates", "b200nn-sys", "src", "lib.rs")).read()
+    used = sorted(set(re.findall(r"\bsys::(\w+)", safe)))
+    assert len(used) > 60
+    missing = [n for n in used if not re.search(r"\b(fn|const|struct)\s+%s\b" % n, sysrs) and not re.search(r"^\s+%s,$" % n, sysrs, flags=re.M)]
+    assert not missing, missing
+    for o, c in ("{}", "()", "[]"):
+        assert safe.count(o) == safe.count(c)
+    hpp = open(os.path.join(ROOT, "include", "b200nn.hpp")).read()
+    for name in ["KernelRegistry", "GpuTensor", "Linear", "Int4Linear", "LayerNorm", "Embedding", "MultiHeadAttention",
+                 "Gpt2Config", "Gpt2Weights", "TransformerLayerWeights", "Gpt2Model", "Int4Gpt2Model", "KvCache", "SimpleRng",
+                 "NnError", "Activation", "FusedActivation"]:
+        assert re.search(r"\b(struct|enum)\s+%s\b" % name, safe), name
+        assert re.search(r"\b(class|struct|enum class|using)\s+%s\b" % name, hpp), name

@@ -943,3 +943,128 @@ impl Drop for KvCache {
         unsafe { sys::b200nn_kvcache_destroy(self.h) }
     }
 }
+
+/// The twelve slices `TransformerBlock::new` takes (gpt2.rs:120-135), dense weights in Linear layout `[out,in]`.
+#[derive(Clone, Debug, Default)]
+pub struct BlockWeights {
+    pub ln_1_weight: Vec<f32>,
+    pub ln_1_bias: Vec<f32>,
+    pub attn_qkv_weight: Vec<f32>,
+    pub attn_qkv_bias: Vec<f32>,
+    pub attn_out_weight: Vec<f32>,
+    pub attn_out_bias: Vec<f32>,
+    pub ln_2_weight: Vec<f32>,
+    pub ln_2_bias: Vec<f32>,
+    pub ffn_up_weight: Vec<f32>,
+    pub ffn_up_bias: Vec<f32>,
+    pub ffn_down_weight: Vec<f32>,
+    pub ffn_down_bias: Vec<f32>,
+}
+
+/// `TransformerBlock` (gpt2.rs:98-289); `new_int4` is `Int4TransformerBlock::new` (gpt2.rs:1232-1296).
+pub struct TransformerBlock {
+    h: *mut sys::b200nn_block,
+    registry: Arc<KernelRegistry>,
+}
+impl TransformerBlock {
+    fn create(w: &BlockWeights, config: &Gpt2Config, group_size: usize, registry: &Arc<KernelRegistry>) -> Result<Self> {
+        let d = config.n_embd;
+        if w.attn_qkv_weight.len() != 3 * d * d
+            || w.attn_out_weight.len() != d * d
+            || w.ffn_up_weight.len() != 4 * d * d
+            || w.ffn_down_weight.len() != 4 * d * d
+            || w.ln_1_weight.len() != d
+            || w.ln_2_weight.len() != d
+        {
+            return Err(NnError::ShapeMismatch("block weights do not match n_embd".into()));
+        }
+        let cw = sys::b200nn_block_weights {
+            ln_1_weight: w.ln_1_weight.as_ptr(),
+            ln_1_bias: w.ln_1_bias.as_ptr(),
+            attn_qkv_weight: w.attn_qkv_weight.as_ptr(),
+            attn_qkv_bias: w.attn_qkv_bias.as_ptr(),
+            attn_out_weight: w.attn_out_weight.as_ptr(),
+            attn_out_bias: w.attn_out_bias.as_ptr(),
+            ln_2_weight: w.ln_2_weight.as_ptr(),
+            ln_2_bias: w.ln_2_bias.as_ptr(),
+            ffn_up_weight: w.ffn_up_weight.as_ptr(),
+            ffn_up_bias: w.ffn_up_bias.as_ptr(),
+            ffn_down_weight: w.ffn_down_weight.as_ptr(),
+            ffn_down_bias: w.ffn_down_bias.as_ptr(),
+        };
+        let cc = config.to_c();
+        let mut h = ptr::null_mut();
+        let rc = unsafe {
+            if group_size == 0 {
+                sys::b200nn_block_create(registry.as_ptr(), &cc, &cw, 0, &mut h)
+            } else {
+                sys::b200nn_int4_block_create(registry.as_ptr(), &cc, &cw, group_size, 0, &mut h)
+            }
+        };
+        registry.check(rc)?;
+        Ok(Self { h, registry: Arc::clone(registry) })
+    }
+    pub fn new(weights: &BlockWeights, config: &Gpt2Config, registry: &Arc<KernelRegistry>) -> Result<Self> {
+        Self::create(weights, config, 0, registry)
+    }
+    pub fn new_int4(weights: &BlockWeights, config: &Gpt2Config, group_size: usize, registry: &Arc<KernelRegistry>) -> Result<Self> {
+        if group_size == 0 {
+            return Err(NnError::Arg("group_size must be non-zero".into()));
+        }
+        Self::create(weights, config, group_size, registry)
+    }
+    /// `forward` / `forward_auto_fused` (gpt2.rs:172-243, 1299-1339): `x [seq_len,d]` of one sequence, causal
+    pub fn forward(&self, x: &GpuTensor) -> Result<GpuTensor> {
+        let mut y = ptr::null_mut();
+        let rc = unsafe { sys::b200nn_block_forward(self.h, x.handle(), &mut y) };
+        GpuTensor::wrap(&self.registry, rc, y)
+    }
+    pub fn forward_auto_fused(&self, x: &GpuTensor) -> Result<GpuTensor> {
+        self.forward(x)
+    }
+}
+impl Drop for TransformerBlock {
+    fn drop(&mut self) {
+        unsafe { sys::b200nn_block_destroy(self.h) }
+    }
+}
+
+/// The batched generate loop in pieces, state resident on the device (no counterpart in the reference, whose
+/// `generate` handles one sequence): prefill the prompts, run greedy steps without host synchronisation, read tokens.
+pub struct DecodeSession {
+    h: *mut sys::b200nn_session,
+    batch: usize,
+    capacity: usize,
+    registry: Arc<KernelRegistry>,
+}
+impl DecodeSession {
+    pub fn new(model: &Gpt2Model, batch: usize, capacity: usize) -> Result<Self> {
+        let mut h = ptr::null_mut();
+        model.registry.check(unsafe { sys::b200nn_session_create(model.h, batch, capacity, 0, &mut h) })?;
+        Ok(Self { h, batch, capacity, registry: Arc::clone(&model.registry) })
+    }
+    pub fn prefill(&mut self, prompts: &[u32], prompt_len: usize) -> Result<()> {
+        if prompts.len() != self.batch * prompt_len {
+            return Err(NnError::ShapeMismatch("prompts must be [batch,prompt_len]".into()));
+        }
+        self.registry.check(unsafe { sys::b200nn_session_prefill(self.h, prompts.as_ptr(), prompt_len) })
+    }
+    pub fn step(&mut self, n_steps: usize) -> Result<()> {
+        self.registry.check(unsafe { sys::b200nn_session_step(self.h, n_steps) })
+    }
+    pub fn position(&self) -> usize {
+        unsafe { sys::b200nn_session_position(self.h) }
+    }
+    /// Tokens generated so far, one vector per sequence.
+    pub fn tokens(&self) -> Result<Vec<Vec<u32>>> {
+        let mut flat = vec![0u32; self.batch * self.capacity];
+        let mut generated = 0usize;
+        self.registry.check(unsafe { sys::b200nn_session_tokens(self.h, flat.as_mut_ptr(), self.capacity, &mut generated) })?;
+        Ok((0..self.batch).map(|b| flat[b * self.capacity..b * self.capacity + generated].to_vec()).collect())
+    }
+}
+impl Drop for DecodeSession {
+    fn drop(&mut self) {
+        unsafe { sys::b200nn_session_destroy(self.h) }
+    }
+}

@@ -637,5 +637,64 @@ inline KvCache::KvCache(const Gpt2Model &model, size_t batch, size_t capacity) {
     reg_->check(b200nn_kvcache_create(model.handle(), batch, capacity, &h_));
 }
 
+// TransformerBlock (gpt2.rs:98-289) and Int4TransformerBlock (gpt2.rs:1219-1339, group_size > 0): the twelve
+// slices TransformerBlock::new takes, dense weights in Linear layout [out,in].
+struct BlockWeights {
+    std::vector<float> ln_1_weight, ln_1_bias, attn_qkv_weight, attn_qkv_bias, attn_out_weight, attn_out_bias;
+    std::vector<float> ln_2_weight, ln_2_bias, ffn_up_weight, ffn_up_bias, ffn_down_weight, ffn_down_bias;
+};
+class TransformerBlock : public Owned<b200nn_block, b200nn_block_destroy> {
+public:
+    TransformerBlock(const BlockWeights &w, const Gpt2Config &cfg, const Registry &reg, size_t group_size = 0, uint32_t flags = 0) {
+        const size_t d = cfg.n_embd;
+        if (w.attn_qkv_weight.size() != 3 * d * d || w.attn_out_weight.size() != d * d || w.ffn_up_weight.size() != 4 * d * d ||
+            w.ffn_down_weight.size() != 4 * d * d || w.ln_1_weight.size() != d || w.ln_2_weight.size() != d)
+            throw NnError(B200NN_ERR_SHAPE, "block weights do not match n_embd");
+        const b200nn_block_weights cw{w.ln_1_weight.data(), w.ln_1_bias.data(), w.attn_qkv_weight.data(), w.attn_qkv_bias.data(),
+                                      w.attn_out_weight.data(), w.attn_out_bias.data(), w.ln_2_weight.data(), w.ln_2_bias.data(),
+                                      w.ffn_up_weight.data(), w.ffn_up_bias.data(), w.ffn_down_weight.data(), w.ffn_down_bias.data()};
+        const b200nn_gpt2_config cc = cfg.c();
+        reg_ = reg;
+        reg->check(group_size ? b200nn_int4_block_create(reg->ctx(), &cc, &cw, group_size, flags, &h_)
+                              : b200nn_block_create(reg->ctx(), &cc, &cw, flags, &h_));
+    }
+    // forward / forward_auto_fused (gpt2.rs:172-243, 1299-1339): x [seq_len,d] of one sequence, causal
+    GpuTensor forward(const GpuTensor &x) const {
+        b200nn_tensor *y = nullptr;
+        const int32_t rc = b200nn_block_forward(h_, x.handle(), &y);
+        return out_(rc, y);
+    }
+    GpuTensor forward_auto_fused(const GpuTensor &x) const { return forward(x); }
+};
+using Int4TransformerBlock = TransformerBlock;
+
+// The batched generate loop in pieces, state resident on the device (no counterpart in the reference, whose
+// generate handles one sequence): prefill the prompts, run greedy steps without host synchronisation, read tokens.
+class DecodeSession : public Owned<b200nn_session, b200nn_session_destroy> {
+public:
+    DecodeSession(const Gpt2Model &model, size_t batch, size_t capacity, uint32_t flags = 0) : batch_(batch), capacity_(capacity) {
+        reg_ = model.registry();
+        reg_->check(b200nn_session_create(model.handle(), batch, capacity, flags, &h_));
+    }
+    void prefill(const std::vector<uint32_t> &prompts, size_t prompt_len) const {
+        if (prompts.size() != batch_ * prompt_len) throw NnError(B200NN_ERR_SHAPE, "prompts must be [batch,prompt_len]");
+        reg_->check(b200nn_session_prefill(h_, prompts.data(), prompt_len));
+    }
+    void step(size_t n_steps) const { reg_->check(b200nn_session_step(h_, n_steps)); }
+    size_t position() const { return b200nn_session_position(h_); }
+    // tokens generated so far, [batch][generated]
+    std::vector<std::vector<uint32_t>> tokens() const {
+        std::vector<uint32_t> flat(batch_ * capacity_);
+        size_t generated = 0;
+        reg_->check(b200nn_session_tokens(h_, flat.data(), capacity_, &generated));
+        std::vector<std::vector<uint32_t>> out(batch_);
+        for (size_t b = 0; b < batch_; ++b) out[b].assign(flat.begin() + b * capacity_, flat.begin() + b * capacity_ + generated);
+        return out;
+    }
+
+private:
+    size_t batch_, capacity_;
+};
+
 }  // namespace b200nn
 #endif  // B200NN_HPP

@@ -180,6 +180,46 @@ int main() {
     std::vector<uint32_t> first = m4.generate(prompt, 5, 0);
     CHECK(lens.size() == 2 && lens[0] == 11 && std::vector<uint32_t>(both.begin(), both.begin() + 11) == first, "generate_batch row 0 == generate");
     CHECK(throws_code(B200NN_ERR_DIM, [&] { std::vector<uint32_t> far(40, 1); model.forward(far); }), "forward beyond n_positions");
+    // ---- DecodeSession: the batched loop in pieces == generate_batch --------------------------------
+    DecodeSession sess(m4, 2, 16);
+    sess.prefill(p2, 6);
+    sess.step(4);
+    std::vector<std::vector<uint32_t>> st = sess.tokens();
+    CHECK(sess.position() == 6 + 4 && st.size() == 2 && st[0].size() == 5, "DecodeSession position / token count");
+    CHECK(st[0] == std::vector<uint32_t>(both.begin() + 6, both.begin() + 11) &&
+              st[1] == std::vector<uint32_t>(both.begin() + 11 + 6, both.begin() + 22),
+          "DecodeSession tokens == generate_batch");
+
+    // ---- TransformerBlock == its parts composed through the layer classes --------------------------
+    const size_t d = 128;
+    BlockWeights bw;
+    bw.ln_1_weight = normal(31, d, 0.1f); for (float &v : bw.ln_1_weight) v += 1.0f;
+    bw.ln_1_bias = normal(32, d, 0.05f);
+    bw.attn_qkv_weight = normal(33, 3 * d * d, 0.06f); bw.attn_qkv_bias = normal(34, 3 * d, 0.02f);
+    bw.attn_out_weight = normal(35, d * d, 0.06f);     bw.attn_out_bias = normal(36, d, 0.02f);
+    bw.ln_2_weight = normal(37, d, 0.1f); for (float &v : bw.ln_2_weight) v += 1.0f;
+    bw.ln_2_bias = normal(38, d, 0.05f);
+    bw.ffn_up_weight = normal(39, 4 * d * d, 0.06f);   bw.ffn_up_bias = normal(40, 4 * d, 0.02f);
+    bw.ffn_down_weight = normal(41, 4 * d * d, 0.06f); bw.ffn_down_bias = normal(42, d, 0.02f);
+    Gpt2Config bc = cfg;
+    TransformerBlock block(bw, bc, reg);
+    GpuTensor bx = GpuTensor::from_host(normal(43, 3 * d, 1.0f), {3, d}, reg);
+    std::vector<float> by = block.forward(bx).to_host();
+    LayerNorm ln1(bw.ln_1_weight, bw.ln_1_bias, bc.layer_norm_epsilon, reg), ln2(bw.ln_2_weight, bw.ln_2_bias, bc.layer_norm_epsilon, reg);
+    MultiHeadAttention mha(bw.attn_qkv_weight, bw.attn_qkv_bias, bw.attn_out_weight, bw.attn_out_bias, d, bc.n_head, reg);
+    Linear up(bw.ffn_up_weight, &bw.ffn_up_bias, d, 4 * d, reg), down(bw.ffn_down_weight, &bw.ffn_down_bias, 4 * d, d, reg);
+    GpuTensor res1 = ops::elementwise_add_out(bx, mha.forward_causal(ln1.forward(bx)), reg);
+    GpuTensor res2 = ops::elementwise_add_out(res1, down.forward(up.forward_auto_fused(ln2.forward(res1), Activation::Gelu)), reg);
+    std::vector<float> composed = res2.to_host();
+    double bmax = 0;
+    for (size_t i = 0; i < by.size(); ++i) bmax = std::fmax(bmax, std::fabs((double)by[i] - composed[i]));
+    CHECK(by.size() == 3 * d && bmax < 5e-3, "TransformerBlock::forward == LN, attention, MLP composed");
+    Int4TransformerBlock block4(bw, bc, reg, 128);
+    std::vector<float> by4 = block4.forward(bx).to_host();
+    double b4max = 0;
+    for (size_t i = 0; i < by4.size(); ++i) b4max = std::fmax(b4max, std::fabs((double)by4[i] - by[i]));
+    CHECK(b4max > 0 && b4max < 0.5, "Int4TransformerBlock::forward close to the f32 block");
+
     CHECK(reg->device_error() == 0, "device error word");
 
     std::printf("%s %d checks, %d failed\n", g_failed ? "FAILED" : "OK", g_checks, g_failed);

@@ -183,6 +183,6 @@ def test_safe_rust_crate_names_only_what_the_sys_crate_declares():
     hpp = open(os.path.join(ROOT, "include", "b200nn.hpp")).read()
     for name in ["KernelRegistry", "GpuTensor", "Linear", "Int4Linear", "LayerNorm", "Embedding", "MultiHeadAttention",
                  "Gpt2Config", "Gpt2Weights", "TransformerLayerWeights", "Gpt2Model", "Int4Gpt2Model", "KvCache", "SimpleRng",
-                 "NnError", "Activation", "FusedActivation"]:
+                 "NnError", "Activation", "FusedActivation", "TransformerBlock", "BlockWeights", "DecodeSession"]:
         assert re.search(r"\b(struct|enum)\s+%s\b" % name, safe), name
         assert re.search(r"\b(class|struct|enum class|using)\s+%s\b" % name, hpp), name

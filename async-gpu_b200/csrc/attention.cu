@@ -486,7 +486,8 @@ int launch_decode_attention(b200nn_ctx *ctx, const void *q, bool q_half, int ldq
     int pairs = B * H;
     const size_t q_elem = q_half ? 2 : 4;
     // block shape of the TMA-fed kernel by pairs per warp of its grid: 16 warps, else 8 warps, else the split kernel
-    const bool wide = ctx->attn_stream_wide_min10 > 0 && 10LL * pairs >= (long long)ctx->attn_stream_wide_min10 * ctx->sm_count * 16;
+    const bool wide = ctx->attn_stream_wide_min10 > 0 && cap <= 255 * 16 && // a stage's chunk index has eight bits
+                      10LL * pairs >= (long long)ctx->attn_stream_wide_min10 * ctx->sm_count * 16;
     const int s_warps = wide ? 16 : 8, s_rows = wide ? 16 : 32;
     if (ctx->attn_stream && 10LL * pairs >= (long long)ctx->attn_stream_min10 * ctx->sm_count * s_warps &&
         cap <= 255 * s_rows &&
